@@ -1,0 +1,161 @@
+/* sabrewing_b200.h -- C-ABI of the B200-native MoE-block backend.
+ *
+ * Two layers of entry points live in one shared library (libsabrewing_b200.so):
+ *
+ *  1. The lag_cuda_* functions.  Names, argument order, pointer domains (host vs
+ *     device) and return conventions are those of the reference's Laguna CUDA tier,
+ *     c/backend_cuda_laguna.h:25-75, so an engine built against that header links
+ *     against this library unchanged.  0 = ok, -1 = error (the caller falls back to
+ *     its CPU path), upload returns NULL on failure.  Blocking: each call returns
+ *     after its stream has been synchronised.  Not thread-safe (one global stream
+ *     and scratch, like the reference, c/backend_cuda_laguna.cu:11-15).
+ *
+ *  2. The sw_moe_* functions: a descriptor-level, device-resident MoE block.  The
+ *     descriptor is the reference's MoeDesc (c/moe_arch.h:33-41); the layer struct
+ *     carries what the reference's MoeHooks reach through engine state
+ *     (c/moe_arch.h:45-55, c/laguna.c:572-617): router weights, correction bias,
+ *     the int4 expert container and the bf16 shared expert.  One call runs
+ *     route -> top-k -> group-by-expert -> int4 gate/up -> SiLU*up -> int4 down ->
+ *     rank-order combine -> *route_scale -> + shared expert -> out += , with no
+ *     host round trip (what c/moe_block.h:18-54 and c/laguna.c:689-787 do on the CPU).
+ *
+ * All sizes are element counts unless stated.  No function aborts the process.
+ */
+#ifndef SABREWING_B200_H
+#define SABREWING_B200_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------- */
+/* 1. Drop-in Laguna tier (c/backend_cuda_laguna.h)                           */
+/* ------------------------------------------------------------------------- */
+
+/* c/backend_cuda_laguna.h:25 -- select device, create the stream. 0 = ok. */
+int    lag_cuda_init(int dev);
+/* c/backend_cuda_laguna.h:26-27 */
+size_t lag_cuda_free_bytes(void);
+size_t lag_cuda_total_bytes(void);
+/* c/backend_cuda_laguna.h:28-29 -- copy n host bytes into new device memory. */
+void  *lag_cuda_upload(const void *h, size_t n);
+void   lag_cuda_free(void *d);
+/* c/backend_cuda_laguna.h:32 -- y[S,O] = x[S,I] . W^T, W device bf16 [O,I], x/y host f32. */
+int    lag_cuda_matmul_bf16(float *y, const float *x, const void *W, int S, int I, int O);
+/* c/backend_cuda_laguna.h:36 -- W device [int8 O*I][f32 scale O]. */
+int    lag_cuda_matmul_q8(float *y, const float *x, const void *W, int S, int I, int O);
+/* c/backend_cuda_laguna.h:39-40 -- W device packed int4 [O,I/2] + f32 row scales [O]. */
+int    lag_cuda_matmul_q4(float *y, const float *x, const void *packed,
+                          const void *scale, int S, int I, int O);
+/* c/backend_cuda_laguna.h:44-46 -- out[D] = W2 . siluglu(W13 . x), one expert, one row. */
+int    lag_cuda_expert_q4(float *out, const float *x,
+                          const void *p13, const void *s13,
+                          const void *p2, const void *s2, int I, int D);
+/* c/backend_cuda_laguna.h:51-54 -- out[D] = sum_k w[k]*expert(sel[k], x); sel/w host. */
+int    lag_cuda_moe_experts(float *out, const float *x,
+                            const void *gu_q, const float *gu_s,
+                            const void *dn_q, const float *dn_s,
+                            const int *sel, const float *w, int K, int I, int D);
+/* c/backend_cuda_laguna.h:70-75 -- grouped experts over S rows with host index
+ * arrays; acc[S,D] = unscaled weighted routed sum, summed in rank order. */
+int    lag_cuda_moe_group(float *acc, const float *x,
+                          const void *gu_q, const float *gu_s,
+                          const void *dn_q, const float *dn_s,
+                          const int *gexp, const int *gbeg, const int *gcnt, int G,
+                          const int *grow, const int *rowof, const float *w,
+                          int S, int K, int I, int D);
+
+/* ------------------------------------------------------------------------- */
+/* 2. Descriptor-level device-resident MoE block                              */
+/* ------------------------------------------------------------------------- */
+
+/* Router gate activation.  0/1 are the reference's MoeRouteAct (c/moe_arch.h:22);
+ * 2 applies the reference's softplusf (c/moe_math.h:54) as the gate -- the
+ * reference has no router that uses it, so it is checked against the CPU
+ * restatement only. */
+enum { SW_ROUTE_SIGMOID = 0, SW_ROUTE_SOFTMAX = 1, SW_ROUTE_SOFTPLUS = 2 };
+/* Shared-expert policy: the two modes the reference wires (c/moe_arch.h:25-30,
+ * c/moe_block.h:44-51). */
+enum { SW_SHARED_NONE = 0, SW_SHARED_UNSCALED = 1 };
+enum { SW_DTYPE_F32 = 0, SW_DTYPE_BF16 = 1 };
+
+/* Same fields, order and types as MoeDesc (c/moe_arch.h:33-41). */
+typedef struct {
+    int   n_experts;
+    int   topk;
+    int   route_act;
+    int   use_corr_bias;
+    int   norm_topk;
+    float route_scale;
+    int   shared_mode;
+} SwMoeDesc;
+
+/* Device-resident weights of one layer.  The int4 container is the reference's
+ * fused per-layer layout (c/laguna.c:92-96,415-419; c/moe_quant.h:13-14): expert e's
+ * gate rows then up rows start at row e*2I of gu_q [E*2I, D/2] (scales gu_s [E*2I]),
+ * its down rows at row e*D of dn_q [E*D, I/2] (scales dn_s [E*D]); value =
+ * nibble-8, low nibble = even column.  When only a contiguous range of experts is
+ * resident on this GPU (expert-parallel shard), gu_q/gu_s/dn_q/dn_s point at the
+ * rows of expert expert_lo and expert_cnt says how many follow; pairs routed to
+ * other experts contribute nothing here. */
+typedef struct {
+    int D, I, SI;              /* hidden, routed ffn width, shared ffn width (0 if none) */
+    int router_dtype;          /* SW_DTYPE_F32 or SW_DTYPE_BF16 */
+    const void  *router_w;     /* [E, D] */
+    const float *corr_bias;    /* [E] or NULL: added to the score for SELECTION only */
+    const float *logit_bias;   /* [E] or NULL: added to the logits before the gate */
+    const void  *gu_q; const float *gu_s;
+    const void  *dn_q; const float *dn_s;
+    const void  *sh_gate, *sh_up, *sh_down;   /* bf16 [SI,D], [SI,D], [D,SI] or NULL */
+    int expert_lo, expert_cnt; /* resident expert range; expert_cnt<=0 means all */
+} SwMoeLayer;
+
+typedef struct SwMoeCtx SwMoeCtx;
+
+/* Scratch and staging for blocks of up to max_tokens rows.  Allocates device
+ * memory once; sw_moe_forward itself allocates nothing. */
+int  sw_moe_ctx_create(SwMoeCtx **ctx, int dev, int max_tokens, int max_experts, int max_topk,
+                       int max_D, int max_I, int max_SI);
+void sw_moe_ctx_destroy(SwMoeCtx *ctx);
+
+/* out[T,D] += MoE(x[T,D]); x, out device f32; stream is a cudaStream_t (NULL =
+ * the context's own stream).  Asynchronous on that stream.  Residual semantics
+ * follow c/moe_block.h:51 / c/laguna.c:781. */
+int  sw_moe_forward(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer,
+                    const float *x, float *out, int T, void *stream);
+/* Same through HOST buffers: pinned staging, H2D, the block, D2H, stream sync --
+ * the shape of a reference lag_cuda_* call (c/backend_cuda_laguna.cu:516-546).
+ * out_host is read and updated in place. */
+int  sw_moe_forward_host(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer,
+                         const float *x_host, float *out_host, int T);
+
+/* Stages, for expert-parallel drivers and for parity checks.  route: router
+ * logits -> gate -> top-k -> weights -> group-by-expert, results kept in ctx.
+ * experts: routed[T,D] = sum over resident experts of w*expert (unscaled, rank
+ * order, overwrites).  finish: out += routed*route_scale + shared(x). */
+int  sw_moe_route(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer,
+                  const float *x, int T, void *stream);
+int  sw_moe_experts(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer,
+                    const float *x, float *routed, int T, void *stream);
+int  sw_moe_finish(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer,
+                   const float *x, const float *routed, float *out, int T, void *stream);
+
+/* Copy the routing of the last sw_moe_route/forward to host arrays (any may be
+ * NULL): sel,w [T*K]; scores [T*E]; *G; gexp,gbeg,gcnt [E]; grow,rowof [T*K] -- the
+ * arrays of c/laguna.c:709-723.  Synchronises the stream used last. */
+int  sw_moe_get_routing(SwMoeCtx *ctx, int *sel, float *w, float *scores, int *G,
+                        int *gexp, int *gbeg, int *gcnt, int *grow, int *rowof);
+
+/* Device-side status word of the last launches (0 = clean); bit 0: an expert id
+ * outside [0,E) reached the dispatch, bit 1: a row index outside [0,T). */
+int  sw_moe_status(SwMoeCtx *ctx);
+/* Number of kernels launched by this library since load. */
+long long sw_launch_count(void);
+/* Text of the last error on the calling thread's most recent failing call. */
+const char *sw_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -24,7 +24,8 @@
 
 #define ORC_API __attribute__((visibility("default")))
 
-enum { ORC_ROUTE_SIGMOID = 0, ORC_ROUTE_SOFTMAX = 1 };   /* c/moe_arch.h:22 */
+enum { ORC_ROUTE_SIGMOID = 0, ORC_ROUTE_SOFTMAX = 1,     /* c/moe_arch.h:22 */
+       ORC_ROUTE_SOFTPLUS = 2 };                          /* softplusf (c/moe_math.h:54) as the gate; no reference router uses it */
 enum { ORC_SHARED_NONE = 0, ORC_SHARED_UNSCALED = 1 };   /* c/moe_arch.h:25-30 */
 
 /* One MoE layer over plain arrays.  Field meaning follows MoeDesc
@@ -47,6 +48,7 @@ typedef struct {
 
 /* ---------------- scalar math (c/moe_math.h:51-72) ---------------- */
 static inline float orc_bf16_f32(uint16_t b) { uint32_t u = (uint32_t)b << 16; float f; memcpy(&f, &u, 4); return f; }
+static inline float orc_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }   /* c/moe_math.h:54 */
 static inline float orc_silu(float x) { return x / (1.f + expf(-x)); }          /* c/moe_math.h:53 */
 
 /* c/moe_math.h:58-62 */
@@ -215,6 +217,7 @@ ORC_API void orc_route(const OrcLayer *L, const float *x, int S, int exact,
         float *r = rl + (int64_t)s * E;
         if (L->logit_bias) for (int e = 0; e < E; e++) r[e] += L->logit_bias[e];
         if (L->route_act == ORC_ROUTE_SOFTMAX) orc_softmax_row(r, E);
+        else if (L->route_act == ORC_ROUTE_SOFTPLUS) for (int e = 0; e < E; e++) r[e] = orc_softplus(r[e]);
         else for (int e = 0; e < E; e++) r[e] = 1.f / (1.f + expf(-r[e]));
         int *sl = sel + (int64_t)s * K; float *wr = w + (int64_t)s * K;
         orc_topk(r, L->corr_bias, L->use_corr_bias, E, K, sl);

@@ -1,0 +1,434 @@
+// C-ABI of the MoE-block backend: the lag_cuda_* drop-in tier and the
+// descriptor-level sw_moe_* entry points (see include/sabrewing_b200.h).
+#include "sw_common.cuh"
+// the library is built with hidden visibility; only the C-ABI is exported
+#pragma GCC visibility push(default)
+#include "../../include/sabrewing_b200.h"
+#pragma GCC visibility pop
+#include <stdio.h>
+#include <stdarg.h>
+#include <string.h>
+#include <stdlib.h>
+
+static long long g_launches = 0;
+void sw_count_launch(int n) { g_launches += n; }
+extern "C" long long sw_launch_count(void) { return g_launches; }
+
+static thread_local char g_err[256] = "";
+static int sw_fail(const char *fmt, ...) {
+    va_list ap; va_start(ap, fmt); vsnprintf(g_err, sizeof g_err, fmt, ap); va_end(ap);
+    return -1;
+}
+extern "C" const char *sw_last_error(void) { return g_err; }
+
+// A CUDA error is sticky only for faults; plain API failures (OOM, bad argument)
+// are cleared so that the next call starts clean (the reference's hygiene rule,
+// c/backend_cuda.cu:63-69).
+static int sw_cuda_fail(cudaError_t e, const char *what) {
+    cudaGetLastError();
+    return sw_fail("%s: %s", what, cudaGetErrorString(e));
+}
+#define SW_CUDA(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return sw_cuda_fail(e_, #call); } while (0)
+
+// grow-on-demand buffers (2x slack so size churn does not re-allocate every call)
+struct SwBuf {
+    void *p = nullptr; size_t cap = 0; bool pinned = false;
+    int ensure(size_t need) {
+        if (need <= cap) return 0;
+        release();
+        size_t want = need * 2;
+        cudaError_t e = pinned ? cudaMallocHost(&p, want) : cudaMalloc(&p, want);
+        if (e != cudaSuccess) { p = nullptr; cap = 0; cudaGetLastError(); return -1; }
+        cap = want; return 0;
+    }
+    void release() { if (p) { if (pinned) cudaFreeHost(p); else cudaFree(p); } p = nullptr; cap = 0; }
+};
+
+// ===========================================================================
+// Descriptor-level context
+// ===========================================================================
+struct SwMoeCtx {
+    int dev = 0, num_sms = 0;
+    int maxT = 0, maxE = 0, maxK = 0, maxD = 0, maxI = 0, maxSI = 0;
+    cudaStream_t stream = nullptr, last_stream = nullptr;
+    SwRouting r{};
+    float *glu = nullptr, *slots = nullptr, *sglu = nullptr, *so = nullptr, *routed = nullptr;
+    float *dx = nullptr, *dout = nullptr, *hx = nullptr, *hout = nullptr;
+    int lastT = 0, lastK = 0, lastE = 0;
+    void *block = nullptr;      // one device allocation holding all device scratch
+};
+
+static size_t sw_align(size_t n) { return (n + 255) & ~(size_t)255; }
+
+extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int max_experts, int max_topk,
+                                 int max_D, int max_I, int max_SI) {
+    if (!out) return sw_fail("ctx_create: null out");
+    *out = nullptr;
+    if (max_tokens <= 0 || max_experts <= 0 || max_experts > SW_MAX_EXPERTS || max_topk <= 0 ||
+        max_topk > SW_MAX_TOPK || max_D <= 0 || max_I <= 0 || max_SI < 0)
+        return sw_fail("ctx_create: bad limits (experts <= %d, topk <= %d)", SW_MAX_EXPERTS, SW_MAX_TOPK);
+    SW_CUDA(cudaSetDevice(dev));
+    SwMoeCtx *c = new SwMoeCtx();
+    c->dev = dev; c->maxT = max_tokens; c->maxE = max_experts; c->maxK = max_topk;
+    c->maxD = max_D; c->maxI = max_I; c->maxSI = max_SI;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) { delete c; return sw_cuda_fail(cudaGetLastError(), "cudaGetDeviceProperties"); }
+    c->num_sms = prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return sw_cuda_fail(cudaGetLastError(), "cudaStreamCreate"); }
+
+    const size_t T = max_tokens, E = max_experts, K = max_topk, D = max_D, I = max_I, SI = max_SI, P = T * K;
+    size_t sizes[] = {
+        T * E * 4,            // scores
+        P * 4, P * 4,         // sel, w
+        256,                  // G
+        E * 4, E * 4, E * 4,  // gexp gbeg gcnt
+        P * 4, P * 4,         // grow rowof
+        256,                  // status
+        P * I * 4,            // glu
+        P * D * 4,            // slots
+        T * (SI ? SI : 1) * 4,// sglu
+        T * D * 4,            // so
+        T * D * 4,            // routed
+        T * D * 4, T * D * 4  // dx, dout
+    };
+    size_t total = 0; for (size_t s : sizes) total += sw_align(s);
+    if (cudaMalloc(&c->block, total) != cudaSuccess) {
+        cudaGetLastError(); cudaStreamDestroy(c->stream); delete c;
+        return sw_fail("ctx_create: cudaMalloc of %zu bytes failed", total);
+    }
+    char *p = (char *)c->block; int i = 0;
+    auto take = [&](void) { void *q = p; p += sw_align(sizes[i++]); return q; };
+    c->r.scores = (float *)take(); c->r.sel = (int *)take(); c->r.w = (float *)take(); c->r.G = (int *)take();
+    c->r.gexp = (int *)take(); c->r.gbeg = (int *)take(); c->r.gcnt = (int *)take();
+    c->r.grow = (int *)take(); c->r.rowof = (int *)take(); c->r.status = (int *)take();
+    c->glu = (float *)take(); c->slots = (float *)take(); c->sglu = (float *)take(); c->so = (float *)take();
+    c->routed = (float *)take(); c->dx = (float *)take(); c->dout = (float *)take();
+    cudaMemsetAsync(c->r.G, 0, 256, c->stream); cudaMemsetAsync(c->r.status, 0, 256, c->stream);
+    if (cudaMallocHost((void **)&c->hx, T * D * 4) != cudaSuccess || cudaMallocHost((void **)&c->hout, T * D * 4) != cudaSuccess) {
+        cudaGetLastError(); sw_moe_ctx_destroy(c);
+        return sw_fail("ctx_create: pinned staging allocation failed");
+    }
+    SW_CUDA(cudaStreamSynchronize(c->stream));
+    *out = c;
+    return 0;
+}
+
+extern "C" void sw_moe_ctx_destroy(SwMoeCtx *c) {
+    if (!c) return;
+    cudaSetDevice(c->dev);
+    if (c->stream) { cudaStreamSynchronize(c->stream); cudaStreamDestroy(c->stream); }
+    if (c->block) cudaFree(c->block);
+    if (c->hx) cudaFreeHost(c->hx);
+    if (c->hout) cudaFreeHost(c->hout);
+    delete c;
+}
+
+static int sw_check(const SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, int T) {
+    if (!c || !d || !L) return sw_fail("null argument");
+    if (T < 0 || T > c->maxT) return sw_fail("T=%d outside [0,%d]", T, c->maxT);
+    if (d->n_experts <= 0 || d->n_experts > c->maxE) return sw_fail("n_experts=%d outside (0,%d]", d->n_experts, c->maxE);
+    if (d->topk <= 0 || d->topk > c->maxK || d->topk > d->n_experts) return sw_fail("topk=%d invalid", d->topk);
+    if (d->route_act < 0 || d->route_act > 2) return sw_fail("route_act=%d unknown", d->route_act);
+    if (d->shared_mode != SW_SHARED_NONE && d->shared_mode != SW_SHARED_UNSCALED)
+        return sw_fail("shared_mode=%d is not wired (the reference wires NONE and UNSCALED only)", d->shared_mode);
+    if (L->D <= 0 || L->D > c->maxD || L->D % 32) return sw_fail("D=%d must be a multiple of 32 and <= %d", L->D, c->maxD);
+    if (L->I <= 0 || L->I > c->maxI || L->I % 32) return sw_fail("I=%d must be a multiple of 32 and <= %d", L->I, c->maxI);
+    if (d->shared_mode != SW_SHARED_NONE) {
+        if (L->SI <= 0 || L->SI > c->maxSI || L->SI % 8) return sw_fail("SI=%d must be a multiple of 8 and <= %d", L->SI, c->maxSI);
+        if (!L->sh_gate || !L->sh_up || !L->sh_down) return sw_fail("shared expert weights missing");
+    }
+    if (!L->router_w || !L->gu_q || !L->gu_s || !L->dn_q || !L->dn_s) return sw_fail("layer weights missing");
+    if (L->router_dtype != SW_DTYPE_F32 && L->router_dtype != SW_DTYPE_BF16) return sw_fail("router_dtype=%d unknown", L->router_dtype);
+    return 0;
+}
+
+static void sw_resident(const SwMoeDesc *d, const SwMoeLayer *L, int *lo, int *cnt) {
+    if (L->expert_cnt > 0) { *lo = L->expert_lo; *cnt = L->expert_cnt; }
+    else { *lo = 0; *cnt = d->n_experts; }
+}
+
+static int sw_route_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, int T, cudaStream_t st) {
+    SwLaunchCfg cfg{c->num_sms, st};
+    const int E = d->n_experts, K = d->topk;
+    if (sw_launch_router_logits(cfg, x, L->router_w, L->router_dtype, L->logit_bias, c->r.scores, T, L->D, E)) return sw_fail("router_logits launch failed");
+    if (sw_launch_route_topk(cfg, c->r.scores, L->corr_bias, d->use_corr_bias, d->route_act, d->norm_topk, T, E, K, c->r.sel, c->r.w)) return sw_fail("route_topk launch failed");
+    if (sw_launch_dispatch(cfg, c->r, T, K, E)) return sw_fail("dispatch launch failed");
+    c->last_stream = st; c->lastT = T; c->lastK = K; c->lastE = E;
+    return 0;
+}
+
+static int sw_expert_stage(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, int T, cudaStream_t st) {
+    SwLaunchCfg cfg{c->num_sms, st};
+    int lo, cnt; sw_resident(d, L, &lo, &cnt);
+    const int K = d->topk, E = d->n_experts;
+    SwQ4Args a{};
+    a.gexp = c->r.gexp; a.gbeg = c->r.gbeg; a.gcnt = c->r.gcnt; a.G = c->r.G; a.grow = c->r.grow;
+    a.expert_lo = lo; a.expert_cnt = cnt;
+    a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K;
+    a.q = (const uint8_t *)L->gu_q; a.s = L->gu_s; a.X = x; a.Y = c->glu; a.KD = L->D; a.OUT = L->I;
+    if (sw_launch_q4_gateup(cfg, a)) return sw_fail("gate/up launch failed");
+    a.q = (const uint8_t *)L->dn_q; a.s = L->dn_s; a.X = c->glu; a.Y = c->slots; a.KD = L->I; a.OUT = L->D;
+    if (sw_launch_q4_down(cfg, a)) return sw_fail("down launch failed");
+    return 0;
+}
+
+static int sw_shared_stage(SwMoeCtx *c, const SwMoeLayer *L, const float *x, int T, cudaStream_t st) {
+    SwLaunchCfg cfg{c->num_sms, st};
+    if (sw_launch_bf16_gateup(cfg, x, L->sh_gate, L->sh_up, c->sglu, T, L->D, L->SI)) return sw_fail("shared gate/up launch failed");
+    if (sw_launch_bf16_rows(cfg, c->sglu, L->sh_down, c->so, T, L->SI, L->D)) return sw_fail("shared down launch failed");
+    return 0;
+}
+
+extern "C" int sw_moe_route(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, int T, void *stream) {
+    if (sw_check(c, d, L, T)) return -1;
+    if (T == 0) return 0;
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    return sw_route_impl(c, d, L, x, T, st);
+}
+
+extern "C" int sw_moe_experts(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, float *routed, int T, void *stream) {
+    if (sw_check(c, d, L, T)) return -1;
+    if (T == 0) return 0;
+    if (c->lastT != T || c->lastK != d->topk || c->lastE != d->n_experts) return sw_fail("experts: no matching sw_moe_route before this call");
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    if (sw_expert_stage(c, d, L, x, T, st)) return -1;
+    SwLaunchCfg cfg{c->num_sms, st};
+    int lo, cnt; sw_resident(d, L, &lo, &cnt);
+    if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, nullptr, routed, T, d->topk, L->D, 1.f, 0, lo, cnt)) return sw_fail("combine launch failed");
+    return 0;
+}
+
+extern "C" int sw_moe_finish(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, const float *routed, float *out, int T, void *stream) {
+    if (sw_check(c, d, L, T)) return -1;
+    if (T == 0) return 0;
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    SwLaunchCfg cfg{c->num_sms, st};
+    const int has_shared = d->shared_mode != SW_SHARED_NONE;
+    if (has_shared && sw_shared_stage(c, L, x, T, st)) return -1;
+    if (sw_launch_finish(cfg, routed, c->so, out, T, L->D, d->route_scale, has_shared)) return sw_fail("finish launch failed");
+    return 0;
+}
+
+extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, float *out, int T, void *stream) {
+    if (sw_check(c, d, L, T)) return -1;
+    if (T == 0) return 0;
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    if (sw_route_impl(c, d, L, x, T, st)) return -1;
+    if (sw_expert_stage(c, d, L, x, T, st)) return -1;
+    const int has_shared = d->shared_mode != SW_SHARED_NONE;
+    if (has_shared && sw_shared_stage(c, L, x, T, st)) return -1;
+    SwLaunchCfg cfg{c->num_sms, st};
+    int lo, cnt; sw_resident(d, L, &lo, &cnt);
+    if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, c->so, out, T, d->topk, L->D,
+                          d->route_scale, 1 | (has_shared ? 2 : 0) | 4, lo, cnt)) return sw_fail("combine launch failed");
+    return 0;
+}
+
+extern "C" int sw_moe_forward_host(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x_host, float *out_host, int T) {
+    if (sw_check(c, d, L, T)) return -1;
+    if (T == 0) return 0;
+    if (!x_host || !out_host) return sw_fail("forward_host: null buffer");
+    const size_t n = (size_t)T * L->D * sizeof(float);
+    memcpy(c->hx, x_host, n); memcpy(c->hout, out_host, n);
+    SW_CUDA(cudaMemcpyAsync(c->dx, c->hx, n, cudaMemcpyHostToDevice, c->stream));
+    SW_CUDA(cudaMemcpyAsync(c->dout, c->hout, n, cudaMemcpyHostToDevice, c->stream));
+    if (sw_moe_forward(c, d, L, c->dx, c->dout, T, c->stream)) return -1;
+    SW_CUDA(cudaMemcpyAsync(c->hout, c->dout, n, cudaMemcpyDeviceToHost, c->stream));
+    SW_CUDA(cudaStreamSynchronize(c->stream));
+    memcpy(out_host, c->hout, n);
+    return 0;
+}
+
+extern "C" int sw_moe_get_routing(SwMoeCtx *c, int *sel, float *w, float *scores, int *G,
+                                  int *gexp, int *gbeg, int *gcnt, int *grow, int *rowof) {
+    if (!c) return sw_fail("null ctx");
+    if (c->lastT <= 0) return sw_fail("get_routing: nothing routed yet");
+    SW_CUDA(cudaStreamSynchronize(c->last_stream));
+    const size_t P = (size_t)c->lastT * c->lastK, E = c->lastE;
+    if (sel)    SW_CUDA(cudaMemcpy(sel, c->r.sel, P * 4, cudaMemcpyDeviceToHost));
+    if (w)      SW_CUDA(cudaMemcpy(w, c->r.w, P * 4, cudaMemcpyDeviceToHost));
+    if (scores) SW_CUDA(cudaMemcpy(scores, c->r.scores, (size_t)c->lastT * E * 4, cudaMemcpyDeviceToHost));
+    if (G)      SW_CUDA(cudaMemcpy(G, c->r.G, 4, cudaMemcpyDeviceToHost));
+    if (gexp)   SW_CUDA(cudaMemcpy(gexp, c->r.gexp, E * 4, cudaMemcpyDeviceToHost));
+    if (gbeg)   SW_CUDA(cudaMemcpy(gbeg, c->r.gbeg, E * 4, cudaMemcpyDeviceToHost));
+    if (gcnt)   SW_CUDA(cudaMemcpy(gcnt, c->r.gcnt, E * 4, cudaMemcpyDeviceToHost));
+    if (grow)   SW_CUDA(cudaMemcpy(grow, c->r.grow, P * 4, cudaMemcpyDeviceToHost));
+    if (rowof)  SW_CUDA(cudaMemcpy(rowof, c->r.rowof, P * 4, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+extern "C" int sw_moe_status(SwMoeCtx *c) {
+    if (!c) return -1;
+    int s = 0;
+    if (c->last_stream) cudaStreamSynchronize(c->last_stream);
+    if (cudaMemcpy(&s, c->r.status, 4, cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return -1; }
+    return s;
+}
+
+// ===========================================================================
+// lag_cuda_* drop-in tier: host pointers in, host pointers out, one sync per call.
+// ===========================================================================
+static struct {
+    int ok = 0, dev = 0, num_sms = 0;
+    cudaStream_t st = nullptr;
+    SwBuf dx, dy, dglu, dslot, didx, dmisc;
+    SwBuf hx{nullptr, 0, true}, hy{nullptr, 0, true}, hidx{nullptr, 0, true};
+} g_lag;
+
+extern "C" int lag_cuda_init(int dev) {
+    cudaSetDeviceFlags(cudaDeviceScheduleSpin);   // many short blocking calls per token (c/backend_cuda_laguna.cu:17-21)
+    cudaGetLastError();
+    if (cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); return -1; }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (!g_lag.st && cudaStreamCreate(&g_lag.st) != cudaSuccess) { cudaGetLastError(); return -1; }
+    void *probe = nullptr;
+    if (cudaMalloc(&probe, 1 << 20) != cudaSuccess) { cudaGetLastError(); return -1; }
+    cudaFree(probe);
+    g_lag.dev = dev; g_lag.num_sms = prop.multiProcessorCount; g_lag.ok = 1;
+    return 0;
+}
+extern "C" size_t lag_cuda_free_bytes(void) {
+    size_t fr = 0, to = 0;
+    if (cudaMemGetInfo(&fr, &to) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return fr;
+}
+extern "C" size_t lag_cuda_total_bytes(void) {
+    size_t fr = 0, to = 0;
+    if (cudaMemGetInfo(&fr, &to) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return to;
+}
+extern "C" void *lag_cuda_upload(const void *h, size_t n) {
+    void *d = nullptr;
+    if (cudaMalloc(&d, n ? n : 1) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (n && cudaMemcpy(d, h, n, cudaMemcpyHostToDevice) != cudaSuccess) { cudaGetLastError(); cudaFree(d); return nullptr; }
+    return d;
+}
+extern "C" void lag_cuda_free(void *d) { if (d) cudaFree(d); }
+
+// stage x (xn bytes) to the device, run `body`, bring yn bytes of dy back to y
+template <typename F>
+static int lag_roundtrip(float *y, const float *x, size_t xn, size_t yn, F body) {
+    if (g_lag.dx.ensure(xn) || g_lag.dy.ensure(yn) || g_lag.hx.ensure(xn) || g_lag.hy.ensure(yn)) return -1;
+    memcpy(g_lag.hx.p, x, xn);
+    if (cudaMemcpyAsync(g_lag.dx.p, g_lag.hx.p, xn, cudaMemcpyHostToDevice, g_lag.st) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (body()) return -1;
+    if (cudaMemcpyAsync(g_lag.hy.p, g_lag.dy.p, yn, cudaMemcpyDeviceToHost, g_lag.st) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (cudaStreamSynchronize(g_lag.st) != cudaSuccess) { cudaGetLastError(); return -1; }
+    memcpy(y, g_lag.hy.p, yn);
+    return 0;
+}
+
+extern "C" int lag_cuda_matmul_bf16(float *y, const float *x, const void *W, int S, int I, int O) {
+    if (!g_lag.ok || S <= 0 || I <= 0 || O <= 0 || (I & 7)) return -1;
+    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st};
+    return lag_roundtrip(y, x, (size_t)S * I * 4, (size_t)S * O * 4, [&] {
+        return sw_launch_bf16_rows(cfg, (const float *)g_lag.dx.p, W, (float *)g_lag.dy.p, S, I, O);
+    });
+}
+extern "C" int lag_cuda_matmul_q8(float *y, const float *x, const void *W, int S, int I, int O) {
+    if (!g_lag.ok || S <= 0 || I <= 0 || O <= 0) return -1;
+    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st};
+    const int8_t *q8 = (const int8_t *)W;
+    const float *scale = (const float *)(q8 + (size_t)I * O);
+    return lag_roundtrip(y, x, (size_t)S * I * 4, (size_t)S * O * 4, [&] {
+        return sw_launch_q8_rows(cfg, (const float *)g_lag.dx.p, q8, scale, (float *)g_lag.dy.p, S, I, O);
+    });
+}
+
+// index block on the device: [G | gexp(n) | gbeg(n) | gcnt(n) | grow(P) | rowof(P) | sel(P) | w(P)]
+struct LagIdx { int *G, *gexp, *gbeg, *gcnt, *grow, *rowof, *sel; float *w; };
+static int lag_stage_idx(LagIdx *d, const int *gexp, const int *gbeg, const int *gcnt, int G,
+                         const int *grow, const int *rowof, const float *w, int P) {
+    size_t nint = 64 + (size_t)3 * G + 3 * (size_t)P, bytes = (nint + P) * 4;
+    if (g_lag.didx.ensure(bytes) || g_lag.hidx.ensure(bytes)) return -1;
+    int *h = (int *)g_lag.hidx.p;
+    h[0] = G;
+    int *hp = h + 64;
+    memcpy(hp, gexp, (size_t)G * 4); hp += G;
+    memcpy(hp, gbeg, (size_t)G * 4); hp += G;
+    memcpy(hp, gcnt, (size_t)G * 4); hp += G;
+    memcpy(hp, grow, (size_t)P * 4); hp += P;
+    memcpy(hp, rowof, (size_t)P * 4); hp += P;
+    for (int i = 0; i < P; i++) hp[i] = 0;          // sel: every pair resident (expert 0 of a 1-expert window)
+    hp += P;
+    memcpy(hp, w, (size_t)P * 4);
+    if (cudaMemcpyAsync(g_lag.didx.p, h, bytes, cudaMemcpyHostToDevice, g_lag.st) != cudaSuccess) { cudaGetLastError(); return -1; }
+    int *dp = (int *)g_lag.didx.p;
+    d->G = dp; dp += 64;
+    d->gexp = dp; dp += G; d->gbeg = dp; dp += G; d->gcnt = dp; dp += G;
+    d->grow = dp; dp += P; d->rowof = dp; dp += P; d->sel = dp; dp += P; d->w = (float *)dp;
+    return 0;
+}
+
+// Core of the grouped entry points.  Expert ids in gexp index the blobs directly.
+static int lag_group_core(float *acc, const float *x, const void *gu_q, const float *gu_s,
+                          const void *dn_q, const float *dn_s,
+                          const int *gexp, const int *gbeg, const int *gcnt, int G,
+                          const int *grow, const int *rowof, const float *w, int S, int K, int I, int D) {
+    if (!g_lag.ok || S <= 0 || K <= 0 || G <= 0 || (D % 32) || (I % 32)) return -1;
+    const int P = S * K;
+    if (g_lag.dglu.ensure((size_t)P * I * 4) || g_lag.dslot.ensure((size_t)P * D * 4)) return -1;
+    LagIdx ix;
+    if (lag_stage_idx(&ix, gexp, gbeg, gcnt, G, grow, rowof, w, P)) return -1;
+    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st};
+    return lag_roundtrip(acc, x, (size_t)S * D * 4, (size_t)S * D * 4, [&] {
+        SwQ4Args a{};
+        a.gexp = ix.gexp; a.gbeg = ix.gbeg; a.gcnt = ix.gcnt; a.G = ix.G; a.grow = ix.grow;
+        a.expert_lo = 0; a.expert_cnt = 0x7fffffff; a.max_groups = G; a.max_rows = P;
+        a.q = (const uint8_t *)gu_q; a.s = gu_s; a.X = (const float *)g_lag.dx.p; a.Y = (float *)g_lag.dglu.p; a.KD = D; a.OUT = I;
+        if (sw_launch_q4_gateup(cfg, a)) return -1;
+        a.q = (const uint8_t *)dn_q; a.s = dn_s; a.X = (const float *)g_lag.dglu.p; a.Y = (float *)g_lag.dslot.p; a.KD = I; a.OUT = D;
+        if (sw_launch_q4_down(cfg, a)) return -1;
+        return sw_launch_combine(cfg, (const float *)g_lag.dslot.p, ix.rowof, ix.sel, ix.w, nullptr, (float *)g_lag.dy.p,
+                                 S, K, D, 1.f, 0, 0, 1);
+    });
+}
+
+extern "C" int lag_cuda_moe_group(float *acc, const float *x, const void *gu_q, const float *gu_s,
+                                  const void *dn_q, const float *dn_s,
+                                  const int *gexp, const int *gbeg, const int *gcnt, int G,
+                                  const int *grow, const int *rowof, const float *w,
+                                  int S, int K, int I, int D) {
+    return lag_group_core(acc, x, gu_q, gu_s, dn_q, dn_s, gexp, gbeg, gcnt, G, grow, rowof, w, S, K, I, D);
+}
+
+extern "C" int lag_cuda_moe_experts(float *out, const float *x, const void *gu_q, const float *gu_s,
+                                    const void *dn_q, const float *dn_s,
+                                    const int *sel, const float *w, int K, int I, int D) {
+    if (K <= 0 || K > 4096) return -1;
+    // one row: each selection is its own group of one packed row, kept in the caller's order
+    int *tmp = (int *)malloc((size_t)K * 5 * sizeof(int));
+    if (!tmp) return -1;
+    int *gbeg = tmp, *gcnt = tmp + K, *grow = tmp + 2 * K, *rowof = tmp + 3 * K;
+    for (int k = 0; k < K; k++) { gbeg[k] = k; gcnt[k] = 1; grow[k] = 0; rowof[k] = k; }
+    int rc = lag_group_core(out, x, gu_q, gu_s, dn_q, dn_s, sel, gbeg, gcnt, K, grow, rowof, w, 1, K, I, D);
+    free(tmp);
+    return rc;
+}
+
+extern "C" int lag_cuda_expert_q4(float *out, const float *x, const void *p13, const void *s13,
+                                  const void *p2, const void *s2, int I, int D) {
+    const int zero = 0, one = 1; const float w1 = 1.f;
+    return lag_group_core(out, x, p13, (const float *)s13, p2, (const float *)s2, &zero, &zero, &one, 1, &zero, &zero, &w1, 1, 1, I, D);
+}
+
+extern "C" int lag_cuda_matmul_q4(float *y, const float *x, const void *packed, const void *scale, int S, int I, int O) {
+    if (!g_lag.ok || S <= 0 || O <= 0 || I <= 0 || (I % 32)) return -1;
+    // a single group of S packed rows through the row-output form of the grouped kernel
+    if (g_lag.dmisc.ensure(256 * 4)) return -1;
+    int h[256] = {0};
+    h[0] = 1; h[64] = 0; h[65] = 0; h[66] = S;      // G | gexp gbeg gcnt
+    if (cudaMemcpyAsync(g_lag.dmisc.p, h, sizeof h, cudaMemcpyHostToDevice, g_lag.st) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (cudaStreamSynchronize(g_lag.st) != cudaSuccess) { cudaGetLastError(); return -1; }   // h is a stack buffer
+    int *dm = (int *)g_lag.dmisc.p;
+    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st};
+    return lag_roundtrip(y, x, (size_t)S * I * 4, (size_t)S * O * 4, [&] {
+        SwQ4Args a{};
+        a.G = dm; a.gexp = dm + 64; a.gbeg = dm + 65; a.gcnt = dm + 66; a.grow = nullptr;
+        a.expert_lo = 0; a.expert_cnt = 1; a.max_groups = 1; a.max_rows = S;
+        a.q = (const uint8_t *)packed; a.s = (const float *)scale; a.X = (const float *)g_lag.dx.p; a.Y = (float *)g_lag.dy.p;
+        a.KD = I; a.OUT = O;
+        return sw_launch_q4_down(cfg, a);
+    });
+}

@@ -1,0 +1,66 @@
+// Shared declarations of the MoE-block kernels and their host launchers.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define SW_FULL_MASK 0xffffffffu
+#define SW_MAX_EXPERTS 1024     // top-k keeps <= 32 scores per lane
+#define SW_MAX_TOPK 32
+
+// Status bits written by kernels into SwRouting::status.
+#define SW_ST_BAD_EXPERT 1
+#define SW_ST_BAD_ROW    2
+
+// Routing + dispatch arrays of one block call (device pointers).  Names follow
+// the reference's host arrays (c/laguna.c:709-723).
+struct SwRouting {
+    float *scores;   // [T,E] logits in, gate scores out
+    int   *sel;      // [T,K] expert ids, rank order
+    float *w;        // [T,K] combine weights
+    int   *G;        // [1]   number of non-empty groups
+    int   *gexp, *gbeg, *gcnt;   // [E]
+    int   *grow;     // [T*K] packed row -> token row
+    int   *rowof;    // [T*K] (token, rank) -> packed row
+    int   *status;   // [1]
+};
+
+struct SwLaunchCfg {
+    int num_sms;
+    cudaStream_t stream;
+};
+
+void sw_count_launch(int n = 1);
+
+// sw_route.cu
+int sw_launch_router_logits(const SwLaunchCfg &c, const float *x, const void *W, int w_dtype,
+                            const float *logit_bias, float *rl, int T, int D, int E);
+int sw_launch_route_topk(const SwLaunchCfg &c, float *scores, const float *corr_bias, int use_bias,
+                         int route_act, int norm_topk, int T, int E, int K, int *sel, float *w);
+int sw_launch_dispatch(const SwLaunchCfg &c, const SwRouting &r, int T, int K, int E);
+
+// sw_experts.cu
+struct SwQ4Args {
+    const uint8_t *q; const float *s;     // blob of the first resident expert
+    const float *X; float *Y;
+    const int *gexp, *gbeg, *gcnt, *G, *grow;
+    int KD;            // contraction length
+    int OUT;           // gate/up: I (pairs of rows); down: rows
+    int expert_lo, expert_cnt;
+    int max_groups;    // upper bound on *G known on the host
+    int max_rows;      // upper bound on rows of all groups together (T*K)
+};
+int sw_launch_q4_gateup(const SwLaunchCfg &c, const SwQ4Args &a);
+int sw_launch_q4_down(const SwLaunchCfg &c, const SwQ4Args &a);
+int sw_launch_bf16_gateup(const SwLaunchCfg &c, const float *x, const void *Wg, const void *Wu,
+                          float *sglu, int T, int D, int SI);
+int sw_launch_bf16_rows(const SwLaunchCfg &c, const float *x, const void *W, float *y, int T, int I, int O);
+int sw_launch_q8_rows(const SwLaunchCfg &c, const float *x, const int8_t *W, const float *scale,
+                      float *y, int T, int I, int O);
+// out/routed combine.  mode bits: 1 = multiply by route_scale, 2 = add `add` rows
+// (shared expert output), 4 = accumulate into out (else overwrite).
+int sw_launch_combine(const SwLaunchCfg &c, const float *slots, const int *rowof, const int *sel,
+                      const float *w, const float *add, float *out, int T, int K, int D,
+                      float route_scale, int mode, int expert_lo, int expert_cnt);
+int sw_launch_finish(const SwLaunchCfg &c, const float *routed, const float *add, float *out,
+                     int T, int D, float route_scale, int has_add);

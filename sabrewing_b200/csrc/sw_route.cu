@@ -1,0 +1,280 @@
+// Router logits, gate activation + top-k, and the device-side group-by-expert
+// dispatch (histogram, prefix scan, stable permute) of the MoE block.
+//
+// Reference behaviour restated here:
+//   router logits   c/laguna.c:574-576,698 (matmul_f32; exact contract c/moe_matmul.h:46-54)
+//   gate            c/moe_block.h:25-26, softmax_row c/moe_math.h:68-72, softplusf c/moe_math.h:54
+//   top-k           moe_topk, c/moe_arch.h:64-89
+//   weights         c/moe_block.h:30-31, c/laguna.c:704-705
+//   dispatch        counting sort, c/laguna.c:709-723
+#include "sw_common.cuh"
+
+// ---------------------------------------------------------------------------
+// Router logits: rl[t,e] = (float) sum_k (double)x[t,k]*W[e,k]  (+ logit_bias[e]).
+// One warp per expert row, TT tokens per pass, fp64 accumulation: the product of
+// two f32 is exact in fp64, so only the order of the additions differs from the
+// reference's sequential double sum, and the result is rounded to f32 once.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void sw_load8(const float *p, float (&v)[8]) {
+    float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void sw_load8(const __nv_bfloat16 *p, float (&v)[8]) {
+    uint4 r = *reinterpret_cast<const uint4 *>(p);
+    uint32_t u[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        v[2 * i]     = __uint_as_float(u[i] << 16);
+        v[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+}
+
+template <typename WT, int TT>
+__global__ void __launch_bounds__(256)
+k_router_logits(const float *__restrict__ x, const WT *__restrict__ W, const float *__restrict__ lbias,
+                float *__restrict__ rl, int T, int D, int E) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * 8 + warp;
+    const int t0 = blockIdx.y * TT;
+    if (e >= E) return;
+    double acc[TT];
+#pragma unroll
+    for (int t = 0; t < TT; t++) acc[t] = 0.0;
+    const WT *wr = W + (size_t)e * D;
+    for (int k = lane * 8; k < D; k += 256) {
+        float wv[8];
+        sw_load8(wr + k, wv);
+#pragma unroll
+        for (int t = 0; t < TT; t++) {
+            if (t0 + t < T) {
+                float xv[8];
+                sw_load8(x + (size_t)(t0 + t) * D + k, xv);
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc[t] = fma((double)xv[i], (double)wv[i], acc[t]);
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < TT; t++) {
+        double a = acc[t];
+#pragma unroll
+        for (int off = 16; off; off >>= 1) a += __shfl_xor_sync(SW_FULL_MASK, a, off);
+        if (lane == 0 && t0 + t < T) {
+            float r = (float)a;
+            if (lbias) r += lbias[e];
+            rl[(size_t)(t0 + t) * E + e] = r;
+        }
+    }
+}
+
+int sw_launch_router_logits(const SwLaunchCfg &c, const float *x, const void *W, int w_dtype,
+                            const float *logit_bias, float *rl, int T, int D, int E) {
+    if (T <= 0) return 0;
+    if (D % 8) return -1;
+    constexpr int TT = 4;
+    dim3 grid((E + 7) / 8, (T + TT - 1) / TT);
+    if (w_dtype == 1)
+        k_router_logits<__nv_bfloat16, TT><<<grid, 256, 0, c.stream>>>(x, (const __nv_bfloat16 *)W, logit_bias, rl, T, D, E);
+    else
+        k_router_logits<float, TT><<<grid, 256, 0, c.stream>>>(x, (const float *)W, logit_bias, rl, T, D, E);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// ---------------------------------------------------------------------------
+// Gate activation + top-k + combine weights: one warp per token.
+// exp/log1p are evaluated in fp64 and rounded to f32, which reproduces a
+// correctly rounded expf; every other operation is the reference's f32 sequence.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float sw_expf_cr(float v) { return (float)exp((double)v); }
+
+__global__ void __launch_bounds__(128)
+k_route_topk(float *__restrict__ scores, const float *__restrict__ corr_bias, int use_bias,
+             int route_act, int norm_topk, int T, int E, int K,
+             int *__restrict__ sel, float *__restrict__ w) {
+    __shared__ float s_sc[4][SW_MAX_EXPERTS];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= T) return;
+    float *r = scores + (size_t)t * E;
+    float *sc = s_sc[warp];
+
+    if (route_act == 1) {                        // softmax_row
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) { float v = r[e]; if (v > m) m = v; }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) { float o = __shfl_xor_sync(SW_FULL_MASK, m, off); if (o > m) m = o; }
+        float r0 = r[0];
+        if (r0 != r0) m = r0;                    // the reference's max starts from x[0]: a NaN there sticks
+        double s = 0.0;
+        for (int e = lane; e < E; e += 32) { float v = sw_expf_cr(r[e] - m); sc[e] = v; s += (double)v; }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) s += __shfl_xor_sync(SW_FULL_MASK, s, off);
+        float inv = (float)(1.0 / s);
+        for (int e = lane; e < E; e += 32) sc[e] *= inv;
+    } else if (route_act == 0) {                 // sigmoid
+        for (int e = lane; e < E; e += 32) sc[e] = 1.f / (1.f + sw_expf_cr(-r[e]));
+    } else {                                     // softplus
+        for (int e = lane; e < E; e += 32) {
+            float v = r[e];
+            sc[e] = v > 20.f ? v : (float)log1p((double)sw_expf_cr(v));
+        }
+    }
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) r[e] = sc[e];     // keep the scores for inspection
+
+    // K rounds of arg-max over score (+bias), strict >, ties to the lower id.
+    const bool ub = use_bias && corr_bias != nullptr;
+    uint32_t used = 0;                           // bit j: this lane's element lane+32j is taken
+    float wsel = 0.f;                            // lane a keeps weight of rank a
+    for (int a = 0; a < K; a++) {
+        float bv = -1e30f; int best = -1;
+        int j = 0;
+        for (int e = lane; e < E; e += 32, j++) {
+            if (used & (1u << j)) continue;
+            float s = sc[e] + (ub ? corr_bias[e] : 0.f);
+            if (s > bv) { bv = s; best = e; }
+        }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) {
+            float ov = __shfl_xor_sync(SW_FULL_MASK, bv, off);
+            int oi = __shfl_xor_sync(SW_FULL_MASK, best, off);
+            if (oi >= 0 && (best < 0 || ov > bv || (ov == bv && oi < best))) { bv = ov; best = oi; }
+        }
+        if (best < 0) {                          // nothing finite: lowest unselected id
+            int cand = 0x7fffffff; j = 0;
+            for (int e = lane; e < E; e += 32, j++) if (!(used & (1u << j))) { cand = e; break; }
+#pragma unroll
+            for (int off = 16; off; off >>= 1) { int o = __shfl_xor_sync(SW_FULL_MASK, cand, off); if (o < cand) cand = o; }
+            best = cand == 0x7fffffff ? 0 : cand;
+        }
+        if ((best & 31) == lane) used |= 1u << (best >> 5);
+        if (lane == a) wsel = sc[best];
+        if (lane == 0) sel[(size_t)t * K + a] = best;
+    }
+    if (norm_topk) {                             // float sum in rank order, then divide
+        float sm = 0.f;
+        for (int a = 0; a < K; a++) sm += __shfl_sync(SW_FULL_MASK, wsel, a);
+        wsel = wsel / sm;
+    }
+    if (lane < K) w[(size_t)t * K + lane] = wsel;
+}
+
+int sw_launch_route_topk(const SwLaunchCfg &c, float *scores, const float *corr_bias, int use_bias,
+                         int route_act, int norm_topk, int T, int E, int K, int *sel, float *w) {
+    if (T <= 0) return 0;
+    if (E > SW_MAX_EXPERTS || K > SW_MAX_TOPK || K > E || K <= 0) return -1;
+    k_route_topk<<<(T + 3) / 4, 128, 0, c.stream>>>(scores, corr_bias, use_bias, route_act, norm_topk, T, E, K, sel, w);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// ---------------------------------------------------------------------------
+// Dispatch: stable counting sort of the T*K (row, expert) pairs by expert.
+// One CTA.  Each warp owns a contiguous segment of the flat pair index, so a
+// per-warp histogram followed by an exclusive scan over (expert, warp) gives
+// every warp the first slot of its pairs for each expert; walking the segment
+// in order with __match_any ranks keeps pairs of one expert in ascending flat
+// index -- the reference's order.
+// ---------------------------------------------------------------------------
+#define SW_DISPATCH_THREADS 1024
+
+__global__ void __launch_bounds__(SW_DISPATCH_THREADS)
+k_dispatch(const int *__restrict__ sel, int npairs, int K, int E, int T,
+           int *__restrict__ Gout, int *__restrict__ gexp, int *__restrict__ gbeg, int *__restrict__ gcnt,
+           int *__restrict__ grow, int *__restrict__ rowof, int *__restrict__ status) {
+    extern __shared__ int sm[];
+    const int NW = SW_DISPATCH_THREADS / 32;
+    int *wh = sm;                    // [NW][E] per-warp histogram -> per-warp running slot offset
+    int *pos = sm + NW * E;          // [E] first slot of expert e
+    int *cnt = pos + E;              // [E]
+    __shared__ int s_wsum[32], s_gsum[32];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    for (int i = tid; i < NW * E; i += SW_DISPATCH_THREADS) wh[i] = 0;
+    __syncthreads();
+
+    int seg = (npairs + NW - 1) / NW;
+    seg = (seg + 31) & ~31;
+    const int s0 = min(warp * seg, npairs), s1 = min(s0 + seg, npairs);
+    for (int i = s0 + lane; i < s1; i += 32) {
+        int e = sel[i];
+        if (e < 0 || e >= E) { atomicOr(status, SW_ST_BAD_EXPERT); continue; }
+        atomicAdd(&wh[warp * E + e], 1);
+    }
+    __syncthreads();
+
+    // per expert: total and exclusive prefix over warps
+    for (int e = tid; e < E; e += SW_DISPATCH_THREADS) {
+        int run = 0;
+        for (int wv = 0; wv < NW; wv++) { int c = wh[wv * E + e]; wh[wv * E + e] = run; run += c; }
+        cnt[e] = run;
+    }
+    __syncthreads();
+
+    // exclusive scan over experts of cnt (slots) and of cnt>0 (group index); E <= 1024 = blockDim
+    int c = tid < E ? cnt[tid] : 0;
+    int nz = c > 0 ? 1 : 0;
+    int sc = c, sg = nz;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        int a = __shfl_up_sync(SW_FULL_MASK, sc, off), b = __shfl_up_sync(SW_FULL_MASK, sg, off);
+        if (lane >= off) { sc += a; sg += b; }
+    }
+    if (lane == 31) { s_wsum[warp] = sc; s_gsum[warp] = sg; }
+    __syncthreads();
+    if (warp == 0) {
+        int a = s_wsum[lane], b = s_gsum[lane];
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            int ua = __shfl_up_sync(SW_FULL_MASK, a, off), ub = __shfl_up_sync(SW_FULL_MASK, b, off);
+            if (lane >= off) { a += ua; b += ub; }
+        }
+        s_wsum[lane] = a; s_gsum[lane] = b;      // inclusive over warps
+    }
+    __syncthreads();
+    {
+        int wbase = warp ? s_wsum[warp - 1] : 0, gbase = warp ? s_gsum[warp - 1] : 0;
+        int excl = wbase + sc - c, gidx = gbase + sg - nz;
+        if (tid < E) {
+            pos[tid] = excl;
+            if (nz) { gexp[gidx] = tid; gbeg[gidx] = excl; gcnt[gidx] = c; }
+        }
+        if (tid == 0) *Gout = s_gsum[31];
+    }
+    __syncthreads();
+
+    // stable scatter
+    for (int base = s0; base < s1; base += 32) {
+        int i = base + lane;
+        int e = i < s1 ? sel[i] : -1;
+        bool ok = e >= 0 && e < E;
+        unsigned peers = __match_any_sync(SW_FULL_MASK, ok ? e : -1 - lane);
+        int off = ok ? wh[warp * E + e] : 0;
+        __syncwarp();
+        if (ok) {
+            int rank = __popc(peers & ((1u << lane) - 1));
+            int slot = pos[e] + off + rank;
+            int row = i / K;
+            if (row >= T) atomicOr(status, SW_ST_BAD_ROW);
+            else { grow[slot] = row; rowof[i] = slot; }
+            if (rank == 0) wh[warp * E + e] = off + __popc(peers);
+        }
+        __syncwarp();
+    }
+}
+
+int sw_launch_dispatch(const SwLaunchCfg &c, const SwRouting &r, int T, int K, int E) {
+    if (T <= 0) return 0;
+    if (E > SW_DISPATCH_THREADS) return -1;
+    size_t smem = (size_t)(SW_DISPATCH_THREADS / 32 + 2) * E * sizeof(int);
+    static bool attr_done = false;
+    if (!attr_done) {
+        if (cudaFuncSetAttribute(k_dispatch, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess) return -1;
+        attr_done = true;
+    }
+    k_dispatch<<<1, SW_DISPATCH_THREADS, smem, c.stream>>>(r.sel, T * K, K, E, T, r.G, r.gexp, r.gbeg, r.gcnt,
+                                                          r.grow, r.rowof, r.status);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}

@@ -1,0 +1,239 @@
+"""Parity of the CUDA path (through the C-ABI) against the CPU checker and the reference goldens.
+
+Bars: expert ids, weights' order and every dispatch array bit-exact; combine weights
+within 2 ulp-level relative error; outputs within 1e-3 relative L2 of the reference's
+exact f32 path (the tolerance of the task statement; measured values are ~1e-6).
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden, synth_case, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+OUT_TOL = 1e-3       # relative L2 bar for outputs
+W_TOL = 5e-7         # relative bar for combine weights (f32 ulp level)
+
+
+def make_block(case, max_tokens=None):
+    from sabrewing_b200.moe_block import MoeBlock, MoeLayer, desc_from_config
+    cfg = case.cfg
+    blk = MoeBlock("cuda:0", max_tokens or max(case.x.shape[0], 1), cfg.E, cfg.K, cfg.D, cfg.I, cfg.SI)
+    layer = MoeLayer(cfg.D, cfg.I, cfg.SI, case.a, "cuda:0")
+    return blk, layer, desc_from_config(cfg)
+
+
+def check_routing(got, want):
+    assert np.array_equal(got["sel"], want["sel"])
+    assert got["G"] == want["G"]
+    for k in ("gexp", "gbeg", "gcnt", "grow", "rowof"):
+        assert np.array_equal(got[k], want[k]), k
+    werr = np.abs(got["w"] - want["w"]) / np.abs(want["w"])
+    assert werr.max() < W_TOL, werr.max()
+
+
+def run_case(case, orc, ref_out=None):
+    blk, layer, desc = make_block(case)
+    x = torch.from_numpy(case.x).cuda(); out = torch.from_numpy(case.hin).cuda()
+    blk.forward(desc, layer, x, out)
+    torch.cuda.synchronize()
+    assert blk.status() == 0
+    want = orc.moe_group(case.host, case.x, case.hin, exact=1)
+    check_routing(blk.routing(), want)
+    err = rel_l2(out.cpu().numpy() - case.hin, want["out"] - case.hin)
+    assert err < OUT_TOL, err
+    if ref_out is not None:
+        assert rel_l2(out.cpu().numpy() - case.hin, ref_out - case.hin) < OUT_TOL
+    # the host-buffer entry point gives the same bits as the device one
+    oh = case.hin.copy()
+    blk.forward_host(desc, layer, case.x, oh)
+    assert np.array_equal(oh, out.cpu().numpy())
+    blk.close()
+    return err
+
+
+@pytest.mark.parametrize("name", ["laguna_tiny", "olmoe_tiny", "zipf_tiny", "wide_tiny"])
+def test_golden_fixtures(orc, name):
+    case, z = load_golden(name)
+    run_case(case, orc, z["ref_out"])
+
+
+@pytest.mark.parametrize("base,kw,T", [
+    ("c1", dict(D=512, I=256), 32),                      # OLMoE-shaped: softmax, no shared
+    ("c2", dict(D=1024, I=256, SI=256), 1),              # Laguna-shaped decode batch 1
+    ("c2", dict(D=1024, I=256, SI=256), 32),             # ... batch 32
+    ("c2", dict(D=512, I=128, SI=128, route_act=2), 8),  # softplus gate variant
+    ("c3", dict(D=512, I=128, SI=128), 300),             # Zipf-skewed, ragged group sizes
+    ("c4", dict(D=640, I=192), 64),                      # 384 experts, softmax
+    ("c5", dict(D=512, I=128, SI=128), 50),              # 512 experts + shared
+])
+def test_scaled_configs(orc, base, kw, T):
+    case = synth_case(base, corr_bias_std=0.01, T=T, **kw)
+    run_case(case, orc)
+
+
+def test_f32_router_weights(orc):
+    from sabrewing_b200.moe_block import MoeBlock, MoeLayer, desc_from_config
+    case = synth_case("c2", D=256, E=64, K=6, I=64, SI=64, T=19)
+    cfg = case.cfg
+    blk = MoeBlock("cuda:0", 19, cfg.E, cfg.K, cfg.D, cfg.I, cfg.SI)
+    layer = MoeLayer(cfg.D, cfg.I, cfg.SI, case.a, "cuda:0", router="f32")
+    x = torch.from_numpy(case.x).cuda(); out = torch.zeros_like(x)
+    blk.forward(desc_from_config(cfg), layer, x, out)
+    check_routing(blk.routing(), orc.moe_group(case.host, case.x, None, exact=1))
+
+
+def test_ties_and_nonfinite_router(orc):
+    # zero router weights: every score equal -> ties to the lower id; bias decides selection only
+    case = synth_case("c2", D=128, E=32, K=5, I=64, SI=64, T=4)
+    case.a["router_w"][:] = 0; case.a["router_bf16"][:] = 0
+    case.a["corr_bias"][:] = 0; case.a["corr_bias"][[7, 21]] = 0.25
+    run_case(case, orc)
+    blk, layer, desc = make_block(case)
+    x = torch.from_numpy(case.x).cuda(); x[1, 3] = float("nan")      # poisons every logit of row 1
+    blk.route(desc, layer, x)
+    r = blk.routing()
+    assert r["sel"][0].tolist() == [7, 21, 0, 1, 2]
+    assert r["sel"][1].tolist() == [0, 1, 2, 3, 4]                   # degraded selection, c/moe_arch.h:75-86
+    assert blk.status() == 0
+
+
+def test_empty_and_oversized_batches():
+    from sabrewing_b200 import capi
+    case = synth_case("c1", D=128, E=8, K=2, I=64, T=3)
+    blk, layer, desc = make_block(case, max_tokens=4)
+    x = torch.zeros((0, 128), device="cuda"); out = torch.zeros((0, 128), device="cuda")
+    blk.forward(desc, layer, x, out)                                 # T=0 is a no-op
+    x5 = torch.zeros((5, 128), device="cuda")
+    with pytest.raises(RuntimeError, match="outside"):
+        blk.forward(desc, layer, x5, torch.zeros_like(x5))
+    d = desc.c(); d.shared_mode = 2; l = layer.c()
+    x3 = torch.zeros((3, 128), device="cuda")
+    assert blk.lib.sw_moe_forward(blk.ctx, C.byref(d), C.byref(l), x3.data_ptr(), x3.data_ptr(), 3, None) == -1
+    assert "not wired" in capi.last_error()
+
+
+def test_expert_parallel_shards_sum_to_the_whole(orc):
+    """Each shard computes only pairs of its resident experts; the shard sums add up to the routed sum."""
+    from sabrewing_b200.moe_block import MoeBlock, MoeLayer, desc_from_config
+    case = synth_case("c4", D=256, E=48, K=8, I=96, T=40)
+    cfg = case.cfg; desc = desc_from_config(cfg)
+    x = torch.from_numpy(case.x).cuda()
+    want = orc.moe_group(case.host, case.x, None, exact=1)
+    for shards in (1, 2, 4, 8):
+        total = torch.zeros_like(x)
+        per = cfg.E // shards
+        for r in range(shards):
+            blk = MoeBlock("cuda:0", 40, cfg.E, cfg.K, cfg.D, cfg.I, cfg.SI)
+            layer = MoeLayer(cfg.D, cfg.I, cfg.SI, case.a, "cuda:0", expert_lo=r * per, expert_cnt=per)
+            blk.route(desc, layer, x)
+            part = torch.empty_like(x)
+            blk.experts(desc, layer, x, part)
+            total += part
+            check_routing(blk.routing(), want)
+            blk.close()
+        assert rel_l2(total.cpu().numpy(), want["routed"]) < OUT_TOL
+
+
+# ---- lag_cuda_* drop-in tier: the reference's own GPU self-test bars (c/laguna.c:1565-1662) ----
+def _lag():
+    from sabrewing_b200 import capi
+    l = capi.lib()
+    assert l.lag_cuda_init(0) == 0
+    return l
+
+
+def _up(l, a):
+    p = l.lag_cuda_upload(a.ctypes.data, a.nbytes)
+    assert p
+    return p
+
+
+def test_lag_known_answer_nibbles():
+    l = _lag()
+    # c/tests/test_backend_cuda.cu:42,105-110, zero-padded to one 32-column unit (nibble 8 = value 0)
+    x = np.zeros((1, 32), np.float32); x[0, :4] = [1, -2, 3, -4]
+    q = np.full((2, 16), 0x88, np.uint8); q[0, :2] = [0x70, 0xf8]; q[1, :2] = [0xa9, 0xcb]
+    s = np.array([1.0, 0.25], np.float32)
+    y = np.empty((1, 2), np.float32)
+    dq, ds = _up(l, q), _up(l, s)
+    assert l.lag_cuda_matmul_q4(y.ctypes.data, x.ctypes.data, dq, ds, 1, 32, 2) == 0
+    assert y.tolist() == [[-34.0, -2.5]]
+    l.lag_cuda_free(dq); l.lag_cuda_free(ds)
+
+
+def test_lag_matmuls_match_cpu(orc):
+    l = _lag()
+    rng = np.random.default_rng(1234)
+    I, O = 3072, 2048
+    x = (rng.random((3, I), dtype=np.float32) * 2 - 1)
+    p = rng.integers(0, 256, (O, I // 2), dtype=np.uint8)
+    sc = (0.01 + rng.random(O, dtype=np.float32) * 0.05).astype(np.float32)
+    y = np.empty((3, O), np.float32)
+    dp, ds = _up(l, p), _up(l, sc)
+    assert l.lag_cuda_matmul_q4(y.ctypes.data, x.ctypes.data, dp, ds, 3, I, O) == 0
+    yc = orc.matmul_q4(x, p, sc, 1)
+    assert (np.abs(y - yc) / (np.abs(yc) + 1e-6)).max() < 1e-3          # the reference's q4 bar
+    l.lag_cuda_free(dp); l.lag_cuda_free(ds)
+    # bf16 residents
+    from sabrewing_b200 import synth
+    Wb = synth.f32_to_bf16(rng.random((O, I), dtype=np.float32) * 2 - 1)
+    dW = _up(l, Wb)
+    assert l.lag_cuda_matmul_bf16(y.ctypes.data, x.ctypes.data, dW, 3, I, O) == 0
+    yc = orc.matmul_bf16(x, Wb, 1)
+    assert (np.abs(y - yc) / (np.abs(yc) + 1e-6)).max() < 5e-3          # the reference's bf16 bar
+    l.lag_cuda_free(dW)
+    # int8 residents: [int8 O*I][f32 scale O]
+    q8 = rng.integers(-127, 128, (O, I), dtype=np.int8)
+    blob = np.concatenate([q8.reshape(-1).view(np.uint8), sc.view(np.uint8)])
+    dW = _up(l, blob)
+    assert l.lag_cuda_matmul_q8(y.ctypes.data, x.ctypes.data, dW, 3, I, O) == 0
+    yc = (x.astype(np.float64) @ q8.astype(np.float64).T) * sc
+    assert rel_l2(y, yc) < 1e-5
+    l.lag_cuda_free(dW)
+
+
+def test_lag_grouped_is_bit_identical_to_per_token(orc):
+    """moe_group vs moe_experts on overlapping selections: max|diff| must be exactly 0."""
+    l = _lag()
+    rng = np.random.default_rng(7)
+    D, I, E, S, K = 3072, 1024, 6, 4, 3
+    sel = np.array([[0, 1, 2], [1, 2, 3], [0, 2, 4], [2, 3, 5]], np.int32)
+    x = (rng.random((S, D), dtype=np.float32) * 2 - 1)
+    w = (0.05 + rng.random((S, K), dtype=np.float32) * 0.3).astype(np.float32)
+    p13 = rng.integers(0, 256, (E * 2 * I, D // 2), dtype=np.uint8)
+    p2 = rng.integers(0, 256, (E * D, I // 2), dtype=np.uint8)
+    s13 = (0.01 + rng.random(E * 2 * I, dtype=np.float32) * 0.03).astype(np.float32)
+    s2 = (0.01 + rng.random(E * D, dtype=np.float32) * 0.03).astype(np.float32)
+    d13, ds13, d2, ds2 = _up(l, p13), _up(l, s13), _up(l, p2), _up(l, s2)
+    yref = np.empty((S, D), np.float32); ygrp = np.empty((S, D), np.float32)
+    for s in range(S):
+        assert l.lag_cuda_moe_experts(yref[s].ctypes.data, x[s].ctypes.data, d13, ds13, d2, ds2,
+                                      sel[s].ctypes.data, w[s].ctypes.data, K, I, D) == 0
+    g = orc.group(sel, E)
+    assert l.lag_cuda_moe_group(ygrp.ctypes.data, x.ctypes.data, d13, ds13, d2, ds2,
+                                g["gexp"].ctypes.data, g["gbeg"].ctypes.data, g["gcnt"].ctypes.data, g["G"],
+                                g["grow"].ctypes.data, g["rowof"].ctypes.data, w.ctypes.data, S, K, I, D) == 0
+    assert np.abs(yref - ygrp).max() == 0.0
+    # and both agree with the CPU path
+    import oracle
+    L = oracle.HostLayer(D, I, 0, E, K, 0, 0, 0, 1.0, 0, 0, gu_q=p13, gu_s=s13, dn_q=p2, dn_s=s2)
+    want = orc.experts_given_routing(L, x, sel, w, exact=1)
+    assert rel_l2(ygrp, want) < OUT_TOL
+    # fused single expert: max|abs| < 1e-3 (the reference's bar for the chained q4->silu->q4)
+    y1 = np.empty(D, np.float32)
+    assert l.lag_cuda_expert_q4(y1.ctypes.data, x[0].ctypes.data, d13, ds13, d2, ds2, I, D) == 0
+    w1 = orc.experts_given_routing(oracle.HostLayer(D, I, 0, E, 1, 0, 0, 0, 1.0, 0, 0, gu_q=p13, gu_s=s13, dn_q=p2, dn_s=s2),
+                                   x[:1], np.zeros((1, 1), np.int32), np.ones((1, 1), np.float32), exact=1)
+    assert np.abs(y1 - w1[0]).max() < 1e-3
+    for d in (d13, ds13, d2, ds2):
+        l.lag_cuda_free(d)
+
+
+def test_lag_rejects_odd_shapes():
+    l = _lag()
+    y = np.zeros(8, np.float32)
+    assert l.lag_cuda_matmul_q4(y.ctypes.data, y.ctypes.data, None, None, 1, 6, 2) == -1   # caller falls back to CPU
