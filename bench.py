@@ -1,0 +1,355 @@
+"""MoE-block benchmark: tokens/s of one Laguna-shaped MoE layer call at a decode batch.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                    [--workload c1|c2|c3|c4|c5] [--batch T] [--layers L]
+
+A step is one pass of the MoE block (route -> top-k -> group-by-expert -> int4
+gate/up -> SiLU*up -> int4 down -> combine + shared expert) over one batch of T
+synthetic token rows.  Steps cycle over L resident layers and 8 token batches so no
+step finds its weights in L2.  N > 1 shards the experts over the ranks (one process
+per GPU) with T rows per rank (weak scaling).  Prints one JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "moe_block_tokens_per_s"
+UNIT = "tokens/s"
+LAYER_KEYS = ("router_w", "corr_bias", "logit_bias", "gu_q", "gu_s", "dn_q", "dn_s", "sh_gate", "sh_up", "sh_down")
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--batch", type=int, default=0, help="token rows per rank and step (0 = the config's)")
+    ap.add_argument("--layers", type=int, default=4, help="resident layers the steps cycle over")
+    ap.add_argument("--cpu-reps", type=int, default=12)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def workload_name(cfg, T, world):
+    return "%s: D=%d E=%d top%d I=%d shared_I=%d, decode batch %d%s" % (
+        cfg.name, cfg.D, cfg.E, cfg.K, cfg.I, cfg.SI, T, " per rank, experts sharded over %d ranks" % world if world > 1 else "")
+
+
+# ---------------------------------------------------------------------------
+class ClockSampler(threading.Thread):
+    """Samples SM clock and clock-event reasons of one GPU through NVML while the bench runs."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x10: "sync_boost"}
+
+    def __init__(self, index, period=0.02):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.marks, self.stop_flag = [], {}, False
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.max_mhz = None
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    rs = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    rs = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((time.perf_counter(), mhz, rs))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def mark(self, name):
+        self.marks[name] = time.perf_counter()
+
+    def summary(self, t0, t1):
+        inside = [s for s in self.samples if t0 <= s[0] <= t1] or self.samples[-3:]
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        bits = 0
+        for s in inside:
+            bits |= s[2]
+        return {"sm_mhz": statistics.median(s[1] for s in inside), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(v for k, v in self.REASONS.items() if bits & k), "samples": len(inside)}
+
+
+def host_layer_from(cfg, arrays):
+    import numpy as np
+    import oracle
+    a = {}
+    for k in LAYER_KEYS:
+        v = arrays.get(k)
+        if v is None:
+            a[k] = None
+        else:
+            v = v.cpu().numpy() if hasattr(v, "cpu") else v
+            a[k] = v.view(np.uint16) if v.dtype == np.int16 else v
+    return oracle.HostLayer(cfg.D, cfg.I, cfg.SI, cfg.E, cfg.K, cfg.route_act, cfg.use_corr_bias, cfg.norm_topk,
+                            cfg.route_scale, cfg.shared_mode, cfg.gs, **a)
+
+
+def cpu_step_fn(cfg, host):
+    """The reference's CPU implementation of one block call (its timed default: AVX-512 f32), or the port."""
+    import oracle
+    ref = oracle.load_ref()
+    laguna_ok = cfg.route_act == 0 and cfg.shared_mode == 1 and cfg.gs == 0 and host.a.get("logit_bias") is None
+    if ref is not None:
+        ref.omp_autotune()                    # one thread per physical core, c/moe_util.h:78-87
+        if laguna_ok:
+            return "reference", ref.threads(), (lambda x, h: ref.laguna_moe_rows(host, x, h, exact=0, group_on=1))
+        return "reference", ref.threads(), (lambda x, h: ref.moe_block_rows(host, x, h, exact=0))
+    orc = oracle.load()
+    return "port", orc.threads(), (lambda x, h: orc.moe_group(host, x, h, exact=0)["out"])
+
+
+def time_cpu(fn, x, reps, budget_s=30.0):
+    import numpy as np
+    h = np.zeros_like(x)
+    fn(x, h)                                  # warm-up
+    best, done, t_start = None, 0, time.perf_counter()
+    while done < reps and (time.perf_counter() - t_start) < budget_s:
+        t0 = time.perf_counter(); fn(x, h); dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+        done += 1
+    return best, done
+
+
+# ---------------------------------------------------------------------------
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    import torch
+    from sabrewing_b200 import synth
+    cfg = synth.CONFIGS[args.workload]
+    T = args.batch or cfg.T
+    arrays = synth.make_layer_device(cfg, "cpu", 0)
+    host = host_layer_from(cfg, arrays)
+    kind, cores, fn = cpu_step_fn(cfg, host)
+    xs = [synth.make_tokens(cfg, T, seed_offset=1000 + i) for i in range(4)]
+    h = np.zeros_like(xs[0])
+    for i in range(args.warmup):
+        fn(xs[i % 4], h)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        fn(xs[i % 4], h)
+    dt = time.perf_counter() - t0
+    val = T * args.steps / dt
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 activations x int4 weights (AVX-512 f32 accumulate)" if kind == "reference" else "f32",
+            "data": "synthetic", "config": {"workload": workload_name(cfg, T, 1)},
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": kind,
+                             "sample": "every step = one full block call of the workload (T=%d rows, one layer)" % T},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from sabrewing_b200 import synth, capi
+    from sabrewing_b200.moe_block import MoeBlock, MoeLayer, desc_from_config
+    from sabrewing_b200.ep import ExpertParallelMoe, shard_range
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    capi.lib()
+
+    cfg = synth.CONFIGS[args.workload]
+    T = args.batch or cfg.T
+    desc = desc_from_config(cfg)
+    lo, cnt = shard_range(cfg.E, world, rank)
+    NB = 8
+
+    sampler = ClockSampler(local)
+    sampler.start()
+
+    layers, host0 = [], None
+    for li in range(args.layers):
+        arrays = synth.make_layer_device(cfg, dev, li)
+        if li == 0 and rank == 0 and world == 1 and not args.no_cpu_baseline:
+            host0 = host_layer_from(cfg, arrays)
+        layers.append(MoeLayer(cfg.D, cfg.I, cfg.SI, arrays, dev, expert_lo=lo if world > 1 else 0,
+                               expert_cnt=cnt if world > 1 else 0))
+        del arrays
+    torch.cuda.empty_cache()
+    xs_host = [torch.from_numpy(synth.make_tokens(cfg, T, seed_offset=1000 + 97 * rank + i)).pin_memory() for i in range(NB)]
+    xs = [x.to(dev) for x in xs_host]
+    outs = [torch.zeros_like(x) for x in xs]
+    block = MoeBlock(dev, T * world, cfg.E, cfg.K, cfg.D, cfg.I, cfg.SI)
+    ep = ExpertParallelMoe(block, desc) if world > 1 else None
+
+    def step(i):
+        layer, x, out = layers[i % len(layers)], xs[i % NB], outs[i % NB]
+        if ep is None:
+            block.forward(desc, layer, x, out)
+        else:
+            ep.forward(layer, x, out)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    l0 = block.lib.sw_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_a = time.perf_counter()
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    t_b = time.perf_counter()
+    launches = block.lib.sw_launch_count() - l0
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.summary(t_a, t_b)
+    value = T * world * args.steps / (ms * 1e-3)
+
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 activations x int4 weights (f32 accumulate)", "data": "synthetic",
+            "config": {"workload": workload_name(cfg, T, world), "global_batch": T * world, "layers_cycled": len(layers),
+                       "l2": "inputs larger than L2: steps cycle over %d layers (%.2f GB of expert blobs each per GPU) and %d token batches"
+                             % (len(layers), layers[0].expert_bytes() / 1e9, NB),
+                       "parallelism": "ep%d" % world if world > 1 else "single"},
+            "clocks": clocks, "gpu_launches": int(launches)}
+
+    # ---- roofline of the dominant kernel: per-stage CUDA events over the same steps (1 GPU) ----
+    if world == 1:
+        block.profile(True)
+        for i in range(min(args.steps, 500)):
+            step(i)
+        torch.cuda.synchronize()
+        stage_ms, calls = block.profile_read()
+        block.profile(False)
+        Gs = []
+        for i in range(min(NB * len(layers), 16)):
+            block.route(desc, layers[i % len(layers)], xs[i % NB]); Gs.append(block.routing()["G"])
+        G = float(np.mean(Gs))
+        per = {k: v / max(calls, 1) for k, v in stage_ms.items()}
+        dom = max(per, key=per.get)
+        P, D, I, SI, E = T * cfg.K, cfg.D, cfg.I, cfg.SI, cfg.E
+        alg = {"q4_gateup": G * (I * D + 8 * I) + T * D * 4 + P * I * 4,
+               "q4_down": G * (I * D // 2 + 4 * D) + P * I * 4 + P * D * 4,
+               "shared_gateup": 2 * SI * D * 2 + T * D * 4 + T * SI * 4,
+               "shared_down": SI * D * 2 + T * SI * 4 + T * D * 4,
+               "router_logits": E * D * 2 + T * D * 4 + T * E * 4,
+               "combine": P * D * 4 + 2 * T * D * 4, "route_topk": 2 * T * E * 4, "dispatch": 3 * P * 4}
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        ach = alg[dom] / (per[dom] * 1e-3) / 1e9
+        block_bytes = G * (1.5 * I * D + 8 * I + 4 * D) + (3 * SI * D * 2 if SI else 0) + E * D * 2 + 2 * T * D * 4
+        line["roofline"] = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                            "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
+                            "traffic": None, "algorithmic_bytes_per_launch": alg[dom], "kernel_ms": per[dom],
+                            "distinct_experts_per_step": G}
+        exp_ms = per["q4_gateup"] + per["q4_down"]
+        line["int4_expert_gbs"] = G * (1.5 * I * D + 8 * I + 4 * D) / (exp_ms * 1e-3) / 1e9
+        line["block_hbm_frac"] = block_bytes / (line["ms_per_step"] * 1e-3) / 1e9 / peak
+        line["stage_ms"] = {k: round(v, 5) for k, v in per.items()}
+
+    # ---- end to end through host buffers: pinned x -> H2D, block, D2H of the result, every step ----
+    if world == 1:
+        hx = [x.numpy() for x in xs_host]
+        ho = [np.zeros_like(h) for h in hx]
+        n_e2e = max(3, min(args.steps, 200))
+        for i in range(3):
+            block.forward_host(desc, layers[i % len(layers)], hx[i % NB], ho[i % NB])
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(n_e2e):
+            block.forward_host(desc, layers[i % len(layers)], hx[i % NB], ho[i % NB])
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        nbytes = T * cfg.D * 4
+        line["e2e"] = {"value": T * n_e2e / dt, "unit": UNIT, "h2d_bytes_per_step": 2 * nbytes, "d2h_bytes_per_step": nbytes,
+                       "steps": n_e2e, "api": "sw_moe_forward_host (host f32 rows in, host f32 rows out, one sync per call)"}
+    else:
+        # expert-parallel: every rank copies its rows in from pinned memory and its result back out each step
+        n_e2e = max(3, min(args.steps, 200))
+        hout = [torch.zeros_like(h).pin_memory() for h in xs_host]
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(n_e2e):
+            xs[i % NB].copy_(xs_host[i % NB], non_blocking=True)
+            step(i)
+            hout[i % NB].copy_(outs[i % NB], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        barrier()
+        dt = time.perf_counter() - t0
+        t = torch.tensor([dt], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX); dt = float(t.item())
+        nbytes = T * cfg.D * 4
+        line["e2e"] = {"value": T * world * n_e2e / dt, "unit": UNIT, "h2d_bytes_per_step": nbytes * world,
+                       "d2h_bytes_per_step": nbytes * world, "steps": n_e2e,
+                       "api": "ExpertParallelMoe.forward with per-step pinned H2D of x and D2H of out on every rank"}
+
+    # ---- CPU baseline on the host cores (rank 0, N=1): the reference's own CPU code on the same layer ----
+    if host0 is not None:
+        kind, cores, fn = cpu_step_fn(cfg, host0)
+        xh = xs_host[0].numpy()
+        best, done = time_cpu(fn, xh, args.cpu_reps)
+        line["cpu_baseline"] = {"value": T / best, "unit": UNIT, "cores": cores, "kind": kind,
+                                "sample": "min of %d full block calls of the same workload (T=%d rows, layer 0) after one warm-up" % (done, T)}
+        want = fn(xh, np.zeros_like(xh))
+        got = torch.zeros_like(xs[0]); block.forward(desc, layers[0], xs[0], got); torch.cuda.synchronize()
+        g = got.cpu().numpy()
+        line["parity_rel_l2_vs_cpu"] = float(np.sqrt(((g - want) ** 2).sum() / (want ** 2).sum()))
+
+    sampler.stop_flag = True
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

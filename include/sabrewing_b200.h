@@ -119,8 +119,8 @@ int  sw_moe_ctx_create(SwMoeCtx **ctx, int dev, int max_tokens, int max_experts,
                        int max_D, int max_I, int max_SI);
 void sw_moe_ctx_destroy(SwMoeCtx *ctx);
 
-/* out[T,D] += MoE(x[T,D]); x, out device f32; stream is a cudaStream_t (NULL =
- * the context's own stream).  Asynchronous on that stream.  Residual semantics
+/* out[T,D] += MoE(x[T,D]); x, out device f32; stream is a cudaStream_t passed
+ * through as given (NULL = CUDA's default stream).  Asynchronous on that stream.  Residual semantics
  * follow c/moe_block.h:51 / c/laguna.c:781. */
 int  sw_moe_forward(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer,
                     const float *x, float *out, int T, void *stream);
@@ -150,6 +150,14 @@ int  sw_moe_get_routing(SwMoeCtx *ctx, int *sel, float *w, float *scores, int *G
 /* Device-side status word of the last launches (0 = clean); bit 0: an expert id
  * outside [0,E) reached the dispatch, bit 1: a row index outside [0,T). */
 int  sw_moe_status(SwMoeCtx *ctx);
+/* Per-stage device timing with CUDA events recorded on the call's stream between
+ * the kernels of sw_moe_forward (what the reference's COLI_CUDA_PROFILE split does,
+ * c/backend_cuda.cu:822-929).  enable=1 starts a fresh accumulation (up to 512
+ * calls), read returns total ms per stage and the number of calls recorded. */
+int  sw_moe_profile(SwMoeCtx *ctx, int enable);
+int  sw_moe_profile_read(SwMoeCtx *ctx, float *ms_per_stage, int *calls);
+int  sw_moe_stage_count(void);
+const char *sw_moe_stage_name(int i);
 /* Number of kernels launched by this library since load. */
 long long sw_launch_count(void);
 /* Text of the last error on the calling thread's most recent failing call. */

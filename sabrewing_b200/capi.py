@@ -53,6 +53,10 @@ SIGNATURES = {
     "sw_moe_finish": (_i, [_vp, _pd, _pl, _vp, _vp, _vp, _i, _vp]),
     "sw_moe_get_routing": (_i, [_vp, _vp, _vp, _vp, C.POINTER(_i), _vp, _vp, _vp, _vp, _vp]),
     "sw_moe_status": (_i, [_vp]),
+    "sw_moe_profile": (_i, [_vp, _i]),
+    "sw_moe_profile_read": (_i, [_vp, C.POINTER(C.c_float), C.POINTER(_i)]),
+    "sw_moe_stage_count": (_i, []),
+    "sw_moe_stage_name": (C.c_char_p, [_i]),
     "sw_launch_count": (C.c_longlong, []),
     "sw_last_error": (C.c_char_p, []),
 }

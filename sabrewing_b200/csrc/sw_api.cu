@@ -56,7 +56,21 @@ struct SwMoeCtx {
     float *dx = nullptr, *dout = nullptr, *hx = nullptr, *hout = nullptr;
     int lastT = 0, lastK = 0, lastE = 0;
     void *block = nullptr;      // one device allocation holding all device scratch
+    // optional per-stage CUDA-event timing (sw_moe_profile)
+    int prof_on = 0, prof_calls = 0;
+    cudaEvent_t *prof_ev = nullptr;   // [SW_PROF_MAX_CALLS][SW_NSTAGES+1]
 };
+
+enum { SW_ST_LOGITS = 0, SW_ST_TOPK, SW_ST_DISPATCH, SW_ST_GATEUP, SW_ST_DOWN, SW_ST_SH_GATEUP, SW_ST_SH_DOWN, SW_ST_COMBINE, SW_NSTAGES };
+#define SW_PROF_MAX_CALLS 512
+static const char *const sw_stage_names[SW_NSTAGES] = {
+    "router_logits", "route_topk", "dispatch", "q4_gateup", "q4_down", "shared_gateup", "shared_down", "combine"};
+
+// record the event that closes stage `stage` (stage -1 = start of the call)
+static inline void sw_prof_mark(SwMoeCtx *c, int stage, cudaStream_t st) {
+    if (!c->prof_on || c->prof_calls >= SW_PROF_MAX_CALLS) return;
+    cudaEventRecord(c->prof_ev[(size_t)c->prof_calls * (SW_NSTAGES + 1) + stage + 1], st);
+}
 
 static size_t sw_align(size_t n) { return (n + 255) & ~(size_t)255; }
 
@@ -120,6 +134,10 @@ extern "C" void sw_moe_ctx_destroy(SwMoeCtx *c) {
     if (c->block) cudaFree(c->block);
     if (c->hx) cudaFreeHost(c->hx);
     if (c->hout) cudaFreeHost(c->hout);
+    if (c->prof_ev) {
+        for (size_t i = 0; i < (size_t)SW_PROF_MAX_CALLS * (SW_NSTAGES + 1); i++) cudaEventDestroy(c->prof_ev[i]);
+        free(c->prof_ev);
+    }
     delete c;
 }
 
@@ -182,7 +200,7 @@ static int sw_shared_stage(SwMoeCtx *c, const SwMoeLayer *L, const float *x, int
 extern "C" int sw_moe_route(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, int T, void *stream) {
     if (sw_check(c, d, L, T)) return -1;
     if (T == 0) return 0;
-    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    cudaStream_t st = (cudaStream_t)stream;
     return sw_route_impl(c, d, L, x, T, st);
 }
 
@@ -190,7 +208,7 @@ extern "C" int sw_moe_experts(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
     if (sw_check(c, d, L, T)) return -1;
     if (T == 0) return 0;
     if (c->lastT != T || c->lastK != d->topk || c->lastE != d->n_experts) return sw_fail("experts: no matching sw_moe_route before this call");
-    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    cudaStream_t st = (cudaStream_t)stream;
     if (sw_expert_stage(c, d, L, x, T, st)) return -1;
     SwLaunchCfg cfg{c->num_sms, st};
     int lo, cnt; sw_resident(d, L, &lo, &cnt);
@@ -201,7 +219,7 @@ extern "C" int sw_moe_experts(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
 extern "C" int sw_moe_finish(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, const float *routed, float *out, int T, void *stream) {
     if (sw_check(c, d, L, T)) return -1;
     if (T == 0) return 0;
-    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    cudaStream_t st = (cudaStream_t)stream;
     SwLaunchCfg cfg{c->num_sms, st};
     const int has_shared = d->shared_mode != SW_SHARED_NONE;
     if (has_shared && sw_shared_stage(c, L, x, T, st)) return -1;
@@ -212,15 +230,39 @@ extern "C" int sw_moe_finish(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *
 extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, float *out, int T, void *stream) {
     if (sw_check(c, d, L, T)) return -1;
     if (T == 0) return 0;
-    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
-    if (sw_route_impl(c, d, L, x, T, st)) return -1;
-    if (sw_expert_stage(c, d, L, x, T, st)) return -1;
-    const int has_shared = d->shared_mode != SW_SHARED_NONE;
-    if (has_shared && sw_shared_stage(c, L, x, T, st)) return -1;
+    cudaStream_t st = (cudaStream_t)stream;
     SwLaunchCfg cfg{c->num_sms, st};
+    const int E = d->n_experts, K = d->topk;
     int lo, cnt; sw_resident(d, L, &lo, &cnt);
-    if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, c->so, out, T, d->topk, L->D,
+    const int has_shared = d->shared_mode != SW_SHARED_NONE;
+
+    sw_prof_mark(c, -1, st);
+    if (sw_launch_router_logits(cfg, x, L->router_w, L->router_dtype, L->logit_bias, c->r.scores, T, L->D, E)) return sw_fail("router_logits launch failed");
+    sw_prof_mark(c, SW_ST_LOGITS, st);
+    if (sw_launch_route_topk(cfg, c->r.scores, L->corr_bias, d->use_corr_bias, d->route_act, d->norm_topk, T, E, K, c->r.sel, c->r.w)) return sw_fail("route_topk launch failed");
+    sw_prof_mark(c, SW_ST_TOPK, st);
+    if (sw_launch_dispatch(cfg, c->r, T, K, E)) return sw_fail("dispatch launch failed");
+    sw_prof_mark(c, SW_ST_DISPATCH, st);
+    c->last_stream = st; c->lastT = T; c->lastK = K; c->lastE = E;
+
+    SwQ4Args a{};
+    a.gexp = c->r.gexp; a.gbeg = c->r.gbeg; a.gcnt = c->r.gcnt; a.G = c->r.G; a.grow = c->r.grow;
+    a.expert_lo = lo; a.expert_cnt = cnt;
+    a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K;
+    a.q = (const uint8_t *)L->gu_q; a.s = L->gu_s; a.X = x; a.Y = c->glu; a.KD = L->D; a.OUT = L->I;
+    if (sw_launch_q4_gateup(cfg, a)) return sw_fail("gate/up launch failed");
+    sw_prof_mark(c, SW_ST_GATEUP, st);
+    a.q = (const uint8_t *)L->dn_q; a.s = L->dn_s; a.X = c->glu; a.Y = c->slots; a.KD = L->I; a.OUT = L->D;
+    if (sw_launch_q4_down(cfg, a)) return sw_fail("down launch failed");
+    sw_prof_mark(c, SW_ST_DOWN, st);
+    if (has_shared && sw_launch_bf16_gateup(cfg, x, L->sh_gate, L->sh_up, c->sglu, T, L->D, L->SI)) return sw_fail("shared gate/up launch failed");
+    sw_prof_mark(c, SW_ST_SH_GATEUP, st);
+    if (has_shared && sw_launch_bf16_rows(cfg, c->sglu, L->sh_down, c->so, T, L->SI, L->D)) return sw_fail("shared down launch failed");
+    sw_prof_mark(c, SW_ST_SH_DOWN, st);
+    if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, c->so, out, T, K, L->D,
                           d->route_scale, 1 | (has_shared ? 2 : 0) | 4, lo, cnt)) return sw_fail("combine launch failed");
+    sw_prof_mark(c, SW_ST_COMBINE, st);
+    if (c->prof_on && c->prof_calls < SW_PROF_MAX_CALLS) c->prof_calls++;
     return 0;
 }
 
@@ -264,6 +306,35 @@ extern "C" int sw_moe_status(SwMoeCtx *c) {
     if (cudaMemcpy(&s, c->r.status, 4, cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return -1; }
     return s;
 }
+
+extern "C" int sw_moe_profile(SwMoeCtx *c, int enable) {
+    if (!c) return sw_fail("null ctx");
+    if (enable && !c->prof_ev) {
+        size_t n = (size_t)SW_PROF_MAX_CALLS * (SW_NSTAGES + 1);
+        c->prof_ev = (cudaEvent_t *)malloc(n * sizeof(cudaEvent_t));
+        if (!c->prof_ev) return sw_fail("profile: out of host memory");
+        for (size_t i = 0; i < n; i++) SW_CUDA(cudaEventCreate(&c->prof_ev[i]));
+    }
+    c->prof_on = enable ? 1 : 0; c->prof_calls = 0;
+    return 0;
+}
+extern "C" int sw_moe_profile_read(SwMoeCtx *c, float *ms, int *calls) {
+    if (!c || !ms) return sw_fail("null argument");
+    for (int s = 0; s < SW_NSTAGES; s++) ms[s] = 0.f;
+    if (calls) *calls = c->prof_calls;
+    if (!c->prof_ev || c->prof_calls == 0) return 0;
+    SW_CUDA(cudaStreamSynchronize(c->last_stream));
+    for (int i = 0; i < c->prof_calls; i++)
+        for (int s = 0; s < SW_NSTAGES; s++) {
+            float t = 0.f;
+            cudaEvent_t *e = c->prof_ev + (size_t)i * (SW_NSTAGES + 1);
+            SW_CUDA(cudaEventElapsedTime(&t, e[s], e[s + 1]));
+            ms[s] += t;
+        }
+    return 0;
+}
+extern "C" int sw_moe_stage_count(void) { return SW_NSTAGES; }
+extern "C" const char *sw_moe_stage_name(int i) { return i >= 0 && i < SW_NSTAGES ? sw_stage_names[i] : ""; }
 
 // ===========================================================================
 // lag_cuda_* drop-in tier: host pointers in, host pointers out, one sync per call.

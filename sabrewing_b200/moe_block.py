@@ -179,5 +179,16 @@ class MoeBlock:
             r["scores"] = sc
         return r
 
+    def profile(self, enable=True):
+        """Start (or stop) per-stage CUDA-event timing of forward(); see profile_read()."""
+        self._chk(self.lib.sw_moe_profile(self.ctx, 1 if enable else 0), "sw_moe_profile")
+
+    def profile_read(self):
+        """{stage name: total ms}, calls recorded since profile(True)."""
+        n = self.lib.sw_moe_stage_count()
+        ms = (C.c_float * n)(); calls = C.c_int(0)
+        self._chk(self.lib.sw_moe_profile_read(self.ctx, ms, C.byref(calls)), "sw_moe_profile_read")
+        return {self.lib.sw_moe_stage_name(i).decode(): float(ms[i]) for i in range(n)}, calls.value
+
     def status(self):
         return self.lib.sw_moe_status(self.ctx)
