@@ -54,6 +54,8 @@ struct SwMoeCtx {
     SwRouting r{};
     float *glu = nullptr, *slots = nullptr, *sglu = nullptr, *so = nullptr, *routed = nullptr;
     float *dx = nullptr, *dout = nullptr, *hx = nullptr, *hout = nullptr;
+    void *xp = nullptr;          // packed fp16 hi/lo copy of x for the tensor-core path
+    float *sums = nullptr;       // row sums of x and partial row sums of the SiLU*up rows
     int lastT = 0, lastK = 0, lastE = 0;
     void *block = nullptr;      // one device allocation holding all device scratch
     // optional per-stage CUDA-event timing (sw_moe_profile)
@@ -103,7 +105,9 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
         T * (SI ? SI : 1) * 4,// sglu
         T * D * 4,            // so
         T * D * 4,            // routed
-        T * D * 4, T * D * 4  // dx, dout
+        T * D * 4, T * D * 4, // dx, dout
+        T * D * 4,            // xp
+        (T + 64) * 4 + P * (I / 8 + 1) * 4   // sums
     };
     size_t total = 0; for (size_t s : sizes) total += sw_align(s);
     if (cudaMalloc(&c->block, total) != cudaSuccess) {
@@ -116,7 +120,7 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
     c->r.gexp = (int *)take(); c->r.gbeg = (int *)take(); c->r.gcnt = (int *)take();
     c->r.grow = (int *)take(); c->r.rowof = (int *)take(); c->r.status = (int *)take();
     c->glu = (float *)take(); c->slots = (float *)take(); c->sglu = (float *)take(); c->so = (float *)take();
-    c->routed = (float *)take(); c->dx = (float *)take(); c->dout = (float *)take();
+    c->routed = (float *)take(); c->dx = (float *)take(); c->dout = (float *)take(); c->xp = take(); c->sums = (float *)take();
     cudaMemsetAsync(c->r.G, 0, 256, c->stream); cudaMemsetAsync(c->r.status, 0, 256, c->stream);
     if (cudaMallocHost((void **)&c->hx, T * D * 4) != cudaSuccess || cudaMallocHost((void **)&c->hout, T * D * 4) != cudaSuccess) {
         cudaGetLastError(); sw_moe_ctx_destroy(c);
@@ -165,6 +169,44 @@ static void sw_resident(const SwMoeDesc *d, const SwMoeLayer *L, int *lo, int *c
     else { *lo = 0; *cnt = d->n_experts; }
 }
 
+// The tensor-core kernels need 128-column steps; other shapes (and SW_FORCE_SIMT=1)
+// take the CUDA-core f32 kernels.
+static bool sw_use_mma(int D, int I) {
+    static int force_simt = -1;
+    if (force_simt < 0) { const char *e = getenv("SW_FORCE_SIMT"); force_simt = (e && *e && *e != '0') ? 1 : 0; }
+    return !force_simt && D % 128 == 0 && I % 128 == 0;
+}
+
+// gate/up then down for the groups in `a` (a.q/a.s/a.X/a.Y/KD/OUT are filled here).
+// x: f32 rows; xp: scratch for the packed copy of x (rows_x rows); glu: scratch
+// [max_rows, I] (f32 or packed, same size); slots: [max_rows, D] f32.
+static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, const float *gu_s,
+                          const void *dn_q, const float *dn_s, const float *x, int rows_x, void *xp,
+                          float *glu, float *slots, float *sums, int D, int I, void (*mark)(void *, int), void *mark_ctx) {
+    if (sw_use_mma(D, I)) {
+        // sums: [rows_x] row sums of x, then [max_rows, I/8] partial row sums of the packed SiLU*up rows
+        float *xsum = sums, *ypart = sums + ((rows_x + 63) & ~63);
+        if (sw_launch_pack_act(cfg, x, xp, xsum, rows_x, D)) return -1;
+        a.q = (const uint8_t *)gu_q; a.s = gu_s; a.KD = D; a.OUT = I;
+        const int mt = sw_q4_mma_mt(cfg, a, true);
+        SwMmaIO io{xp, xsum, 1, glu, ypart};
+        if (sw_launch_q4_mma(cfg, a, io, true, mt)) return -1;
+        if (mark) mark(mark_ctx, 0);
+        a.q = (const uint8_t *)dn_q; a.s = dn_s; a.KD = I; a.OUT = D;
+        SwMmaIO io2{glu, ypart, I / (8 * mt), slots, nullptr};
+        if (sw_launch_q4_mma(cfg, a, io2, false, sw_q4_mma_mt(cfg, a, false))) return -1;
+        if (mark) mark(mark_ctx, 1);
+        return 0;
+    }
+    a.q = (const uint8_t *)gu_q; a.s = gu_s; a.X = x; a.Y = glu; a.KD = D; a.OUT = I;
+    if (sw_launch_q4_gateup(cfg, a)) return -1;
+    if (mark) mark(mark_ctx, 0);
+    a.q = (const uint8_t *)dn_q; a.s = dn_s; a.X = glu; a.Y = slots; a.KD = I; a.OUT = D;
+    if (sw_launch_q4_down(cfg, a)) return -1;
+    if (mark) mark(mark_ctx, 1);
+    return 0;
+}
+
 static int sw_route_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, int T, cudaStream_t st) {
     SwLaunchCfg cfg{c->num_sms, st};
     const int E = d->n_experts, K = d->topk;
@@ -183,10 +225,8 @@ static int sw_expert_stage(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
     a.gexp = c->r.gexp; a.gbeg = c->r.gbeg; a.gcnt = c->r.gcnt; a.G = c->r.G; a.grow = c->r.grow;
     a.expert_lo = lo; a.expert_cnt = cnt;
     a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K;
-    a.q = (const uint8_t *)L->gu_q; a.s = L->gu_s; a.X = x; a.Y = c->glu; a.KD = L->D; a.OUT = L->I;
-    if (sw_launch_q4_gateup(cfg, a)) return sw_fail("gate/up launch failed");
-    a.q = (const uint8_t *)L->dn_q; a.s = L->dn_s; a.X = c->glu; a.Y = c->slots; a.KD = L->I; a.OUT = L->D;
-    if (sw_launch_q4_down(cfg, a)) return sw_fail("down launch failed");
+    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, L->D, L->I, nullptr, nullptr))
+        return sw_fail("expert launch failed");
     return 0;
 }
 
@@ -249,12 +289,10 @@ extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
     a.gexp = c->r.gexp; a.gbeg = c->r.gbeg; a.gcnt = c->r.gcnt; a.G = c->r.G; a.grow = c->r.grow;
     a.expert_lo = lo; a.expert_cnt = cnt;
     a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K;
-    a.q = (const uint8_t *)L->gu_q; a.s = L->gu_s; a.X = x; a.Y = c->glu; a.KD = L->D; a.OUT = L->I;
-    if (sw_launch_q4_gateup(cfg, a)) return sw_fail("gate/up launch failed");
-    sw_prof_mark(c, SW_ST_GATEUP, st);
-    a.q = (const uint8_t *)L->dn_q; a.s = L->dn_s; a.X = c->glu; a.Y = c->slots; a.KD = L->I; a.OUT = L->D;
-    if (sw_launch_q4_down(cfg, a)) return sw_fail("down launch failed");
-    sw_prof_mark(c, SW_ST_DOWN, st);
+    struct MarkCtx { SwMoeCtx *c; cudaStream_t st; } mc{c, st};
+    auto mark = [](void *p, int which) { MarkCtx *m = (MarkCtx *)p; sw_prof_mark(m->c, which == 0 ? SW_ST_GATEUP : SW_ST_DOWN, m->st); };
+    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, L->D, L->I, mark, &mc))
+        return sw_fail("expert launch failed");
     if (has_shared && sw_launch_bf16_gateup(cfg, x, L->sh_gate, L->sh_up, c->sglu, T, L->D, L->SI)) return sw_fail("shared gate/up launch failed");
     sw_prof_mark(c, SW_ST_SH_GATEUP, st);
     if (has_shared && sw_launch_bf16_rows(cfg, c->sglu, L->sh_down, c->so, T, L->SI, L->D)) return sw_fail("shared down launch failed");
@@ -342,7 +380,7 @@ extern "C" const char *sw_moe_stage_name(int i) { return i >= 0 && i < SW_NSTAGE
 static struct {
     int ok = 0, dev = 0, num_sms = 0;
     cudaStream_t st = nullptr;
-    SwBuf dx, dy, dglu, dslot, didx, dmisc;
+    SwBuf dx, dy, dxp, dglu, dslot, dsums, didx, dmisc;
     SwBuf hx{nullptr, 0, true}, hy{nullptr, 0, true}, hidx{nullptr, 0, true};
 } g_lag;
 
@@ -439,7 +477,8 @@ static int lag_group_core(float *acc, const float *x, const void *gu_q, const fl
                           const int *grow, const int *rowof, const float *w, int S, int K, int I, int D) {
     if (!g_lag.ok || S <= 0 || K <= 0 || G <= 0 || (D % 32) || (I % 32)) return -1;
     const int P = S * K;
-    if (g_lag.dglu.ensure((size_t)P * I * 4) || g_lag.dslot.ensure((size_t)P * D * 4)) return -1;
+    if (g_lag.dglu.ensure((size_t)P * I * 4) || g_lag.dslot.ensure((size_t)P * D * 4) || g_lag.dxp.ensure((size_t)S * D * 4) ||
+        g_lag.dsums.ensure(((size_t)S + 64 + (size_t)P * (I / 8 + 1)) * 4)) return -1;
     LagIdx ix;
     if (lag_stage_idx(&ix, gexp, gbeg, gcnt, G, grow, rowof, w, P)) return -1;
     SwLaunchCfg cfg{g_lag.num_sms, g_lag.st};
@@ -447,10 +486,8 @@ static int lag_group_core(float *acc, const float *x, const void *gu_q, const fl
         SwQ4Args a{};
         a.gexp = ix.gexp; a.gbeg = ix.gbeg; a.gcnt = ix.gcnt; a.G = ix.G; a.grow = ix.grow;
         a.expert_lo = 0; a.expert_cnt = 0x7fffffff; a.max_groups = G; a.max_rows = P;
-        a.q = (const uint8_t *)gu_q; a.s = gu_s; a.X = (const float *)g_lag.dx.p; a.Y = (float *)g_lag.dglu.p; a.KD = D; a.OUT = I;
-        if (sw_launch_q4_gateup(cfg, a)) return -1;
-        a.q = (const uint8_t *)dn_q; a.s = dn_s; a.X = (const float *)g_lag.dglu.p; a.Y = (float *)g_lag.dslot.p; a.KD = I; a.OUT = D;
-        if (sw_launch_q4_down(cfg, a)) return -1;
+        if (sw_run_experts(cfg, a, gu_q, gu_s, dn_q, dn_s, (const float *)g_lag.dx.p, S, g_lag.dxp.p,
+                           (float *)g_lag.dglu.p, (float *)g_lag.dslot.p, (float *)g_lag.dsums.p, D, I, nullptr, nullptr)) return -1;
         return sw_launch_combine(cfg, (const float *)g_lag.dslot.p, ix.rowof, ix.sel, ix.w, nullptr, (float *)g_lag.dy.p,
                                  S, K, D, 1.f, 0, 0, 1);
     });

@@ -52,6 +52,17 @@ struct SwQ4Args {
 };
 int sw_launch_q4_gateup(const SwLaunchCfg &c, const SwQ4Args &a);
 int sw_launch_q4_down(const SwLaunchCfg &c, const SwQ4Args &a);
+// sw_mma.cu: tensor-core path (needs KD % 128 == 0)
+struct SwMmaIO {
+    const void *XP;        // packed activation rows
+    const float *xsum;     // [rows, xsum_parts] partial sums of each packed row's values
+    int xsum_parts;
+    void *Y;               // gate/up: packed rows; down: f32 rows
+    float *ypart;          // gate/up only: [rows, OUT/(8*mt)] sums of what each item wrote
+};
+int sw_launch_pack_act(const SwLaunchCfg &c, const float *x, void *xp, float *rowsum, int rows, int KD);
+int sw_q4_mma_mt(const SwLaunchCfg &c, const SwQ4Args &a, bool gateup);
+int sw_launch_q4_mma(const SwLaunchCfg &c, const SwQ4Args &a, const SwMmaIO &io, bool gateup, int mt);
 int sw_launch_bf16_gateup(const SwLaunchCfg &c, const float *x, const void *Wg, const void *Wu,
                           float *sglu, int T, int D, int SI);
 int sw_launch_bf16_rows(const SwLaunchCfg &c, const float *x, const void *W, float *y, int T, int I, int O);

@@ -1,0 +1,383 @@
+// Bandwidth-bound grouped int4 expert products for decode-size groups.
+//
+// Every warp streams whole weight rows (16-byte cp.async copies into a private
+// shared-memory ring), dequantises the nibbles in registers straight into
+// tensor-core A fragments and multiplies them with activation B fragments that
+// were pre-split into fp16 hi + lo halves (x = hi + lo to ~21 bits),
+// accumulating in f32.  The per-row f32 scale is applied in the epilogue as
+// acc*scale[o], like the reference (c/moe_quant.h:104,
+// c/backend_cuda_laguna.cu:156).  No CTA-wide synchronisation: a warp is the
+// unit of work.
+//
+// Dequantisation without arithmetic.  A nibble n masked in place into the low
+// mantissa bits of an fp16 is the subnormal n*2^-24 (bits 0..3) or n*2^-20 (bits
+// 4..7); both are exact tensor-core operands.  So the A fragments are just
+// (w & 0x000F000F), (w & 0x00F000F0) of the weight word and of the word shifted
+// by 8: five integer instructions per eight weights.  The factor 16 of the
+// odd columns is taken out of the activations when they are packed (x/16 there),
+// and the "-8" of value = nibble-8 is restored in the epilogue:
+//     dot = 2^24 * acc - 8 * sum_k x_k
+// with the row sums of the activations computed once where the rows are produced.
+//
+// Fragment bookkeeping (m16n8k16, lane = 4*g + t):
+//   A rows g / g+8 are two weight rows; for gate/up they are gate row i and up
+//   row I+i, so the SiLU(gate)*up epilogue is thread-local.
+//   A thread's 16 bytes of a weight row are 32 consecutive columns; one 32-bit
+//   word (8 columns c0..c7) gives the half2 pairs (c0,c4)(c1,c5)(c2,c6)(c3,c7),
+//   which feed two MMAs as k-slots {2t,2t+1 | 2t+8,2t+9}.  The activations are
+//   stored in exactly that order ("packed rows"), so the B fragments of those two
+//   MMAs are one 16-byte load.
+//   B columns: groups of up to 4 token rows put the hi halves of tokens 0..3 in
+//   columns 0..3 and their lo halves in columns 4..7 (one MMA per tile, the two
+//   column halves are added in the epilogue); groups of 5..8 rows use one MMA for
+//   hi and one for lo.
+//
+// Packed activation row of length KD (KD % 128 == 0): KD/8 chunks of 32 bytes,
+// chunk = [8 fp16 hi | 8 fp16 lo] of columns 8c..8c+7 in the order
+// 0,4,1,5,2,6,3,7 (odd columns divided by 16), chunks ordered (step s = c/16,
+// word wi = c%4, quarter t = (c/4)%4) so that the four lanes of one row read 64
+// contiguous bytes.
+#include "sw_common.cuh"
+#include <cuda_fp16.h>
+#include <stdlib.h>
+
+__device__ __forceinline__ void sw_mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                           uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// 8 nibbles -> 4 half2 operands: [0]=(n0,n4)*2^-24 [1]=(n1,n5)*2^-20 [2]=(n2,n6)*2^-24 [3]=(n3,n7)*2^-20
+__device__ __forceinline__ void sw_dq4(uint32_t w, uint32_t (&h)[4]) {
+    const uint32_t w2 = w >> 8;
+    h[0] = w & 0x000F000Fu; h[1] = w & 0x00F000F0u;
+    h[2] = w2 & 0x000F000Fu; h[3] = w2 & 0x00F000F0u;
+}
+#define SW_ACC_SCALE 16777216.f      /* 2^24 */
+
+__device__ __forceinline__ uint32_t sw_word(const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+// position (in halves) of column `col` inside a packed row: chunk*16 + slot
+__device__ __forceinline__ size_t sw_packed_pos(int col) {
+    const int c8 = col >> 3, s = c8 >> 4, tt = (c8 >> 2) & 3, wi = c8 & 3, j = col & 7;
+    return (size_t)(((s * 4 + wi) * 4 + tt) * 16 + ((j & 3) * 2 + (j >> 2)));
+}
+
+// f32 -> fp16 hi/lo pair (saturating at the fp16 range); returns the value the pair represents
+__device__ __forceinline__ float sw_split_f16(float v, __half &hi, __half &lo) {
+    v = fminf(fmaxf(v, -65504.f), 65504.f);
+    hi = __float2half_rn(v);
+    const float h = __half2float(hi);
+    lo = __float2half_rn(v - h);
+    return h + __half2float(lo);
+}
+
+// ---------------------------------------------------------------------------
+// x[rows, KD] f32 -> packed rows + row sums of the represented values.
+// One CTA per row; the sum is reduced in double in a fixed order.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+k_pack_act(const float *__restrict__ x, uint4 *__restrict__ xp, float *__restrict__ rowsum, int rows, int KD) {
+    __shared__ double s_part[8];
+    const int cpr = KD >> 3;                                  // chunks per row
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        double sum = 0.0;
+        for (int c8 = threadIdx.x; c8 < cpr; c8 += 256) {
+            const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)r * KD + c8 * 8);
+            const float4 a = src[0], b = src[1];
+            // order 0,4,1,5,2,6,3,7; odd columns carry 1/16
+            const float v[8] = {a.x, b.x, a.y * 0.0625f, b.y * 0.0625f, a.z, b.z, a.w * 0.0625f, b.w * 0.0625f};
+            __half hi[8], lo[8];
+            float even = 0.f, odd = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float rep = sw_split_f16(v[i], hi[i], lo[i]);
+                if ((i >> 1) & 1) odd += rep; else even += rep;
+            }
+            sum += (double)even + 16.0 * (double)odd;
+            const int s = c8 >> 4, tt = (c8 >> 2) & 3, wi = c8 & 3;
+            uint4 *dst = xp + ((size_t)r * cpr + ((s * 4 + wi) * 4 + tt)) * 2;
+            dst[0] = *reinterpret_cast<uint4 *>(hi);
+            dst[1] = *reinterpret_cast<uint4 *>(lo);
+        }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) sum += __shfl_xor_sync(SW_FULL_MASK, sum, off);
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = sum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t = 0.0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) t += s_part[i];
+            rowsum[r] = (float)t;
+        }
+    }
+}
+
+int sw_launch_pack_act(const SwLaunchCfg &c, const float *x, void *xp, float *rowsum, int rows, int KD) {
+    if (rows <= 0) return 0;
+    if (KD % 128) return -1;
+    int grid = rows < c.num_sms * 8 ? rows : c.num_sms * 8;
+    k_pack_act<<<grid, 256, 0, c.stream>>>(x, (uint4 *)xp, rowsum, rows, KD);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// ---------------------------------------------------------------------------
+// Grouped int4 product.  Warp item = (group, block of MT m-tiles).
+//   GATEUP: m-tile = gate rows i..i+7 and up rows I+i..I+i+7, output = packed
+//           fp16 hi/lo rows of SiLU(gate)*up  [T*K, I] plus, per packed row and
+//           item, the sum of the values it wrote (ypart[row, I/8 slots]), from
+//           which the down product rebuilds its row sums in a fixed order
+//   else  : m-tile = 16 output rows, output = f32 slots [T*K, D]
+// A pass covers 4 token rows (hi|lo side by side) or 8; larger groups loop and
+// find the weights of the item in L2.
+//
+// Weight stream: every thread owns a private ring of P stages in shared memory
+// and fills it with 16-byte cp.async copies of the bytes it will itself consume
+// (one stage = one 128-column step of its 2*MT rows), so P-1 steps of HBM
+// traffic are in flight per thread at no register cost and without any barrier:
+// a thread only ever reads back what it copied, after cp.async.wait_group.
+//
+// Accumulation: the tensor core adds products into its accumulator with
+// truncation, which biases a long chain; each 128-column step therefore starts
+// from a zero accumulator and is added to the running f32 sum with an ordinary
+// round-to-nearest add.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void sw_cp_async16(unsigned smem_addr, const void *gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_addr), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void sw_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void sw_cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
+
+template <bool GATEUP, int MT, int P>
+__global__ void __launch_bounds__(128, (MT == 4 ? 3 : 4))
+k_q4_mma(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
+         const uint4 *__restrict__ XP, const float *__restrict__ xsum, int xsum_parts,
+         void *__restrict__ Yout, float *__restrict__ ypart,
+         const int *__restrict__ gexp, const int *__restrict__ gbeg, const int *__restrict__ gcnt,
+         const int *__restrict__ Gp, const int *__restrict__ grow,
+         int KD, int OUT, int expert_lo, int expert_cnt) {
+    extern __shared__ uint4 sw_ring[];                        // [P][2*MT][128]
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int warps_total = gridDim.x * 4, wid = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int G = *Gp;
+    constexpr int OPI = MT * (GATEUP ? 8 : 16);              // outputs per item
+    constexpr int STAGE = 2 * MT * 128;                       // uint4 per ring stage
+    const int mb_per_group = (OUT + OPI - 1) / OPI;
+    const int items = G * mb_per_group;
+    const int S = KD >> 7;                                    // 128-column steps
+    const unsigned row_u4 = (unsigned)(KD >> 5);              // uint4 per weight row
+    const size_t xrow_u4 = (size_t)(KD >> 2);                 // uint4 per packed activation row
+    const int nrows_w = GATEUP ? 2 * OUT : OUT;
+    const uint4 *my = sw_ring + threadIdx.x;
+    const unsigned my_s = (unsigned)__cvta_generic_to_shared(sw_ring + threadIdx.x);
+
+    for (int item = wid; item < items; item += warps_total) {
+        const int gi = item / mb_per_group, mb = item - gi * mb_per_group;
+        const int e = gexp[gi] - expert_lo;
+        if (e < 0 || e >= expert_cnt) continue;
+        const int n = gcnt[gi], beg = gbeg[gi];
+        const uint4 *wq = reinterpret_cast<const uint4 *>(Wq) + (size_t)e * nrows_w * row_u4 + t;
+        const float *ws = Ws + (size_t)e * nrows_w;
+
+        unsigned roff[2 * MT];                                // [2*mt] = row of role g, [2*mt+1] = row of role g+8
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+            int ra, rb;
+            if (GATEUP) { int o = min(mb * OPI + mt * 8 + g, OUT - 1); ra = o; rb = OUT + o; }
+            else        { int o = mb * OPI + mt * 16 + g; ra = min(o, OUT - 1); rb = min(o + 8, OUT - 1); }
+            roff[2 * mt] = (unsigned)ra * row_u4;
+            roff[2 * mt + 1] = (unsigned)rb * row_u4;
+        }
+
+        for (int c0 = 0; c0 < n;) {
+            const bool m8 = n - c0 > 4;                       // warp-uniform: 8 rows (hi, lo apart) or 4 rows (hi|lo)
+            const int ntok = m8 ? min(8, n - c0) : n - c0;
+            // B column g of this thread: which packed row, and which half of the chunk
+            const int bt = m8 ? g : (g & 3);
+            const int r = c0 + min(bt, ntok - 1);
+            const int rowid = GATEUP ? grow[beg + r] : beg + r;
+            const uint4 *xb = XP + (size_t)rowid * xrow_u4 + (size_t)t * 2 + ((!m8 && g >= 4) ? 1 : 0);
+
+            float acc[MT][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) acc[mt][i] = 0.f;
+
+            // prologue: stages 0..P-2 (one commit per stage keeps the group count uniform)
+#pragma unroll
+            for (int p = 0; p < P - 1; p++) {
+                if (p < S) {
+#pragma unroll
+                    for (int q = 0; q < 2 * MT; q++) sw_cp_async16(my_s + (unsigned)(p * STAGE + q * 128) * 16u, wq + roff[q] + p * 4);
+                }
+                sw_cp_async_commit();
+            }
+            int sc = 0, sf = P - 1;                           // ring slot consumed / filled next
+            for (int s = 0; s < S; s++) {
+                if (s + P - 1 < S) {
+#pragma unroll
+                    for (int q = 0; q < 2 * MT; q++) sw_cp_async16(my_s + (unsigned)(sf * STAGE + q * 128) * 16u, wq + roff[q] + (s + P - 1) * 4);
+                }
+                sw_cp_async_commit();
+                sw_cp_async_wait<P - 1>();                    // stage s has landed
+                uint4 wv[2 * MT];
+#pragma unroll
+                for (int q = 0; q < 2 * MT; q++) wv[q] = my[sc * STAGE + q * 128];
+                sc = sc + 1 == P ? 0 : sc + 1;
+                sf = sf + 1 == P ? 0 : sf + 1;
+
+                float part[MT][4];
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) part[mt][i] = 0.f;
+#pragma unroll
+                for (int wi = 0; wi < 4; wi++) {
+                    const uint4 *bp = xb + (size_t)((s * 4 + wi) * 4) * 2;
+                    const uint4 b0 = __ldg(bp);
+                    uint4 b1 = b0;
+                    if (m8) b1 = __ldg(bp + 1);
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++) {
+                        uint32_t ga[4], ua[4];
+                        sw_dq4(sw_word(wv[2 * mt], wi), ga);
+                        sw_dq4(sw_word(wv[2 * mt + 1], wi), ua);
+                        sw_mma_f16(part[mt], ga[0], ua[0], ga[1], ua[1], b0.x, b0.y);
+                        sw_mma_f16(part[mt], ga[2], ua[2], ga[3], ua[3], b0.z, b0.w);
+                        if (m8) {
+                            sw_mma_f16(part[mt], ga[0], ua[0], ga[1], ua[1], b1.x, b1.y);
+                            sw_mma_f16(part[mt], ga[2], ua[2], ga[3], ua[3], b1.z, b1.w);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) acc[mt][i] += part[mt][i];
+            }
+            sw_cp_async_wait<0>();
+
+            // In 4-row mode columns j and j+4 hold the hi and lo parts of one token: fold them.
+            if (!m8) {
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) acc[mt][i] += __shfl_down_sync(SW_FULL_MASK, acc[mt][i], 2);
+            }
+            // token rows of this thread's two columns, and the "-8 * sum x" correction
+            const bool own = m8 || t < 2;
+            float corr[2]; int tok[2];
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                tok[j] = c0 + 2 * t + j;
+                const bool ok = own && tok[j] < c0 + ntok;
+                float sx = 0.f;
+                if (ok) {
+                    const int rid = GATEUP ? grow[beg + tok[j]] : beg + tok[j];
+                    const float *ps = xsum + (size_t)rid * xsum_parts;
+                    for (int k = 0; k < xsum_parts; k++) sx += ps[k];
+                }
+                corr[j] = 8.f * sx;
+                if (!ok) tok[j] = -1;
+            }
+
+            // epilogue: c[0],c[1] = (row g, tokens 2t,2t+1), c[2],c[3] = (row g+8, same tokens)
+            if (GATEUP) {
+                float ysum[2] = {0.f, 0.f};
+                __half *Y = reinterpret_cast<__half *>(Yout);
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+                    const int o = mb * OPI + mt * 8 + g;
+                    const bool ov = o < OUT;
+                    const float sg = ov ? ws[o] : 0.f, su = ov ? ws[OUT + o] : 0.f;
+                    const size_t pos = sw_packed_pos(ov ? o : 0);
+                    const float pre = (o & 1) ? 0.0625f : 1.f;
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        if (tok[j] < 0 || !ov) continue;
+                        const float gv = (acc[mt][j] * SW_ACC_SCALE - corr[j]) * sg;
+                        const float uv = (acc[mt][2 + j] * SW_ACC_SCALE - corr[j]) * su;
+                        const float y = (gv / (1.f + expf(-gv))) * uv;
+                        __half hi, lo;
+                        const float rep = sw_split_f16(y * pre, hi, lo);
+                        ysum[j] += (o & 1) ? rep * 16.f : rep;
+                        __half *row = Y + (size_t)(beg + tok[j]) * (2 * (size_t)OUT);
+                        row[pos] = hi; row[pos + 8] = lo;
+                    }
+                }
+                // sum over the item's outputs (the 8 row groups g) in a fixed order
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    float v = ysum[j];
+                    v += __shfl_xor_sync(SW_FULL_MASK, v, 4);
+                    v += __shfl_xor_sync(SW_FULL_MASK, v, 8);
+                    v += __shfl_xor_sync(SW_FULL_MASK, v, 16);
+                    if (g == 0 && tok[j] >= 0) ypart[(size_t)(beg + tok[j]) * mb_per_group + mb] = v;
+                }
+            } else {
+                float *Y = reinterpret_cast<float *>(Yout);
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+                    const int oa = mb * OPI + mt * 16 + g, ob = oa + 8;
+                    const float sa = oa < OUT ? ws[oa] : 0.f, sb = ob < OUT ? ws[ob] : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        if (tok[j] < 0) continue;
+                        float *row = Y + (size_t)(beg + tok[j]) * OUT;
+                        if (oa < OUT) row[oa] = (acc[mt][j] * SW_ACC_SCALE - corr[j]) * sa;
+                        if (ob < OUT) row[ob] = (acc[mt][2 + j] * SW_ACC_SCALE - corr[j]) * sb;
+                    }
+                }
+            }
+            c0 += ntok;
+        }
+    }
+}
+
+template <bool GATEUP, int MT, int P>
+static int sw_launch_q4_mma_t(const SwLaunchCfg &c, const SwQ4Args &a, const SwMmaIO &io) {
+    static int ctas_per_sm = 0;                       // resident CTAs of this instantiation
+    constexpr int SMEM = P * 2 * MT * 128 * 16;
+    auto kern = k_q4_mma<GATEUP, MT, P>;
+    if (ctas_per_sm == 0) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, kern, 128, SMEM) != cudaSuccess || ctas_per_sm < 1) {
+            cudaGetLastError(); ctas_per_sm = 1;
+        }
+    }
+    long long grid = (long long)c.num_sms * ctas_per_sm;
+    constexpr int OPI = MT * (GATEUP ? 8 : 16);
+    long long items = (long long)a.max_groups * ((a.OUT + OPI - 1) / OPI);
+    long long need = (items + 3) / 4;
+    if (grid > need) grid = need;
+    if (grid < 1) grid = 1;
+    kern<<<(unsigned)grid, 128, SMEM, c.stream>>>(a.q, a.s, (const uint4 *)io.XP, io.xsum, io.xsum_parts, io.Y, io.ypart,
+                                                  a.gexp, a.gbeg, a.gcnt, a.G, a.grow, a.KD, a.OUT, a.expert_lo, a.expert_cnt);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// m-tiles per warp item for a launch: few groups (single-row decode) want small
+// items so that every SM gets work; SW_MMA_MT=1|2|4 overrides the choice (tuning knob).
+int sw_q4_mma_mt(const SwLaunchCfg &c, const SwQ4Args &a, bool gateup) {
+    static int mt_env = -1;
+    if (mt_env < 0) { const char *e = getenv("SW_MMA_MT"); mt_env = e ? atoi(e) : 0; }
+    if (mt_env == 1 || mt_env == 2 || mt_env == 4) return mt_env;
+    const int opi4 = gateup ? 32 : 64;
+    const long long items4 = (long long)a.max_groups * ((a.OUT + opi4 - 1) / opi4);
+    return items4 >= (long long)c.num_sms * 32 ? 4 : items4 >= (long long)c.num_sms * 8 ? 2 : 1;
+}
+
+// io.XP: packed activation rows (gate/up: the token rows, indexed through grow;
+// down: the packed SiLU*up rows) with io.xsum[row, xsum_parts] partial row sums.
+// io.Y: gate/up -> packed rows [max_rows, OUT] and io.ypart[max_rows, OUT/(8*mt)]; down -> f32.
+int sw_launch_q4_mma(const SwLaunchCfg &c, const SwQ4Args &a, const SwMmaIO &io, bool gateup, int mt) {
+    if (a.max_groups <= 0 || a.max_rows <= 0) return 0;
+    if (a.KD % 128 || a.OUT <= 0) return -1;
+    if (gateup) return mt == 4 ? sw_launch_q4_mma_t<true, 4, 4>(c, a, io) : mt == 2 ? sw_launch_q4_mma_t<true, 2, 6>(c, a, io) : sw_launch_q4_mma_t<true, 1, 12>(c, a, io);
+    return mt == 4 ? sw_launch_q4_mma_t<false, 4, 4>(c, a, io) : mt == 2 ? sw_launch_q4_mma_t<false, 2, 6>(c, a, io) : sw_launch_q4_mma_t<false, 1, 12>(c, a, io);
+}
