@@ -55,6 +55,8 @@ struct SwMoeCtx {
     float *glu = nullptr, *slots = nullptr, *sglu = nullptr, *so = nullptr, *routed = nullptr;
     float *dx = nullptr, *dout = nullptr, *hx = nullptr, *hout = nullptr;
     void *xp = nullptr;          // packed fp16 hi/lo copy of x for the tensor-core path
+    double *rpart = nullptr;     // fp64 partial router logits [slices][T][E]
+    void *spk = nullptr;         // packed bf16 hi/lo copy of x for the shared expert
     float *sums = nullptr;       // row sums of x and partial row sums of the SiLU*up rows
     int lastT = 0, lastK = 0, lastE = 0;
     void *block = nullptr;      // one device allocation holding all device scratch
@@ -103,11 +105,13 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
         P * I * 4,            // glu
         P * D * 4,            // slots
         T * (SI ? SI : 1) * 4,// sglu
-        T * D * 4,            // so
+        (((D + 255) / 256) * T * 2 * (SI ? SI : 1) + ((SI + 255) / 256 + 1) * T * D) * 4,   // so: slice partials of the shared expert
         T * D * 4,            // routed
         T * D * 4, T * D * 4, // dx, dout
         T * D * 4,            // xp
-        (T + 64) * 4 + P * (I / 8 + 1) * 4   // sums
+        (T + 64) * 4 + P * (I / 8 + 1) * 4,  // sums
+        T * D * 4,            // spk
+        ((size_t)((D + 255) / 256) * (T < 128 ? T : 128) + ((size_t)c->num_sms * 16 * 256 + E - 1) / E + T + 64) * E * 8   // rpart
     };
     size_t total = 0; for (size_t s : sizes) total += sw_align(s);
     if (cudaMalloc(&c->block, total) != cudaSuccess) {
@@ -120,7 +124,7 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
     c->r.gexp = (int *)take(); c->r.gbeg = (int *)take(); c->r.gcnt = (int *)take();
     c->r.grow = (int *)take(); c->r.rowof = (int *)take(); c->r.status = (int *)take();
     c->glu = (float *)take(); c->slots = (float *)take(); c->sglu = (float *)take(); c->so = (float *)take();
-    c->routed = (float *)take(); c->dx = (float *)take(); c->dout = (float *)take(); c->xp = take(); c->sums = (float *)take();
+    c->routed = (float *)take(); c->dx = (float *)take(); c->dout = (float *)take(); c->xp = take(); c->sums = (float *)take(); c->spk = take(); c->rpart = (double *)take();
     cudaMemsetAsync(c->r.G, 0, 256, c->stream); cudaMemsetAsync(c->r.status, 0, 256, c->stream);
     if (cudaMallocHost((void **)&c->hx, T * D * 4) != cudaSuccess || cudaMallocHost((void **)&c->hout, T * D * 4) != cudaSuccess) {
         cudaGetLastError(); sw_moe_ctx_destroy(c);
@@ -207,11 +211,32 @@ static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, 
     return 0;
 }
 
+// router logits + gate + top-k; fp64 tensor-core logits when D is a multiple of 32
+static int sw_logits_topk(SwMoeCtx *c, const SwLaunchCfg &cfg, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, int T,
+                          bool mark) {
+    const int E = d->n_experts, K = d->topk;
+    static int force_simt = -1;
+    if (force_simt < 0) { const char *e = getenv("SW_FORCE_SIMT"); force_simt = (e && *e && *e != '0') ? 1 : 0; }
+    if (!force_simt && L->D % 32 == 0) {
+        const int KS = sw_router_slices(c->num_sms, T, L->D, E);
+        if (sw_launch_router_dmma(cfg, x, L->router_w, L->router_dtype, c->rpart, T, L->D, E, KS)) return sw_fail("router launch failed");
+        if (mark) sw_prof_mark(c, SW_ST_LOGITS, cfg.stream);
+        if (sw_launch_route_topk(cfg, c->r.scores, c->rpart, KS, L->logit_bias, L->corr_bias, d->use_corr_bias, d->route_act,
+                                 d->norm_topk, T, E, K, c->r.sel, c->r.w)) return sw_fail("route_topk launch failed");
+    } else {
+        if (sw_launch_router_logits(cfg, x, L->router_w, L->router_dtype, L->logit_bias, c->r.scores, T, L->D, E)) return sw_fail("router_logits launch failed");
+        if (mark) sw_prof_mark(c, SW_ST_LOGITS, cfg.stream);
+        if (sw_launch_route_topk(cfg, c->r.scores, nullptr, 0, nullptr, L->corr_bias, d->use_corr_bias, d->route_act,
+                                 d->norm_topk, T, E, K, c->r.sel, c->r.w)) return sw_fail("route_topk launch failed");
+    }
+    if (mark) sw_prof_mark(c, SW_ST_TOPK, cfg.stream);
+    return 0;
+}
+
 static int sw_route_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, int T, cudaStream_t st) {
     SwLaunchCfg cfg{c->num_sms, st};
     const int E = d->n_experts, K = d->topk;
-    if (sw_launch_router_logits(cfg, x, L->router_w, L->router_dtype, L->logit_bias, c->r.scores, T, L->D, E)) return sw_fail("router_logits launch failed");
-    if (sw_launch_route_topk(cfg, c->r.scores, L->corr_bias, d->use_corr_bias, d->route_act, d->norm_topk, T, E, K, c->r.sel, c->r.w)) return sw_fail("route_topk launch failed");
+    if (sw_logits_topk(c, cfg, d, L, x, T, false)) return -1;
     if (sw_launch_dispatch(cfg, c->r, T, K, E)) return sw_fail("dispatch launch failed");
     c->last_stream = st; c->lastT = T; c->lastK = K; c->lastE = E;
     return 0;
@@ -230,10 +255,38 @@ static int sw_expert_stage(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
     return 0;
 }
 
-static int sw_shared_stage(SwMoeCtx *c, const SwMoeLayer *L, const float *x, int T, cudaStream_t st) {
+// Shared expert: so[T,D] = down(silu(gate x) * (up x)).  Tensor-core path when the
+// widths are multiples of 32; `pk` is scratch for the packed copy of x, sglu holds
+// the packed (or f32) intermediate.
+static int sw_shared_run(const SwLaunchCfg &cfg, const SwMoeLayer *L, const float *x, int T, void *pk, float *sglu, float *spart,
+                         float **so, int *so_slices, void (*mark)(void *, int), void *mark_ctx) {
+    static int force_simt = -1;
+    if (force_simt < 0) { const char *e = getenv("SW_FORCE_SIMT"); force_simt = (e && *e && *e != '0') ? 1 : 0; }
+    if (!force_simt && L->D % 32 == 0 && L->SI % 32 == 0) {
+        const int ks1 = sw_shared_slices(cfg.num_sms, (L->SI + 7) / 8, L->D);
+        const int ks2 = sw_shared_slices(cfg.num_sms, (L->D + 15) / 16, L->SI);
+        if (sw_launch_pack_bf16(cfg, x, pk, T, L->D)) return -1;
+        if (sw_launch_bf16_mma(cfg, L->sh_gate, L->sh_up, pk, spart, T, L->D, L->SI, ks1, true)) return -1;
+        if (sw_launch_shared_glu(cfg, spart, ks1, T, L->SI, sglu)) return -1;
+        if (mark) mark(mark_ctx, 0);
+        float *dpart = spart + (size_t)ks1 * T * 2 * L->SI;
+        if (sw_launch_bf16_mma(cfg, L->sh_down, nullptr, sglu, dpart, T, L->SI, L->D, ks2, false)) return -1;
+        if (mark) mark(mark_ctx, 1);
+        *so = dpart; *so_slices = ks2;
+        return 0;
+    }
+    float *o = spart;
+    if (sw_launch_bf16_gateup(cfg, x, L->sh_gate, L->sh_up, sglu, T, L->D, L->SI)) return -1;
+    if (mark) mark(mark_ctx, 0);
+    if (sw_launch_bf16_rows(cfg, sglu, L->sh_down, o, T, L->SI, L->D)) return -1;
+    if (mark) mark(mark_ctx, 1);
+    *so = o; *so_slices = 1;
+    return 0;
+}
+
+static int sw_shared_stage(SwMoeCtx *c, const SwMoeLayer *L, const float *x, int T, cudaStream_t st, float **so, int *so_slices) {
     SwLaunchCfg cfg{c->num_sms, st};
-    if (sw_launch_bf16_gateup(cfg, x, L->sh_gate, L->sh_up, c->sglu, T, L->D, L->SI)) return sw_fail("shared gate/up launch failed");
-    if (sw_launch_bf16_rows(cfg, c->sglu, L->sh_down, c->so, T, L->SI, L->D)) return sw_fail("shared down launch failed");
+    if (sw_shared_run(cfg, L, x, T, c->spk, c->sglu, c->so, so, so_slices, nullptr, nullptr)) return sw_fail("shared expert launch failed");
     return 0;
 }
 
@@ -252,7 +305,7 @@ extern "C" int sw_moe_experts(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
     if (sw_expert_stage(c, d, L, x, T, st)) return -1;
     SwLaunchCfg cfg{c->num_sms, st};
     int lo, cnt; sw_resident(d, L, &lo, &cnt);
-    if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, nullptr, routed, T, d->topk, L->D, 1.f, 0, lo, cnt)) return sw_fail("combine launch failed");
+    if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, nullptr, 0, routed, T, d->topk, L->D, 1.f, 0, lo, cnt)) return sw_fail("combine launch failed");
     return 0;
 }
 
@@ -262,8 +315,9 @@ extern "C" int sw_moe_finish(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *
     cudaStream_t st = (cudaStream_t)stream;
     SwLaunchCfg cfg{c->num_sms, st};
     const int has_shared = d->shared_mode != SW_SHARED_NONE;
-    if (has_shared && sw_shared_stage(c, L, x, T, st)) return -1;
-    if (sw_launch_finish(cfg, routed, c->so, out, T, L->D, d->route_scale, has_shared)) return sw_fail("finish launch failed");
+    float *so = nullptr; int so_slices = 1;
+    if (has_shared && sw_shared_stage(c, L, x, T, st, &so, &so_slices)) return -1;
+    if (sw_launch_finish(cfg, routed, so, so_slices, out, T, L->D, d->route_scale, has_shared)) return sw_fail("finish launch failed");
     return 0;
 }
 
@@ -277,10 +331,7 @@ extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
     const int has_shared = d->shared_mode != SW_SHARED_NONE;
 
     sw_prof_mark(c, -1, st);
-    if (sw_launch_router_logits(cfg, x, L->router_w, L->router_dtype, L->logit_bias, c->r.scores, T, L->D, E)) return sw_fail("router_logits launch failed");
-    sw_prof_mark(c, SW_ST_LOGITS, st);
-    if (sw_launch_route_topk(cfg, c->r.scores, L->corr_bias, d->use_corr_bias, d->route_act, d->norm_topk, T, E, K, c->r.sel, c->r.w)) return sw_fail("route_topk launch failed");
-    sw_prof_mark(c, SW_ST_TOPK, st);
+    if (sw_logits_topk(c, cfg, d, L, x, T, true)) return -1;
     if (sw_launch_dispatch(cfg, c->r, T, K, E)) return sw_fail("dispatch launch failed");
     sw_prof_mark(c, SW_ST_DISPATCH, st);
     c->last_stream = st; c->lastT = T; c->lastK = K; c->lastE = E;
@@ -293,11 +344,14 @@ extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
     auto mark = [](void *p, int which) { MarkCtx *m = (MarkCtx *)p; sw_prof_mark(m->c, which == 0 ? SW_ST_GATEUP : SW_ST_DOWN, m->st); };
     if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, L->D, L->I, mark, &mc))
         return sw_fail("expert launch failed");
-    if (has_shared && sw_launch_bf16_gateup(cfg, x, L->sh_gate, L->sh_up, c->sglu, T, L->D, L->SI)) return sw_fail("shared gate/up launch failed");
-    sw_prof_mark(c, SW_ST_SH_GATEUP, st);
-    if (has_shared && sw_launch_bf16_rows(cfg, c->sglu, L->sh_down, c->so, T, L->SI, L->D)) return sw_fail("shared down launch failed");
-    sw_prof_mark(c, SW_ST_SH_DOWN, st);
-    if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, c->so, out, T, K, L->D,
+    auto smark = [](void *p, int which) { MarkCtx *m = (MarkCtx *)p; sw_prof_mark(m->c, which == 0 ? SW_ST_SH_GATEUP : SW_ST_SH_DOWN, m->st); };
+    float *so = nullptr; int so_slices = 1;
+    if (has_shared) {
+        if (sw_shared_run(cfg, L, x, T, c->spk, c->sglu, c->so, &so, &so_slices, smark, &mc)) return sw_fail("shared expert launch failed");
+    } else {
+        sw_prof_mark(c, SW_ST_SH_GATEUP, st); sw_prof_mark(c, SW_ST_SH_DOWN, st);
+    }
+    if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, so, so_slices, out, T, K, L->D,
                           d->route_scale, 1 | (has_shared ? 2 : 0) | 4, lo, cnt)) return sw_fail("combine launch failed");
     sw_prof_mark(c, SW_ST_COMBINE, st);
     if (c->prof_on && c->prof_calls < SW_PROF_MAX_CALLS) c->prof_calls++;
@@ -488,7 +542,7 @@ static int lag_group_core(float *acc, const float *x, const void *gu_q, const fl
         a.expert_lo = 0; a.expert_cnt = 0x7fffffff; a.max_groups = G; a.max_rows = P;
         if (sw_run_experts(cfg, a, gu_q, gu_s, dn_q, dn_s, (const float *)g_lag.dx.p, S, g_lag.dxp.p,
                            (float *)g_lag.dglu.p, (float *)g_lag.dslot.p, (float *)g_lag.dsums.p, D, I, nullptr, nullptr)) return -1;
-        return sw_launch_combine(cfg, (const float *)g_lag.dslot.p, ix.rowof, ix.sel, ix.w, nullptr, (float *)g_lag.dy.p,
+        return sw_launch_combine(cfg, (const float *)g_lag.dslot.p, ix.rowof, ix.sel, ix.w, nullptr, 0, (float *)g_lag.dy.p,
                                  S, K, D, 1.f, 0, 0, 1);
     });
 }

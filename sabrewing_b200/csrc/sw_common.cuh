@@ -35,7 +35,12 @@ void sw_count_launch(int n = 1);
 // sw_route.cu
 int sw_launch_router_logits(const SwLaunchCfg &c, const float *x, const void *W, int w_dtype,
                             const float *logit_bias, float *rl, int T, int D, int E);
-int sw_launch_route_topk(const SwLaunchCfg &c, float *scores, const float *corr_bias, int use_bias,
+int sw_router_slices(int num_sms, int T, int D, int E);
+int sw_launch_router_dmma(const SwLaunchCfg &c, const float *x, const void *W, int w_dtype, double *part,
+                          int T, int D, int E, int KS);
+// part != NULL: logits are first formed as (float)(sum of KS fp64 partials [KS][T][E]) + lbias
+int sw_launch_route_topk(const SwLaunchCfg &c, float *scores, const double *part, int KS, const float *lbias,
+                         const float *corr_bias, int use_bias,
                          int route_act, int norm_topk, int T, int E, int K, int *sel, float *w);
 int sw_launch_dispatch(const SwLaunchCfg &c, const SwRouting &r, int T, int K, int E);
 
@@ -63,6 +68,11 @@ struct SwMmaIO {
 int sw_launch_pack_act(const SwLaunchCfg &c, const float *x, void *xp, float *rowsum, int rows, int KD);
 int sw_q4_mma_mt(const SwLaunchCfg &c, const SwQ4Args &a, bool gateup);
 int sw_launch_q4_mma(const SwLaunchCfg &c, const SwQ4Args &a, const SwMmaIO &io, bool gateup, int mt);
+int sw_launch_pack_bf16(const SwLaunchCfg &c, const float *x, void *xp, int rows, int KD);
+int sw_shared_slices(int num_sms, int mblocks, int KD);
+int sw_launch_bf16_mma(const SwLaunchCfg &c, const void *W0, const void *W1, const void *XP, float *part,
+                       int T, int KD, int O, int KS, bool gateup);
+int sw_launch_shared_glu(const SwLaunchCfg &c, const float *part, int KS, int T, int SI, void *out);
 int sw_launch_bf16_gateup(const SwLaunchCfg &c, const float *x, const void *Wg, const void *Wu,
                           float *sglu, int T, int D, int SI);
 int sw_launch_bf16_rows(const SwLaunchCfg &c, const float *x, const void *W, float *y, int T, int I, int O);
@@ -70,8 +80,9 @@ int sw_launch_q8_rows(const SwLaunchCfg &c, const float *x, const int8_t *W, con
                       float *y, int T, int I, int O);
 // out/routed combine.  mode bits: 1 = multiply by route_scale, 2 = add `add` rows
 // (shared expert output), 4 = accumulate into out (else overwrite).
+// `add` holds add_slices consecutive [T,D] arrays that are summed in order.
 int sw_launch_combine(const SwLaunchCfg &c, const float *slots, const int *rowof, const int *sel,
-                      const float *w, const float *add, float *out, int T, int K, int D,
+                      const float *w, const float *add, int add_slices, float *out, int T, int K, int D,
                       float route_scale, int mode, int expert_lo, int expert_cnt);
-int sw_launch_finish(const SwLaunchCfg &c, const float *routed, const float *add, float *out,
+int sw_launch_finish(const SwLaunchCfg &c, const float *routed, const float *add, int add_slices, float *out,
                      int T, int D, float route_scale, int has_add);

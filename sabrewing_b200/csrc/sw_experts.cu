@@ -306,7 +306,7 @@ int sw_launch_q8_rows(const SwLaunchCfg &c, const float *x, const int8_t *W, con
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const int *__restrict__ sel,
-          const float *__restrict__ w, const float *__restrict__ add, float *__restrict__ out,
+          const float *__restrict__ w, const float *__restrict__ add, int add_slices, float *__restrict__ out,
           int T, int K, int D, float route_scale, int mode, int expert_lo, int expert_cnt) {
     const int D4 = D >> 2;
     const size_t n = (size_t)T * D4;
@@ -323,7 +323,11 @@ k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const 
         }
         if (mode & 1) { acc.x *= route_scale; acc.y *= route_scale; acc.z *= route_scale; acc.w *= route_scale; }
         if (mode & 2) {
-            const float4 s = reinterpret_cast<const float4 *>(add)[idx];
+            float4 s = reinterpret_cast<const float4 *>(add)[idx];
+            for (int k = 1; k < add_slices; k++) {
+                const float4 s2 = reinterpret_cast<const float4 *>(add)[(size_t)k * n + idx];
+                s.x += s2.x; s.y += s2.y; s.z += s2.z; s.w += s2.w;
+            }
             acc.x += s.x; acc.y += s.y; acc.z += s.z; acc.w += s.w;
         }
         float4 *o = reinterpret_cast<float4 *>(out) + idx;
@@ -333,39 +337,46 @@ k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const 
 }
 
 int sw_launch_combine(const SwLaunchCfg &c, const float *slots, const int *rowof, const int *sel,
-                      const float *w, const float *add, float *out, int T, int K, int D,
+                      const float *w, const float *add, int add_slices, float *out, int T, int K, int D,
                       float route_scale, int mode, int expert_lo, int expert_cnt) {
     if (T <= 0) return 0;
     if (D % 4) return -1;
     size_t n = (size_t)T * (D / 4);
     long long grid = (long long)((n + 255) / 256);
     if (grid > (long long)c.num_sms * 16) grid = (long long)c.num_sms * 16;
-    k_combine<<<(unsigned)grid, 256, 0, c.stream>>>(slots, rowof, sel, w, add, out, T, K, D, route_scale, mode, expert_lo, expert_cnt);
+    k_combine<<<(unsigned)grid, 256, 0, c.stream>>>(slots, rowof, sel, w, add, add_slices, out, T, K, D, route_scale, mode, expert_lo, expert_cnt);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 // out += routed*route_scale (+ add)
 __global__ void __launch_bounds__(256)
-k_finish(const float *__restrict__ routed, const float *__restrict__ add, float *__restrict__ out,
+k_finish(const float *__restrict__ routed, const float *__restrict__ add, int add_slices, float *__restrict__ out,
          size_t n4, float route_scale, int has_add) {
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n4; idx += (size_t)gridDim.x * blockDim.x) {
         float4 a = reinterpret_cast<const float4 *>(routed)[idx];
         a.x *= route_scale; a.y *= route_scale; a.z *= route_scale; a.w *= route_scale;
-        if (has_add) { float4 s = reinterpret_cast<const float4 *>(add)[idx]; a.x += s.x; a.y += s.y; a.z += s.z; a.w += s.w; }
+        if (has_add) {
+            float4 s = reinterpret_cast<const float4 *>(add)[idx];
+            for (int k = 1; k < add_slices; k++) {
+                const float4 s2 = reinterpret_cast<const float4 *>(add)[(size_t)k * n4 + idx];
+                s.x += s2.x; s.y += s2.y; s.z += s2.z; s.w += s2.w;
+            }
+            a.x += s.x; a.y += s.y; a.z += s.z; a.w += s.w;
+        }
         float4 h = reinterpret_cast<float4 *>(out)[idx];
         h.x += a.x; h.y += a.y; h.z += a.z; h.w += a.w;
         reinterpret_cast<float4 *>(out)[idx] = h;
     }
 }
-int sw_launch_finish(const SwLaunchCfg &c, const float *routed, const float *add, float *out,
+int sw_launch_finish(const SwLaunchCfg &c, const float *routed, const float *add, int add_slices, float *out,
                      int T, int D, float route_scale, int has_add) {
     if (T <= 0) return 0;
     if (D % 4) return -1;
     size_t n4 = (size_t)T * (D / 4);
     long long grid = (long long)((n4 + 255) / 256);
     if (grid > (long long)c.num_sms * 16) grid = (long long)c.num_sms * 16;
-    k_finish<<<(unsigned)grid, 256, 0, c.stream>>>(routed, add, out, n4, route_scale, has_add);
+    k_finish<<<(unsigned)grid, 256, 0, c.stream>>>(routed, add, add_slices, out, n4, route_scale, has_add);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -41,6 +41,13 @@
 #include <cuda_fp16.h>
 #include <stdlib.h>
 
+__device__ __forceinline__ uint4 sw_ldg_stream(const uint4 *p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+
 __device__ __forceinline__ void sw_mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                            uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -151,6 +158,72 @@ __device__ __forceinline__ void sw_cp_async16(unsigned smem_addr, const void *gm
 __device__ __forceinline__ void sw_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void sw_cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
 
+// One pass over the contraction for a warp item: streams the 2*MT weight rows
+// through the private ring and accumulates MT m-tiles against one n-tile.
+// M8: 8 token rows (separate hi and lo MMAs); else 4 rows with hi|lo side by side.
+template <int MT, int P, bool M8>
+__device__ __forceinline__ void sw_q4_kloop(float (&acc)[MT][4], const uint4 *my, unsigned my_s, const uint4 *wq,
+                                            const unsigned (&roff)[2 * MT], const uint4 *xb, int S) {
+    constexpr int STAGE = 2 * MT * 128;
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[mt][i] = 0.f;
+    // prologue: stages 0..P-2 (one commit per stage keeps the group count uniform)
+#pragma unroll
+    for (int p = 0; p < P - 1; p++) {
+        if (p < S) {
+#pragma unroll
+            for (int q = 0; q < 2 * MT; q++) sw_cp_async16(my_s + (unsigned)(p * STAGE + q * 128) * 16u, wq + roff[q] + p * 4);
+        }
+        sw_cp_async_commit();
+    }
+    int sc = 0, sf = P - 1;                           // ring slot consumed / filled next
+    for (int s = 0; s < S; s++) {
+        if (s + P - 1 < S) {
+#pragma unroll
+            for (int q = 0; q < 2 * MT; q++) sw_cp_async16(my_s + (unsigned)(sf * STAGE + q * 128) * 16u, wq + roff[q] + (s + P - 1) * 4);
+        }
+        sw_cp_async_commit();
+        sw_cp_async_wait<P - 1>();                    // stage s has landed
+        uint4 wv[2 * MT];
+#pragma unroll
+        for (int q = 0; q < 2 * MT; q++) wv[q] = my[sc * STAGE + q * 128];
+        sc = sc + 1 == P ? 0 : sc + 1;
+        sf = sf + 1 == P ? 0 : sf + 1;
+
+        float part[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) part[mt][i] = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < 4; wi++) {
+            const uint4 *bp = xb + (s * 4 + wi) * 8;
+            const uint4 b0 = __ldg(bp);
+            uint4 b1;
+            if (M8) b1 = __ldg(bp + 1);
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                uint32_t ga[4], ua[4];
+                sw_dq4(sw_word(wv[2 * mt], wi), ga);
+                sw_dq4(sw_word(wv[2 * mt + 1], wi), ua);
+                sw_mma_f16(part[mt], ga[0], ua[0], ga[1], ua[1], b0.x, b0.y);
+                sw_mma_f16(part[mt], ga[2], ua[2], ga[3], ua[3], b0.z, b0.w);
+                if (M8) {
+                    sw_mma_f16(part[mt], ga[0], ua[0], ga[1], ua[1], b1.x, b1.y);
+                    sw_mma_f16(part[mt], ga[2], ua[2], ga[3], ua[3], b1.z, b1.w);
+                }
+            }
+        }
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[mt][i] += part[mt][i];
+    }
+    sw_cp_async_wait<0>();
+}
+
 template <bool GATEUP, int MT, int P>
 __global__ void __launch_bounds__(128, (MT == 4 ? 3 : 4))
 k_q4_mma(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
@@ -202,64 +275,8 @@ k_q4_mma(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
             const uint4 *xb = XP + (size_t)rowid * xrow_u4 + (size_t)t * 2 + ((!m8 && g >= 4) ? 1 : 0);
 
             float acc[MT][4];
-#pragma unroll
-            for (int mt = 0; mt < MT; mt++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) acc[mt][i] = 0.f;
-
-            // prologue: stages 0..P-2 (one commit per stage keeps the group count uniform)
-#pragma unroll
-            for (int p = 0; p < P - 1; p++) {
-                if (p < S) {
-#pragma unroll
-                    for (int q = 0; q < 2 * MT; q++) sw_cp_async16(my_s + (unsigned)(p * STAGE + q * 128) * 16u, wq + roff[q] + p * 4);
-                }
-                sw_cp_async_commit();
-            }
-            int sc = 0, sf = P - 1;                           // ring slot consumed / filled next
-            for (int s = 0; s < S; s++) {
-                if (s + P - 1 < S) {
-#pragma unroll
-                    for (int q = 0; q < 2 * MT; q++) sw_cp_async16(my_s + (unsigned)(sf * STAGE + q * 128) * 16u, wq + roff[q] + (s + P - 1) * 4);
-                }
-                sw_cp_async_commit();
-                sw_cp_async_wait<P - 1>();                    // stage s has landed
-                uint4 wv[2 * MT];
-#pragma unroll
-                for (int q = 0; q < 2 * MT; q++) wv[q] = my[sc * STAGE + q * 128];
-                sc = sc + 1 == P ? 0 : sc + 1;
-                sf = sf + 1 == P ? 0 : sf + 1;
-
-                float part[MT][4];
-#pragma unroll
-                for (int mt = 0; mt < MT; mt++)
-#pragma unroll
-                    for (int i = 0; i < 4; i++) part[mt][i] = 0.f;
-#pragma unroll
-                for (int wi = 0; wi < 4; wi++) {
-                    const uint4 *bp = xb + (size_t)((s * 4 + wi) * 4) * 2;
-                    const uint4 b0 = __ldg(bp);
-                    uint4 b1 = b0;
-                    if (m8) b1 = __ldg(bp + 1);
-#pragma unroll
-                    for (int mt = 0; mt < MT; mt++) {
-                        uint32_t ga[4], ua[4];
-                        sw_dq4(sw_word(wv[2 * mt], wi), ga);
-                        sw_dq4(sw_word(wv[2 * mt + 1], wi), ua);
-                        sw_mma_f16(part[mt], ga[0], ua[0], ga[1], ua[1], b0.x, b0.y);
-                        sw_mma_f16(part[mt], ga[2], ua[2], ga[3], ua[3], b0.z, b0.w);
-                        if (m8) {
-                            sw_mma_f16(part[mt], ga[0], ua[0], ga[1], ua[1], b1.x, b1.y);
-                            sw_mma_f16(part[mt], ga[2], ua[2], ga[3], ua[3], b1.z, b1.w);
-                        }
-                    }
-                }
-#pragma unroll
-                for (int mt = 0; mt < MT; mt++)
-#pragma unroll
-                    for (int i = 0; i < 4; i++) acc[mt][i] += part[mt][i];
-            }
-            sw_cp_async_wait<0>();
+            if (m8) sw_q4_kloop<MT, P, true>(acc, my, my_s, wq, roff, xb, S);
+            else    sw_q4_kloop<MT, P, false>(acc, my, my_s, wq, roff, xb, S);
 
             // In 4-row mode columns j and j+4 hold the hi and lo parts of one token: fold them.
             if (!m8) {
@@ -380,4 +397,219 @@ int sw_launch_q4_mma(const SwLaunchCfg &c, const SwQ4Args &a, const SwMmaIO &io,
     if (a.KD % 128 || a.OUT <= 0) return -1;
     if (gateup) return mt == 4 ? sw_launch_q4_mma_t<true, 4, 4>(c, a, io) : mt == 2 ? sw_launch_q4_mma_t<true, 2, 6>(c, a, io) : sw_launch_q4_mma_t<true, 1, 12>(c, a, io);
     return mt == 4 ? sw_launch_q4_mma_t<false, 4, 4>(c, a, io) : mt == 2 ? sw_launch_q4_mma_t<false, 2, 6>(c, a, io) : sw_launch_q4_mma_t<false, 1, 12>(c, a, io);
+}
+
+// ===========================================================================
+// bf16 shared expert on the tensor cores.
+//
+// Weights are bf16 and go into the A fragments as they are (a thread's 16
+// bytes of a row are 8 consecutive columns = the k-slots of two MMAs), the
+// activations are split into two bf16 terms (x = hi + lo to 16 bits) stored
+// row-major as 32-byte chunks [8 hi | 8 lo] per 8 columns.  Rows g / g+8 of an
+// m-tile are gate row i and up row i (SiLU(gate)*up is thread-local) or two
+// output rows of the down projection.  Up to 32 token rows per pass.
+// Reference contract: matmul_bf16_k round_x=0 (c/moe_matmul.h:92-111) and
+// lag_shared (c/laguna.c:596-602).
+// ===========================================================================
+__device__ __forceinline__ void sw_mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                            uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void sw_split_bf16(float v, __nv_bfloat16 &hi, __nv_bfloat16 &lo) {
+    hi = __float2bfloat16_rn(v);
+    lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
+
+// x[rows, KD] f32 -> rows of KD/8 chunks [8 bf16 hi | 8 bf16 lo]
+__global__ void __launch_bounds__(256)
+k_pack_bf16(const float *__restrict__ x, uint4 *__restrict__ xp, int rows, int KD) {
+    const int cpr = KD >> 3;
+    const size_t n = (size_t)rows * cpr;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+        const float4 *src = reinterpret_cast<const float4 *>(x) + idx * 2;
+        const float4 a = src[0], b = src[1];
+        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        __nv_bfloat16 hi[8], lo[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) sw_split_bf16(v[i], hi[i], lo[i]);
+        xp[idx * 2] = *reinterpret_cast<uint4 *>(hi);
+        xp[idx * 2 + 1] = *reinterpret_cast<uint4 *>(lo);
+    }
+}
+
+int sw_launch_pack_bf16(const SwLaunchCfg &c, const float *x, void *xp, int rows, int KD) {
+    if (rows <= 0) return 0;
+    if (KD % 8) return -1;
+    size_t n = (size_t)rows * (KD / 8);
+    long long grid = (long long)((n + 255) / 256);
+    if (grid > (long long)c.num_sms * 8) grid = (long long)c.num_sms * 8;
+    k_pack_bf16<<<(unsigned)grid, 256, 0, c.stream>>>(x, (uint4 *)xp, rows, KD);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// KD % 32 == 0.  Warp item = (block of 16 weight rows, slice of the contraction);
+// the f32 partial sums of a slice go to Ypart[slice][token][OW] (OW = 2*O for
+// gate/up: gate at o, up at O+o; OW = O for down) and are added in slice order by
+// the consumer (k_shared_glu / the combine), which keeps every tensor-core
+// accumulation chain short and the result independent of scheduling.  The weight
+// rows stream through a per-thread cp.async ring like the int4 kernel.
+template <bool GATEUP, int P>
+__global__ void __launch_bounds__(128)
+k_bf16_mma(const __nv_bfloat16 *__restrict__ W0, const __nv_bfloat16 *__restrict__ W1,
+           const uint4 *__restrict__ XP, float *__restrict__ Ypart, int T, int KD, int O, int KS, int slice) {
+    extern __shared__ uint4 sw_ring[];                        // [P][2][128]
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int warps_total = gridDim.x * 4, wid = blockIdx.x * 4 + (threadIdx.x >> 5);
+    constexpr int OPI = GATEUP ? 8 : 16;
+    const int mblocks = (O + OPI - 1) / OPI;
+    const int items = mblocks * KS;
+    const size_t row_u4 = (size_t)(KD >> 3);                  // uint4 per weight row
+    const size_t xrow_u4 = (size_t)(KD >> 2);                 // uint4 per packed activation row
+    const int OW = GATEUP ? 2 * O : O;
+    constexpr int NTM = 4;                                    // n-tiles per pass
+    const uint4 *my = sw_ring + threadIdx.x;
+    const unsigned my_s = (unsigned)__cvta_generic_to_shared(sw_ring + threadIdx.x);
+
+    for (int item = wid; item < items; item += warps_total) {
+        const int ks = item % KS, mb = item / KS;
+        const int s0 = (ks * slice) >> 5, s1 = min(KD, (ks + 1) * slice) >> 5;   // 32-column steps [s0, s1)
+        const int S = s1 - s0;
+        const uint4 *pa, *pb;
+        if (GATEUP) {
+            const int o = min(mb * 8 + g, O - 1);
+            pa = reinterpret_cast<const uint4 *>(W0) + (size_t)o * row_u4 + t + (size_t)s0 * 4;
+            pb = reinterpret_cast<const uint4 *>(W1) + (size_t)o * row_u4 + t + (size_t)s0 * 4;
+        } else {
+            const int o = mb * 16 + g;
+            pa = reinterpret_cast<const uint4 *>(W0) + (size_t)min(o, O - 1) * row_u4 + t + (size_t)s0 * 4;
+            pb = reinterpret_cast<const uint4 *>(W0) + (size_t)min(o + 8, O - 1) * row_u4 + t + (size_t)s0 * 4;
+        }
+        for (int c0 = 0; c0 < T; c0 += 8 * NTM) {
+            const int nt_used = min(NTM, (T - c0 + 7) >> 3);  // warp-uniform
+            const uint4 *xb[NTM];
+#pragma unroll
+            for (int nt = 0; nt < NTM; nt++) xb[nt] = XP + (size_t)min(c0 + nt * 8 + g, T - 1) * xrow_u4 + (size_t)t * 2 + (size_t)s0 * 8;
+            float acc[NTM][4];
+#pragma unroll
+            for (int nt = 0; nt < NTM; nt++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) acc[nt][i] = 0.f;
+
+#pragma unroll
+            for (int p = 0; p < P - 1; p++) {
+                if (p < S) { sw_cp_async16(my_s + (unsigned)(p * 256) * 16u, pa + p * 4); sw_cp_async16(my_s + (unsigned)(p * 256 + 128) * 16u, pb + p * 4); }
+                sw_cp_async_commit();
+            }
+            int sc = 0, sf = P - 1;
+            for (int s = 0; s < S; s++) {
+                if (s + P - 1 < S) {
+                    sw_cp_async16(my_s + (unsigned)(sf * 256) * 16u, pa + (s + P - 1) * 4);
+                    sw_cp_async16(my_s + (unsigned)(sf * 256 + 128) * 16u, pb + (s + P - 1) * 4);
+                }
+                sw_cp_async_commit();
+                sw_cp_async_wait<P - 1>();
+                const uint4 wa = my[sc * 256], wb = my[sc * 256 + 128];
+                sc = sc + 1 == P ? 0 : sc + 1;
+                sf = sf + 1 == P ? 0 : sf + 1;
+#pragma unroll
+                for (int nt = 0; nt < NTM; nt++) {
+                    if (nt < nt_used) {
+                        const uint4 bh = __ldg(xb[nt] + (size_t)s * 8), bl = __ldg(xb[nt] + (size_t)s * 8 + 1);
+                        sw_mma_bf16(acc[nt], wa.x, wb.x, wa.y, wb.y, bh.x, bh.y);
+                        sw_mma_bf16(acc[nt], wa.z, wb.z, wa.w, wb.w, bh.z, bh.w);
+                        sw_mma_bf16(acc[nt], wa.x, wb.x, wa.y, wb.y, bl.x, bl.y);
+                        sw_mma_bf16(acc[nt], wa.z, wb.z, wa.w, wb.w, bl.z, bl.w);
+                    }
+                }
+            }
+            sw_cp_async_wait<0>();
+            // c[0],c[1] = (row g, tokens 2t,2t+1); c[2],c[3] = (row g+8, same tokens)
+            const int oa = GATEUP ? mb * 8 + g : mb * 16 + g;
+            const int ob = GATEUP ? O + oa : oa + 8;
+            const bool va = oa < O, vb = GATEUP ? va : ob < O;
+#pragma unroll
+            for (int nt = 0; nt < NTM; nt++) {
+                if (nt >= nt_used) continue;
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const int tok = c0 + nt * 8 + 2 * t + j;
+                    if (tok >= T) continue;
+                    float *row = Ypart + ((size_t)ks * T + tok) * OW;
+                    if (va) row[oa] = acc[nt][j];
+                    if (vb) row[ob] = acc[nt][2 + j];
+                }
+            }
+        }
+    }
+}
+
+// sglu packed rows [T, SI] (bf16 hi|lo chunks) = SiLU(sum_ks gate) * (sum_ks up)
+__global__ void __launch_bounds__(256)
+k_shared_glu(const float *__restrict__ part, int KS, int T, int SI, uint4 *__restrict__ out) {
+    const int cpr = SI >> 3;
+    const size_t n = (size_t)T * cpr;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+        const int tok = (int)(idx / cpr), c8 = (int)(idx - (size_t)tok * cpr);
+        float gv[8], uv[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) { gv[i] = 0.f; uv[i] = 0.f; }
+        for (int ks = 0; ks < KS; ks++) {
+            const float4 *pg = reinterpret_cast<const float4 *>(part + ((size_t)ks * T + tok) * (2 * (size_t)SI) + c8 * 8);
+            const float4 *pu = reinterpret_cast<const float4 *>(part + ((size_t)ks * T + tok) * (2 * (size_t)SI) + SI + c8 * 8);
+            const float4 a = pg[0], b = pg[1], c = pu[0], d = pu[1];
+            gv[0] += a.x; gv[1] += a.y; gv[2] += a.z; gv[3] += a.w; gv[4] += b.x; gv[5] += b.y; gv[6] += b.z; gv[7] += b.w;
+            uv[0] += c.x; uv[1] += c.y; uv[2] += c.z; uv[3] += c.w; uv[4] += d.x; uv[5] += d.y; uv[6] += d.z; uv[7] += d.w;
+        }
+        __nv_bfloat16 hi[8], lo[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) sw_split_bf16((gv[i] / (1.f + expf(-gv[i]))) * uv[i], hi[i], lo[i]);
+        out[idx * 2] = *reinterpret_cast<uint4 *>(hi);
+        out[idx * 2 + 1] = *reinterpret_cast<uint4 *>(lo);
+    }
+}
+
+// Slices of the contraction for a shared-expert product with `mblocks` row blocks.
+int sw_shared_slices(int num_sms, int mblocks, int KD) {
+    int want = (num_sms * 12 + mblocks - 1) / mblocks;
+    int maxs = KD / 256 > 0 ? KD / 256 : 1;
+    return want < 1 ? 1 : want > maxs ? maxs : want;
+}
+
+// Shared expert product: XP = packed rows (k_pack_bf16 / k_shared_glu); part = f32 [KS][T][OW].
+int sw_launch_bf16_mma(const SwLaunchCfg &c, const void *W0, const void *W1, const void *XP, float *part,
+                       int T, int KD, int O, int KS, bool gateup) {
+    if (T <= 0 || O <= 0) return 0;
+    if (KD % 32 || KS < 1) return -1;
+    constexpr int P = 8;
+    constexpr int SMEM = P * 2 * 128 * 16;
+    static bool attr = false;
+    if (!attr) {
+        if (cudaFuncSetAttribute(k_bf16_mma<true, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(k_bf16_mma<false, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
+        attr = true;
+    }
+    const int mblocks = (O + (gateup ? 8 : 16) - 1) / (gateup ? 8 : 16);
+    const int slice = ((KD + KS - 1) / KS + 31) & ~31;
+    long long items = (long long)mblocks * KS, need = (items + 3) / 4;
+    long long grid = (long long)c.num_sms * 4;
+    if (grid > need) grid = need;
+    if (gateup) k_bf16_mma<true, P><<<(unsigned)grid, 128, SMEM, c.stream>>>((const __nv_bfloat16 *)W0, (const __nv_bfloat16 *)W1, (const uint4 *)XP, part, T, KD, O, KS, slice);
+    else k_bf16_mma<false, P><<<(unsigned)grid, 128, SMEM, c.stream>>>((const __nv_bfloat16 *)W0, nullptr, (const uint4 *)XP, part, T, KD, O, KS, slice);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int sw_launch_shared_glu(const SwLaunchCfg &c, const float *part, int KS, int T, int SI, void *out) {
+    if (T <= 0) return 0;
+    if (SI % 8) return -1;
+    size_t n = (size_t)T * (SI / 8);
+    long long grid = (long long)((n + 255) / 256);
+    if (grid > (long long)c.num_sms * 8) grid = (long long)c.num_sms * 8;
+    k_shared_glu<<<(unsigned)grid, 256, 0, c.stream>>>(part, KS, T, SI, (uint4 *)out);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

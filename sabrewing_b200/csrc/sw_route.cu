@@ -82,6 +82,90 @@ int sw_launch_router_logits(const SwLaunchCfg &c, const float *x, const void *W,
 }
 
 // ---------------------------------------------------------------------------
+// Router logits on the fp64 tensor cores (mma.sync m8n8k4 f64).  Warp item =
+// (tile of 8 experts, pass of up to 32 token rows, slice of 256 columns); the
+// slices' partial sums go to part[slice][t][e] in fp64 and are added in a fixed
+// order by the top-k kernel before the single rounding to f32.  Lane (r, c) feeds
+// the k-slot c of step j with column 8c+j of the 32-column step, so both the
+// weight row (16 bytes of bf16 / 32 of f32) and the token row (32 bytes) are
+// contiguous loads.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void sw_dmma(double (&c)[2], double a, double b) {
+    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+                 : "+d"(c[0]), "+d"(c[1]) : "d"(a), "d"(b));
+}
+
+template <typename WT>
+__global__ void __launch_bounds__(128)
+k_router_dmma(const float *__restrict__ x, const WT *__restrict__ W, double *__restrict__ part,
+              int T, int D, int E, int KS, int slice) {
+    const int lane = threadIdx.x & 31, r = lane >> 2, c = lane & 3;
+    const int warps_total = gridDim.x * 4, wid = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int etiles = (E + 7) >> 3, passes = (T + 31) >> 5;
+    const int items = etiles * passes * KS;
+    for (int item = wid; item < items; item += warps_total) {
+        const int ks = item % KS, rest = item / KS, et = rest % etiles, ps = rest / etiles;
+        const int k0 = ks * slice, k1 = min(D, k0 + slice);
+        const int e = min(et * 8 + r, E - 1);
+        const WT *wr = W + (size_t)e * D + c * 8;
+        const float *xr[4];
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) xr[nt] = x + (size_t)min(ps * 32 + nt * 8 + r, T - 1) * D + c * 8;
+        const int nt_used = min(4, (T - ps * 32 + 7) >> 3);
+        double acc[4][2];
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) { acc[nt][0] = 0.0; acc[nt][1] = 0.0; }
+        for (int k = k0; k < k1; k += 32) {
+            float wv[8];
+            sw_load8(wr + k, wv);
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+                if (nt < nt_used) {
+                    float xv[8];
+                    sw_load8(xr[nt] + k, xv);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) sw_dmma(acc[nt], (double)wv[j], (double)xv[j]);
+                }
+            }
+        }
+        // C[row = expert r][col = token 2c, 2c+1]
+        const int eo = et * 8 + r;
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+            if (nt >= nt_used || eo >= E) continue;
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int t = ps * 32 + nt * 8 + 2 * c + j;
+                if (t < T) part[((size_t)ks * T + t) * E + eo] = acc[nt][j];
+            }
+        }
+    }
+}
+
+// Number of column slices the DMMA router uses for (T, E, D); the top-k kernel sums this many partials.
+int sw_router_slices(int num_sms, int T, int D, int E) {
+    const int etiles = (E + 7) / 8, passes = (T + 31) / 32;
+    int want = (num_sms * 16 + etiles * passes - 1) / (etiles * passes);
+    int maxs = (D + 255) / 256;
+    return want < 1 ? 1 : want > maxs ? maxs : want;
+}
+
+int sw_launch_router_dmma(const SwLaunchCfg &c, const float *x, const void *W, int w_dtype, double *part,
+                          int T, int D, int E, int KS) {
+    if (T <= 0) return 0;
+    if (D % 32) return -1;
+    const int etiles = (E + 7) / 8, passes = (T + 31) / 32;
+    int slice = ((D + KS - 1) / KS + 31) & ~31;
+    long long items = (long long)etiles * passes * KS, need = (items + 3) / 4;
+    long long grid = (long long)c.num_sms * 8;
+    if (grid > need) grid = need;
+    if (w_dtype == 1) k_router_dmma<__nv_bfloat16><<<(unsigned)grid, 128, 0, c.stream>>>(x, (const __nv_bfloat16 *)W, part, T, D, E, KS, slice);
+    else k_router_dmma<float><<<(unsigned)grid, 128, 0, c.stream>>>(x, (const float *)W, part, T, D, E, KS, slice);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// ---------------------------------------------------------------------------
 // Gate activation + top-k + combine weights: one warp per token.
 // exp/log1p are evaluated in fp64 and rounded to f32, which reproduces a
 // correctly rounded expf; every other operation is the reference's f32 sequence.
@@ -89,7 +173,8 @@ int sw_launch_router_logits(const SwLaunchCfg &c, const float *x, const void *W,
 __device__ __forceinline__ float sw_expf_cr(float v) { return (float)exp((double)v); }
 
 __global__ void __launch_bounds__(128)
-k_route_topk(float *__restrict__ scores, const float *__restrict__ corr_bias, int use_bias,
+k_route_topk(float *__restrict__ scores, const double *__restrict__ part, int KS, const float *__restrict__ lbias,
+             const float *__restrict__ corr_bias, int use_bias,
              int route_act, int norm_topk, int T, int E, int K,
              int *__restrict__ sel, float *__restrict__ w) {
     __shared__ float s_sc[4][SW_MAX_EXPERTS];
@@ -98,6 +183,16 @@ k_route_topk(float *__restrict__ scores, const float *__restrict__ corr_bias, in
     if (t >= T) return;
     float *r = scores + (size_t)t * E;
     float *sc = s_sc[warp];
+    if (part) {                                  // logits = (float)(sum of the fp64 slice partials) + bias
+        for (int e = lane; e < E; e += 32) {
+            double a = 0.0;
+            for (int ks = 0; ks < KS; ks++) a += part[((size_t)ks * T + t) * E + e];
+            float v = (float)a;
+            if (lbias) v += lbias[e];
+            r[e] = v;
+        }
+        __syncwarp();
+    }
 
     if (route_act == 1) {                        // softmax_row
         float m = -INFINITY;
@@ -160,11 +255,12 @@ k_route_topk(float *__restrict__ scores, const float *__restrict__ corr_bias, in
     if (lane < K) w[(size_t)t * K + lane] = wsel;
 }
 
-int sw_launch_route_topk(const SwLaunchCfg &c, float *scores, const float *corr_bias, int use_bias,
+int sw_launch_route_topk(const SwLaunchCfg &c, float *scores, const double *part, int KS, const float *lbias,
+                         const float *corr_bias, int use_bias,
                          int route_act, int norm_topk, int T, int E, int K, int *sel, float *w) {
     if (T <= 0) return 0;
     if (E > SW_MAX_EXPERTS || K > SW_MAX_TOPK || K > E || K <= 0) return -1;
-    k_route_topk<<<(T + 3) / 4, 128, 0, c.stream>>>(scores, corr_bias, use_bias, route_act, norm_topk, T, E, K, sel, w);
+    k_route_topk<<<(T + 3) / 4, 128, 0, c.stream>>>(scores, part, KS, lbias, corr_bias, use_bias, route_act, norm_topk, T, E, K, sel, w);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
