@@ -173,32 +173,62 @@ static void sw_resident(const SwMoeDesc *d, const SwMoeLayer *L, int *lo, int *c
     else { *lo = 0; *cnt = d->n_experts; }
 }
 
-// The tensor-core kernels need 128-column steps; other shapes (and SW_FORCE_SIMT=1)
-// take the CUDA-core f32 kernels.
-static bool sw_use_mma(int D, int I) {
-    static int force_simt = -1;
-    if (force_simt < 0) { const char *e = getenv("SW_FORCE_SIMT"); force_simt = (e && *e && *e != '0') ? 1 : 0; }
-    return !force_simt && D % 128 == 0 && I % 128 == 0;
-}
-
 // gate/up then down for the groups in `a` (a.q/a.s/a.X/a.Y/KD/OUT are filled here).
 // x: f32 rows; xp: scratch for the packed copy of x (rows_x rows); glu: scratch
 // [max_rows, I] (f32 or packed, same size); slots: [max_rows, D] f32.
+// Expert path: 2 = TMA-staged tensor-core kernels (default when the driver exports the
+// tensor-map encoder), 1 = cp.async tensor-core kernels, 0 = CUDA-core f32 kernels.
+// SW_EXPERT_PATH=tma|mma|simt overrides.
+static int sw_expert_path(int D, int I) {
+    static int pref = -1;
+    if (pref < 0) {
+        const char *e = getenv("SW_EXPERT_PATH");
+        pref = 2;
+        if (e && !strcmp(e, "mma")) pref = 1;
+        if (e && !strcmp(e, "simt")) pref = 0;
+        const char *f = getenv("SW_FORCE_SIMT");
+        if (f && *f && *f != '0') pref = 0;
+    }
+    if (pref == 0 || D % 128 || I % 128) return 0;
+    if (pref == 2 && !sw_tma_available()) return 1;
+    return pref;
+}
+
 static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, const float *gu_s,
                           const void *dn_q, const float *dn_s, const float *x, int rows_x, void *xp,
-                          float *glu, float *slots, float *sums, int D, int I, void (*mark)(void *, int), void *mark_ctx) {
-    if (sw_use_mma(D, I)) {
-        // sums: [rows_x] row sums of x, then [max_rows, I/8] partial row sums of the packed SiLU*up rows
+                          float *glu, float *slots, float *sums, int *status, int D, int I,
+                          void (*mark)(void *, int), void *mark_ctx) {
+    int path = sw_expert_path(D, I);
+    if (path == 2 && (((uintptr_t)gu_q | (uintptr_t)dn_q) & 15)) path = 1;    // TMA wants 16-byte aligned blobs
+    if (path > 0) {
+        // sums: [rows_x] row sums of x, then [max_rows, parts] partial row sums of the packed SiLU*up rows
         float *xsum = sums, *ypart = sums + ((rows_x + 63) & ~63);
         if (sw_launch_pack_act(cfg, x, xp, xsum, rows_x, D)) return -1;
+        const long long nexp = a.expert_cnt > 4096 ? 4096 : a.expert_cnt;   // bounds the tensor map when the caller gave no count
         a.q = (const uint8_t *)gu_q; a.s = gu_s; a.KD = D; a.OUT = I;
-        const int mt = sw_q4_mma_mt(cfg, a, true);
-        SwMmaIO io{xp, xsum, 1, glu, ypart};
-        if (sw_launch_q4_mma(cfg, a, io, true, mt)) return -1;
+        int parts;
+        if (path == 2) {
+            int mt = (long long)a.max_groups * ((I + 63) / 64) >= (long long)cfg.num_sms * 4 ? 2 : 1;
+            { const char *e = getenv("SW_TMA_MT"); if (e && (atoi(e) == 1 || atoi(e) == 2)) mt = atoi(e); }
+            SwMmaIO io{xp, xsum, 1, glu, ypart};
+            if (sw_launch_q4_tma(cfg, a, io, status, nexp * 2 * I, true, mt)) return -1;
+            parts = sw_q4_tma_parts(I, mt);
+        } else {
+            const int mt = sw_q4_mma_mt(cfg, a, true);
+            SwMmaIO io{xp, xsum, 1, glu, ypart};
+            if (sw_launch_q4_mma(cfg, a, io, true, mt)) return -1;
+            parts = I / (8 * mt);
+        }
         if (mark) mark(mark_ctx, 0);
         a.q = (const uint8_t *)dn_q; a.s = dn_s; a.KD = I; a.OUT = D;
-        SwMmaIO io2{glu, ypart, I / (8 * mt), slots, nullptr};
-        if (sw_launch_q4_mma(cfg, a, io2, false, sw_q4_mma_mt(cfg, a, false))) return -1;
+        SwMmaIO io2{glu, ypart, parts, slots, nullptr};
+        if (path == 2) {
+            int mt = (long long)a.max_groups * ((D + 127) / 128) >= (long long)cfg.num_sms * 4 ? 2 : 1;
+            { const char *e = getenv("SW_TMA_MT"); if (e && (atoi(e) == 1 || atoi(e) == 2)) mt = atoi(e); }
+            if (sw_launch_q4_tma(cfg, a, io2, status, nexp * D, false, mt)) return -1;
+        } else {
+            if (sw_launch_q4_mma(cfg, a, io2, false, sw_q4_mma_mt(cfg, a, false))) return -1;
+        }
         if (mark) mark(mark_ctx, 1);
         return 0;
     }
@@ -250,7 +280,7 @@ static int sw_expert_stage(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
     a.gexp = c->r.gexp; a.gbeg = c->r.gbeg; a.gcnt = c->r.gcnt; a.G = c->r.G; a.grow = c->r.grow;
     a.expert_lo = lo; a.expert_cnt = cnt;
     a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K;
-    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, L->D, L->I, nullptr, nullptr))
+    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, nullptr, nullptr))
         return sw_fail("expert launch failed");
     return 0;
 }
@@ -342,7 +372,7 @@ extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
     a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K;
     struct MarkCtx { SwMoeCtx *c; cudaStream_t st; } mc{c, st};
     auto mark = [](void *p, int which) { MarkCtx *m = (MarkCtx *)p; sw_prof_mark(m->c, which == 0 ? SW_ST_GATEUP : SW_ST_DOWN, m->st); };
-    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, L->D, L->I, mark, &mc))
+    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, mark, &mc))
         return sw_fail("expert launch failed");
     auto smark = [](void *p, int which) { MarkCtx *m = (MarkCtx *)p; sw_prof_mark(m->c, which == 0 ? SW_ST_SH_GATEUP : SW_ST_SH_DOWN, m->st); };
     float *so = nullptr; int so_slices = 1;
@@ -506,6 +536,7 @@ static int lag_stage_idx(LagIdx *d, const int *gexp, const int *gbeg, const int 
     size_t nint = 64 + (size_t)3 * G + 3 * (size_t)P, bytes = (nint + P) * 4;
     if (g_lag.didx.ensure(bytes) || g_lag.hidx.ensure(bytes)) return -1;
     int *h = (int *)g_lag.hidx.p;
+    for (int i = 0; i < 64; i++) h[i] = 0;
     h[0] = G;
     int *hp = h + 64;
     memcpy(hp, gexp, (size_t)G * 4); hp += G;
@@ -541,7 +572,7 @@ static int lag_group_core(float *acc, const float *x, const void *gu_q, const fl
         a.gexp = ix.gexp; a.gbeg = ix.gbeg; a.gcnt = ix.gcnt; a.G = ix.G; a.grow = ix.grow;
         a.expert_lo = 0; a.expert_cnt = 0x7fffffff; a.max_groups = G; a.max_rows = P;
         if (sw_run_experts(cfg, a, gu_q, gu_s, dn_q, dn_s, (const float *)g_lag.dx.p, S, g_lag.dxp.p,
-                           (float *)g_lag.dglu.p, (float *)g_lag.dslot.p, (float *)g_lag.dsums.p, D, I, nullptr, nullptr)) return -1;
+                           (float *)g_lag.dglu.p, (float *)g_lag.dslot.p, (float *)g_lag.dsums.p, ix.G + 32, D, I, nullptr, nullptr)) return -1;
         return sw_launch_combine(cfg, (const float *)g_lag.dslot.p, ix.rowof, ix.sel, ix.w, nullptr, 0, (float *)g_lag.dy.p,
                                  S, K, D, 1.f, 0, 0, 1);
     });

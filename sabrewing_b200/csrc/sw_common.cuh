@@ -11,6 +11,7 @@
 // Status bits written by kernels into SwRouting::status.
 #define SW_ST_BAD_EXPERT 1
 #define SW_ST_BAD_ROW    2
+#define SW_ST_TIMEOUT    4     // a bounded device-side wait ran out
 
 // Routing + dispatch arrays of one block call (device pointers).  Names follow
 // the reference's host arrays (c/laguna.c:709-723).
@@ -68,6 +69,10 @@ struct SwMmaIO {
 int sw_launch_pack_act(const SwLaunchCfg &c, const float *x, void *xp, float *rowsum, int rows, int KD);
 int sw_q4_mma_mt(const SwLaunchCfg &c, const SwQ4Args &a, bool gateup);
 int sw_launch_q4_mma(const SwLaunchCfg &c, const SwQ4Args &a, const SwMmaIO &io, bool gateup, int mt);
+// sw_tma.cu: TMA-staged variant of the int4 products
+bool sw_tma_available();
+int sw_q4_tma_parts(int OUT, int mt);
+int sw_launch_q4_tma(const SwLaunchCfg &c, const SwQ4Args &a, const SwMmaIO &io, int *status, long long rows_total, bool gateup, int mt);
 int sw_launch_pack_bf16(const SwLaunchCfg &c, const float *x, void *xp, int rows, int KD);
 int sw_shared_slices(int num_sms, int mblocks, int KD);
 int sw_launch_bf16_mma(const SwLaunchCfg &c, const void *W0, const void *W1, const void *XP, float *part,
