@@ -51,6 +51,8 @@ struct SwMoeCtx {
     int dev = 0, num_sms = 0;
     int maxT = 0, maxE = 0, maxK = 0, maxD = 0, maxI = 0, maxSI = 0;
     cudaStream_t stream = nullptr, last_stream = nullptr;
+    cudaStream_t aux = nullptr;                 // the shared expert runs here, beside routing and the routed experts
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     SwRouting r{};
     float *glu = nullptr, *slots = nullptr, *sglu = nullptr, *so = nullptr, *routed = nullptr;
     float *dx = nullptr, *dout = nullptr, *hx = nullptr, *hout = nullptr;
@@ -92,7 +94,10 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) { delete c; return sw_cuda_fail(cudaGetLastError(), "cudaGetDeviceProperties"); }
     c->num_sms = prop.multiProcessorCount;
-    if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return sw_cuda_fail(cudaGetLastError(), "cudaStreamCreate"); }
+    if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&c->aux, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess) { delete c; return sw_cuda_fail(cudaGetLastError(), "cudaStreamCreate"); }
 
     const size_t T = max_tokens, E = max_experts, K = max_topk, D = max_D, I = max_I, SI = max_SI, P = T * K;
     size_t sizes[] = {
@@ -139,6 +144,9 @@ extern "C" void sw_moe_ctx_destroy(SwMoeCtx *c) {
     if (!c) return;
     cudaSetDevice(c->dev);
     if (c->stream) { cudaStreamSynchronize(c->stream); cudaStreamDestroy(c->stream); }
+    if (c->aux) { cudaStreamSynchronize(c->aux); cudaStreamDestroy(c->aux); }
+    if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+    if (c->ev_join) cudaEventDestroy(c->ev_join);
     if (c->block) cudaFree(c->block);
     if (c->hx) cudaFreeHost(c->hx);
     if (c->hout) cudaFreeHost(c->hout);
@@ -360,6 +368,20 @@ extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
     int lo, cnt; sw_resident(d, L, &lo, &cnt);
     const int has_shared = d->shared_mode != SW_SHARED_NONE;
 
+    struct MarkCtx { SwMoeCtx *c; cudaStream_t st; } mc{c, st};
+    auto smark = [](void *p, int which) { MarkCtx *m = (MarkCtx *)p; sw_prof_mark(m->c, which == 0 ? SW_ST_SH_GATEUP : SW_ST_SH_DOWN, m->st); };
+    float *so = nullptr; int so_slices = 1;
+    // The shared expert depends only on x: outside stage profiling it runs on the
+    // context's second stream, forked here and joined before the combine.
+    const bool overlap = has_shared && !c->prof_on;
+    if (overlap) {
+        SwLaunchCfg acfg{c->num_sms, c->aux};
+        SW_CUDA(cudaEventRecord(c->ev_fork, st));
+        SW_CUDA(cudaStreamWaitEvent(c->aux, c->ev_fork, 0));
+        if (sw_shared_run(acfg, L, x, T, c->spk, c->sglu, c->so, &so, &so_slices, nullptr, nullptr)) return sw_fail("shared expert launch failed");
+        SW_CUDA(cudaEventRecord(c->ev_join, c->aux));
+    }
+
     sw_prof_mark(c, -1, st);
     if (sw_logits_topk(c, cfg, d, L, x, T, true)) return -1;
     if (sw_launch_dispatch(cfg, c->r, T, K, E)) return sw_fail("dispatch launch failed");
@@ -370,13 +392,13 @@ extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
     a.gexp = c->r.gexp; a.gbeg = c->r.gbeg; a.gcnt = c->r.gcnt; a.G = c->r.G; a.grow = c->r.grow;
     a.expert_lo = lo; a.expert_cnt = cnt;
     a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K;
-    struct MarkCtx { SwMoeCtx *c; cudaStream_t st; } mc{c, st};
     auto mark = [](void *p, int which) { MarkCtx *m = (MarkCtx *)p; sw_prof_mark(m->c, which == 0 ? SW_ST_GATEUP : SW_ST_DOWN, m->st); };
     if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, mark, &mc))
         return sw_fail("expert launch failed");
-    auto smark = [](void *p, int which) { MarkCtx *m = (MarkCtx *)p; sw_prof_mark(m->c, which == 0 ? SW_ST_SH_GATEUP : SW_ST_SH_DOWN, m->st); };
-    float *so = nullptr; int so_slices = 1;
-    if (has_shared) {
+    if (overlap) {
+        SW_CUDA(cudaStreamWaitEvent(st, c->ev_join, 0));
+        sw_prof_mark(c, SW_ST_SH_GATEUP, st); sw_prof_mark(c, SW_ST_SH_DOWN, st);
+    } else if (has_shared) {
         if (sw_shared_run(cfg, L, x, T, c->spk, c->sglu, c->so, &so, &so_slices, smark, &mc)) return sw_fail("shared expert launch failed");
     } else {
         sw_prof_mark(c, SW_ST_SH_GATEUP, st); sw_prof_mark(c, SW_ST_SH_DOWN, st);

@@ -172,54 +172,76 @@ int sw_launch_router_dmma(const SwLaunchCfg &c, const float *x, const void *W, i
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float sw_expf_cr(float v) { return (float)exp((double)v); }
 
-__global__ void __launch_bounds__(128)
+// One CTA of 256 threads per token.  Phase 1 (all threads, one expert each per
+// pass): logits from the fp64 slice partials (or as given), gate activation,
+// score and score+bias into shared memory.  Phase 2 (warp 0): the K selection
+// rounds over shared memory and the combine weights.
+__global__ void __launch_bounds__(256)
 k_route_topk(float *__restrict__ scores, const double *__restrict__ part, int KS, const float *__restrict__ lbias,
              const float *__restrict__ corr_bias, int use_bias,
              int route_act, int norm_topk, int T, int E, int K,
              int *__restrict__ sel, float *__restrict__ w) {
-    __shared__ float s_sc[4][SW_MAX_EXPERTS];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + warp;
-    if (t >= T) return;
+    __shared__ float s_sc[SW_MAX_EXPERTS], s_sb[SW_MAX_EXPERTS];
+    __shared__ float s_redf[8];
+    __shared__ double s_redd[8];
+    const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     float *r = scores + (size_t)t * E;
-    float *sc = s_sc[warp];
-    if (part) {                                  // logits = (float)(sum of the fp64 slice partials) + bias
-        for (int e = lane; e < E; e += 32) {
+    const bool ub = use_bias && corr_bias != nullptr;
+
+    // logits
+    for (int e = tid; e < E; e += 256) {
+        float v;
+        if (part) {
             double a = 0.0;
             for (int ks = 0; ks < KS; ks++) a += part[((size_t)ks * T + t) * E + e];
-            float v = (float)a;
+            v = (float)a;
             if (lbias) v += lbias[e];
-            r[e] = v;
-        }
-        __syncwarp();
+        } else v = r[e];
+        s_sc[e] = v;
     }
+    __syncthreads();
 
-    if (route_act == 1) {                        // softmax_row
+    if (route_act == 1) {                        // softmax_row: float max, exp, double sum in index order per thread, 1/sum
         float m = -INFINITY;
-        for (int e = lane; e < E; e += 32) { float v = r[e]; if (v > m) m = v; }
+        for (int e = tid; e < E; e += 256) { float v = s_sc[e]; if (v > m) m = v; }
 #pragma unroll
         for (int off = 16; off; off >>= 1) { float o = __shfl_xor_sync(SW_FULL_MASK, m, off); if (o > m) m = o; }
-        float r0 = r[0];
-        if (r0 != r0) m = r0;                    // the reference's max starts from x[0]: a NaN there sticks
-        double s = 0.0;
-        for (int e = lane; e < E; e += 32) { float v = sw_expf_cr(r[e] - m); sc[e] = v; s += (double)v; }
+        if (lane == 0) s_redf[warp] = m;
+        __syncthreads();
+        m = s_redf[0];
 #pragma unroll
-        for (int off = 16; off; off >>= 1) s += __shfl_xor_sync(SW_FULL_MASK, s, off);
-        float inv = (float)(1.0 / s);
-        for (int e = lane; e < E; e += 32) sc[e] *= inv;
+        for (int i = 1; i < 8; i++) if (s_redf[i] > m) m = s_redf[i];
+        const float r0 = s_sc[0];
+        if (r0 != r0) m = r0;                    // the reference's max starts from x[0]: a NaN there sticks
+        double sum = 0.0;
+        for (int e = tid; e < E; e += 256) { float v = sw_expf_cr(s_sc[e] - m); s_sb[e] = v; sum += (double)v; }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) sum += __shfl_xor_sync(SW_FULL_MASK, sum, off);
+        if (lane == 0) s_redd[warp] = sum;
+        __syncthreads();
+        sum = 0.0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) sum += s_redd[i];
+        const float inv = (float)(1.0 / sum);
+        for (int e = tid; e < E; e += 256) s_sc[e] = s_sb[e] * inv;
     } else if (route_act == 0) {                 // sigmoid
-        for (int e = lane; e < E; e += 32) sc[e] = 1.f / (1.f + sw_expf_cr(-r[e]));
+        for (int e = tid; e < E; e += 256) s_sc[e] = 1.f / (1.f + sw_expf_cr(-s_sc[e]));
     } else {                                     // softplus
-        for (int e = lane; e < E; e += 32) {
-            float v = r[e];
-            sc[e] = v > 20.f ? v : (float)log1p((double)sw_expf_cr(v));
+        for (int e = tid; e < E; e += 256) {
+            const float v = s_sc[e];
+            s_sc[e] = v > 20.f ? v : (float)log1p((double)sw_expf_cr(v));
         }
     }
-    __syncwarp();
-    for (int e = lane; e < E; e += 32) r[e] = sc[e];     // keep the scores for inspection
+    __syncthreads();
+    for (int e = tid; e < E; e += 256) {
+        const float sc = s_sc[e];
+        r[e] = sc;                               // keep the scores for inspection
+        s_sb[e] = sc + (ub ? corr_bias[e] : 0.f);
+    }
+    __syncthreads();
+    if (warp != 0) return;
 
-    // K rounds of arg-max over score (+bias), strict >, ties to the lower id.
-    const bool ub = use_bias && corr_bias != nullptr;
+    // K rounds of arg-max over score+bias, strict >, ties to the lower id.
     uint32_t used = 0;                           // bit j: this lane's element lane+32j is taken
     float wsel = 0.f;                            // lane a keeps weight of rank a
     for (int a = 0; a < K; a++) {
@@ -227,7 +249,7 @@ k_route_topk(float *__restrict__ scores, const double *__restrict__ part, int KS
         int j = 0;
         for (int e = lane; e < E; e += 32, j++) {
             if (used & (1u << j)) continue;
-            float s = sc[e] + (ub ? corr_bias[e] : 0.f);
+            const float s = s_sb[e];
             if (s > bv) { bv = s; best = e; }
         }
 #pragma unroll
@@ -244,7 +266,7 @@ k_route_topk(float *__restrict__ scores, const double *__restrict__ part, int KS
             best = cand == 0x7fffffff ? 0 : cand;
         }
         if ((best & 31) == lane) used |= 1u << (best >> 5);
-        if (lane == a) wsel = sc[best];
+        if (lane == a) wsel = s_sc[best];
         if (lane == 0) sel[(size_t)t * K + a] = best;
     }
     if (norm_topk) {                             // float sum in rank order, then divide
@@ -260,7 +282,7 @@ int sw_launch_route_topk(const SwLaunchCfg &c, float *scores, const double *part
                          int route_act, int norm_topk, int T, int E, int K, int *sel, float *w) {
     if (T <= 0) return 0;
     if (E > SW_MAX_EXPERTS || K > SW_MAX_TOPK || K > E || K <= 0) return -1;
-    k_route_topk<<<(T + 3) / 4, 128, 0, c.stream>>>(scores, part, KS, lbias, corr_bias, use_bias, route_act, norm_topk, T, E, K, sel, w);
+    k_route_topk<<<T, 256, 0, c.stream>>>(scores, part, KS, lbias, corr_bias, use_bias, route_act, norm_topk, T, E, K, sel, w);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
