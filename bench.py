@@ -37,6 +37,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=4, help="resident layers the steps cycle over")
     ap.add_argument("--cpu-reps", type=int, default=12)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch the kernels of every step one by one instead of replaying CUDA graphs")
     return ap.parse_args()
 
 
@@ -213,10 +214,24 @@ def run_ours(args):
     block = MoeBlock(dev, T * world, cfg.E, cfg.K, cfg.D, cfg.I, cfg.SI)
     ep = ExpertParallelMoe(block, desc) if world > 1 else None
 
-    def step(i):
-        layer, x, out = layers[i % len(layers)], xs[i % NB], outs[i % NB]
+    # one captured CUDA graph per (layer, batch) pair the steps cycle over (single GPU)
+    graphs = {}
+    if ep is None and not args.no_graph:
+        for li in range(len(layers)):
+            for bi in range(NB):
+                if (li - bi) % np.gcd(len(layers), NB) == 0:     # only the pairs (i % L, i % NB) that occur
+                    graphs[(li, bi)] = block.graph(desc, layers[li], xs[bi], outs[bi])
+        torch.cuda.synchronize()
+
+    def step(i, use_graph=True):
+        li, bi = i % len(layers), i % NB
+        layer, x, out = layers[li], xs[bi], outs[bi]
         if ep is None:
-            block.forward(desc, layer, x, out)
+            g = graphs.get((li, bi)) if use_graph else None
+            if g is not None:
+                g.replay()
+            else:
+                block.forward(desc, layer, x, out)
         else:
             ep.forward(layer, x, out)
 
@@ -252,14 +267,15 @@ def run_ours(args):
             "config": {"workload": workload_name(cfg, T, world), "global_batch": T * world, "layers_cycled": len(layers),
                        "l2": "inputs larger than L2: steps cycle over %d layers (%.2f GB of expert blobs each per GPU) and %d token batches"
                              % (len(layers), layers[0].expert_bytes() / 1e9, NB),
-                       "parallelism": "ep%d" % world if world > 1 else "single"},
+                       "parallelism": "ep%d" % world if world > 1 else "single",
+                       "launch": "cuda graph replay per step" if graphs else "one launch per kernel"},
             "clocks": clocks, "gpu_launches": int(launches)}
 
     # ---- roofline of the dominant kernel: per-stage CUDA events over the same steps (1 GPU) ----
     if world == 1:
         block.profile(True)
         for i in range(min(args.steps, 500)):
-            step(i)
+            step(i, use_graph=False)
         torch.cuda.synchronize()
         stage_ms, calls = block.profile_read()
         block.profile(False)

@@ -130,6 +130,16 @@ int  sw_moe_forward(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *laye
 int  sw_moe_forward_host(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer,
                          const float *x_host, float *out_host, int T);
 
+/* CUDA-graph replay of sw_moe_forward for fixed (desc, layer, x, out, T): create
+ * runs the block once eagerly (out is updated by that call too), captures a second
+ * call and instantiates it; launch replays it on `stream`.  The context's scratch
+ * is shared, so replays of graphs of one context must not overlap on the GPU. */
+typedef struct SwMoeGraph SwMoeGraph;
+int  sw_moe_graph_create(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer,
+                         const float *x, float *out, int T, SwMoeGraph **graph);
+int  sw_moe_graph_launch(SwMoeGraph *graph, void *stream);
+void sw_moe_graph_destroy(SwMoeGraph *graph);
+
 /* Stages, for expert-parallel drivers and for parity checks.  route: router
  * logits -> gate -> top-k -> weights -> group-by-expert, results kept in ctx.
  * experts: routed[T,D] = sum over resident experts of w*expert (unscaled, rank

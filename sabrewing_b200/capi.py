@@ -48,6 +48,9 @@ SIGNATURES = {
     "sw_moe_ctx_destroy": (None, [_vp]),
     "sw_moe_forward": (_i, [_vp, _pd, _pl, _vp, _vp, _i, _vp]),
     "sw_moe_forward_host": (_i, [_vp, _pd, _pl, _vp, _vp, _i]),
+    "sw_moe_graph_create": (_i, [_vp, _pd, _pl, _vp, _vp, _i, C.POINTER(_vp)]),
+    "sw_moe_graph_launch": (_i, [_vp, _vp]),
+    "sw_moe_graph_destroy": (None, [_vp]),
     "sw_moe_route": (_i, [_vp, _pd, _pl, _vp, _i, _vp]),
     "sw_moe_experts": (_i, [_vp, _pd, _pl, _vp, _vp, _i, _vp]),
     "sw_moe_finish": (_i, [_vp, _pd, _pl, _vp, _vp, _vp, _i, _vp]),

@@ -425,6 +425,52 @@ extern "C" int sw_moe_forward_host(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeL
     return 0;
 }
 
+// ---------------------------------------------------------------------------
+// CUDA-graph replay of one block call: the launches of sw_moe_forward for fixed
+// (desc, layer, x, out, T) are captured once and replayed with one graph launch.
+// ---------------------------------------------------------------------------
+struct SwMoeGraph { cudaGraph_t graph; cudaGraphExec_t exec; SwMoeCtx *ctx; int T, K, E; int kernels; };
+
+extern "C" int sw_moe_graph_create(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, float *out, int T,
+                                   SwMoeGraph **gout) {
+    if (!gout) return sw_fail("graph_create: null out");
+    *gout = nullptr;
+    if (sw_check(c, d, L, T)) return -1;
+    if (T == 0) return sw_fail("graph_create: empty batch");
+    const int prof = c->prof_on; c->prof_on = 0;
+    // one eager call first: function attributes, occupancy queries and tensor maps are set up outside capture
+    if (sw_moe_forward(c, d, L, x, out, T, c->stream)) { c->prof_on = prof; return -1; }
+    SW_CUDA(cudaStreamSynchronize(c->stream));
+    cudaGraph_t graph = nullptr;
+    if (cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { c->prof_on = prof; return sw_cuda_fail(cudaGetLastError(), "cudaStreamBeginCapture"); }
+    const long long l0 = g_launches;
+    const int rc = sw_moe_forward(c, d, L, x, out, T, c->stream);
+    const int kernels = (int)(g_launches - l0);
+    g_launches = l0;                                   // captured, not launched
+    cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+    c->prof_on = prof;
+    if (rc || e != cudaSuccess || !graph) { cudaGetLastError(); if (graph) cudaGraphDestroy(graph); return rc ? -1 : sw_fail("graph capture failed: %s", cudaGetErrorString(e)); }
+    cudaGraphExec_t exec = nullptr;
+    if (cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) { cudaGetLastError(); cudaGraphDestroy(graph); return sw_fail("cudaGraphInstantiate failed"); }
+    SwMoeGraph *g = new SwMoeGraph{graph, exec, c, T, d->topk, d->n_experts, kernels};
+    *gout = g;
+    return 0;
+}
+
+extern "C" int sw_moe_graph_launch(SwMoeGraph *g, void *stream) {
+    if (!g) return sw_fail("graph_launch: null graph");
+    SW_CUDA(cudaGraphLaunch(g->exec, (cudaStream_t)stream));
+    g->ctx->last_stream = (cudaStream_t)stream; g->ctx->lastT = g->T; g->ctx->lastK = g->K; g->ctx->lastE = g->E;
+    sw_count_launch(g->kernels);
+    return 0;
+}
+
+extern "C" void sw_moe_graph_destroy(SwMoeGraph *g) {
+    if (!g) return;
+    cudaGraphExecDestroy(g->exec); cudaGraphDestroy(g->graph);
+    delete g;
+}
+
 extern "C" int sw_moe_get_routing(SwMoeCtx *c, int *sel, float *w, float *scores, int *G,
                                   int *gexp, int *gbeg, int *gcnt, int *grow, int *rowof) {
     if (!c) return sw_fail("null ctx");

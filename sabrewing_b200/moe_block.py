@@ -86,6 +86,23 @@ class MoeLayer:
         return sum(t.numel() * t.element_size() for t in (self.gu_q, self.gu_s, self.dn_q, self.dn_s))
 
 
+class MoeGraph:
+    """A captured block call; replay() launches it on a stream."""
+
+    def __init__(self, block, handle, last, keep):
+        self.block, self.handle, self._last, self._keep = block, handle, last, keep
+
+    def replay(self, stream=None):
+        b = self.block
+        b._last = self._last
+        b._chk(b.lib.sw_moe_graph_launch(self.handle, b._stream(stream)), "sw_moe_graph_launch")
+
+    def close(self):
+        if self.handle:
+            self.block.lib.sw_moe_graph_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+
 class MoeBlock:
     """One scratch context; run any layer whose sizes fit the limits given here."""
 
@@ -130,6 +147,14 @@ class MoeBlock:
         self._chk(self.lib.sw_moe_forward(self.ctx, C.byref(d), C.byref(l), x.data_ptr(), out.data_ptr(), T,
                                           self._stream(stream)), "sw_moe_forward")
         return out
+
+    def graph(self, desc, layer, x, out):
+        """Capture forward(desc, layer, x, out) into a CUDA graph (runs the block twice on `out` while doing so)."""
+        d, l = desc.c(), layer.c()
+        g = C.c_void_p()
+        self._chk(self.lib.sw_moe_graph_create(self.ctx, C.byref(d), C.byref(l), x.data_ptr(), out.data_ptr(), x.shape[0],
+                                               C.byref(g)), "sw_moe_graph_create")
+        return MoeGraph(self, g, (x.shape[0], desc.topk, desc.n_experts), (layer, x, out))
 
     def forward_host(self, desc, layer, x_host, out_host):
         """Same through host numpy buffers (H2D, block, D2H, sync); out_host updated in place."""

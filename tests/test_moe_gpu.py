@@ -75,6 +75,23 @@ def test_scaled_configs(orc, base, kw, T):
     run_case(case, orc)
 
 
+def test_graph_replay_matches_eager(orc):
+    case = synth_case("c2", D=512, E=64, K=6, I=128, SI=128, T=12)
+    blk, layer, desc = make_block(case)
+    x = torch.from_numpy(case.x).cuda()
+    eager = torch.from_numpy(case.hin).cuda(); blk.forward(desc, layer, x, eager)
+    out = torch.zeros_like(x)
+    g = blk.graph(desc, layer, x, out)          # runs the block twice on `out`
+    out.copy_(torch.from_numpy(case.hin).cuda())
+    l0 = blk.lib.sw_launch_count()
+    g.replay()
+    torch.cuda.synchronize()
+    assert blk.lib.sw_launch_count() - l0 >= 8   # the replay launched the block's kernels
+    assert torch.equal(out, eager)
+    check_routing(blk.routing(), orc.moe_group(case.host, case.x, None, exact=1))
+    g.close(); blk.close()
+
+
 def test_f32_router_weights(orc):
     from sabrewing_b200.moe_block import MoeBlock, MoeLayer, desc_from_config
     case = synth_case("c2", D=256, E=64, K=6, I=64, SI=64, T=19)
