@@ -151,6 +151,22 @@ int  sw_moe_experts(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *laye
 int  sw_moe_finish(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer,
                    const float *x, const float *routed, float *out, int T, void *stream);
 
+/* Routing without any allocation (no counterpart in the reference, which sizes its
+ * scratch with cudaMalloc on demand, c/backend_cuda_laguna.cu:471-493): router
+ * logits -> gate -> top-k -> combine weights for T <= 8 rows, n_experts <= 512,
+ * D <= 8192 (D % 32 == 0).  x [T,D] f32, sel [T*K] int32 and w [T*K] f32 are device
+ * buffers owned by the caller; the working memory is a fixed ~1.1 MB array inside
+ * the library image that every GPU loading the library keeps until exit.  Meant
+ * for hosts that cannot allocate when they need a routing decision (all free
+ * device memory already given away, or no tolerance for the device-wide
+ * synchronisation of an allocation).  Same ids and weights as sw_moe_route.  Sizes
+ * beyond the limits return -1 with an error text.  The array is shared by all
+ * calls on a GPU: calls that overlap on the device race, so order them.  The
+ * first call on each device looks up the array's device address; issue it outside
+ * any stream capture. */
+int  sw_moe_route_static(const SwMoeDesc *desc, const SwMoeLayer *layer, const float *x, int T,
+                         int *sel, float *w, void *stream);
+
 /* Copy the routing of the last sw_moe_route/forward to host arrays (any may be
  * NULL): sel,w [T*K]; scores [T*E]; *G; gexp,gbeg,gcnt [E]; grow,rowof [T*K] -- the
  * arrays of c/laguna.c:709-723.  Synchronises the stream used last. */

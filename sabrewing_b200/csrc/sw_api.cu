@@ -20,6 +20,7 @@ static int sw_fail(const char *fmt, ...) {
     return -1;
 }
 extern "C" const char *sw_last_error(void) { return g_err; }
+int sw_noalloc_fail(const char *msg) { return sw_fail("%s", msg); }
 
 // A CUDA error is sticky only for faults; plain API failures (OOM, bad argument)
 // are cleared so that the next call starts clean (the reference's hygiene rule,
