@@ -5,6 +5,7 @@
 #pragma GCC visibility push(default)
 #include "../../include/sabrewing_b200.h"
 #pragma GCC visibility pop
+#include <cuda_fp16.h>
 #include <stdio.h>
 #include <stdarg.h>
 #include <string.h>
@@ -45,6 +46,9 @@ struct SwBuf {
     void release() { if (p) { if (pinned) cudaFreeHost(p); else cudaFree(p); } p = nullptr; cap = 0; }
 };
 
+// scratch of the tcgen05 path: gathered fp16 hi/lo token rows [P, D] x2, chunk list
+struct SwUmmaScratch { void *xg; int *nchunks; void *chunks; };
+
 // ===========================================================================
 // Descriptor-level context
 // ===========================================================================
@@ -58,6 +62,7 @@ struct SwMoeCtx {
     float *glu = nullptr, *slots = nullptr, *sglu = nullptr, *so = nullptr, *routed = nullptr;
     float *dx = nullptr, *dout = nullptr, *hx = nullptr, *hout = nullptr;
     void *xp = nullptr;          // packed fp16 hi/lo copy of x for the tensor-core path
+    SwUmmaScratch um{nullptr, nullptr, nullptr};
     double *rpart = nullptr;     // fp64 partial router logits [slices][T][E]
     void *spk = nullptr;         // packed bf16 hi/lo copy of x for the shared expert
     float *sums = nullptr;       // row sums of x and partial row sums of the SiLU*up rows
@@ -117,6 +122,8 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
         T * D * 4,            // xp
         (T + 64) * 4 + P * (I / 8 + 1) * 4,  // sums
         T * D * 4,            // spk
+        P * D * 4,            // um.xg: gathered fp16 hi + lo token rows
+        (P / 128 + E + 64) * 8 + 256,   // um.chunks + nchunks
         ((size_t)((D + 255) / 256) * (T < 128 ? T : 128) + ((size_t)c->num_sms * 16 * 256 + E - 1) / E + T + 64) * E * 8   // rpart
     };
     size_t total = 0; for (size_t s : sizes) total += sw_align(s);
@@ -130,7 +137,7 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
     c->r.gexp = (int *)take(); c->r.gbeg = (int *)take(); c->r.gcnt = (int *)take();
     c->r.grow = (int *)take(); c->r.rowof = (int *)take(); c->r.status = (int *)take();
     c->glu = (float *)take(); c->slots = (float *)take(); c->sglu = (float *)take(); c->so = (float *)take();
-    c->routed = (float *)take(); c->dx = (float *)take(); c->dout = (float *)take(); c->xp = take(); c->sums = (float *)take(); c->spk = take(); c->rpart = (double *)take();
+    c->routed = (float *)take(); c->dx = (float *)take(); c->dout = (float *)take(); c->xp = take(); c->sums = (float *)take(); c->spk = take(); c->um.xg = take(); { char *q = (char *)take(); c->um.nchunks = (int *)q; c->um.chunks = q + 256; } c->rpart = (double *)take();
     cudaMemsetAsync(c->r.G, 0, 256, c->stream); cudaMemsetAsync(c->r.status, 0, 256, c->stream);
     if (cudaMallocHost((void **)&c->hx, T * D * 4) != cudaSuccess || cudaMallocHost((void **)&c->hout, T * D * 4) != cudaSuccess) {
         cudaGetLastError(); sw_moe_ctx_destroy(c);
@@ -188,27 +195,51 @@ static void sw_resident(const SwMoeDesc *d, const SwMoeLayer *L, int *lo, int *c
 // Expert path: 2 = TMA-staged tensor-core kernels (default when the driver exports the
 // tensor-map encoder), 1 = cp.async tensor-core kernels, 0 = CUDA-core f32 kernels.
 // SW_EXPERT_PATH=tma|mma|simt overrides.
-static int sw_expert_path(int D, int I) {
-    static int pref = -1;
+// 3 = tcgen05/TMEM grouped GEMM, chosen when groups average SW_UMMA_MIN_ROWS (12) rows or more.
+static int sw_expert_path(int D, int I, int rows, int groups) {
+    static int pref = -1, umma_min = 12;
     if (pref < 0) {
         const char *e = getenv("SW_EXPERT_PATH");
         pref = 2;
+        if (e && !strcmp(e, "umma")) pref = 3;
+        if (e && !strcmp(e, "tma")) pref = 4;            // TMA decode kernels whatever the group size
         if (e && !strcmp(e, "mma")) pref = 1;
         if (e && !strcmp(e, "simt")) pref = 0;
         const char *f = getenv("SW_FORCE_SIMT");
         if (f && *f && *f != '0') pref = 0;
+        const char *m = getenv("SW_UMMA_MIN_ROWS");
+        if (m) umma_min = atoi(m);
     }
     if (pref == 0 || D % 128 || I % 128) return 0;
-    if (pref == 2 && !sw_tma_available()) return 1;
-    return pref;
+    if (pref == 1 || !sw_tma_available()) return 1;
+    if (pref == 4) return 2;
+    if (pref == 3 || (groups > 0 && rows >= (long long)umma_min * groups)) return 3;
+    return 2;
 }
 
 static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, const float *gu_s,
                           const void *dn_q, const float *dn_s, const float *x, int rows_x, void *xp,
                           float *glu, float *slots, float *sums, int *status, int D, int I,
-                          void (*mark)(void *, int), void *mark_ctx) {
-    int path = sw_expert_path(D, I);
-    if (path == 2 && (((uintptr_t)gu_q | (uintptr_t)dn_q) & 15)) path = 1;    // TMA wants 16-byte aligned blobs
+                          void (*mark)(void *, int), void *mark_ctx, const SwUmmaScratch *um = nullptr) {
+    int path = sw_expert_path(D, I, a.max_rows, a.max_groups);
+    if (path >= 2 && (((uintptr_t)gu_q | (uintptr_t)dn_q) & 15)) path = 1;    // TMA wants 16-byte aligned blobs
+    if (path == 3 && !um) path = 2;
+    if (path == 3) {
+        // tcgen05 path: gather + split the token rows in packed-slot order, build the chunk list, two grouped GEMMs
+        const long long nexp = a.expert_cnt > 4096 ? 4096 : a.expert_cnt;
+        const int P = a.max_rows, max_chunks = P / 128 + a.max_groups;
+        __half *xh = (__half *)um->xg, *xl = xh + (size_t)P * D;
+        __half *gh = (__half *)glu, *gl = gh + (size_t)P * I;
+        if (sw_launch_umma_gather(cfg, x, a.grow, P, D, xh, xl)) return -1;
+        if (sw_launch_umma_chunks(cfg, a, um->nchunks, um->chunks)) return -1;
+        a.q = (const uint8_t *)gu_q; a.s = gu_s; a.KD = D; a.OUT = I;
+        if (sw_launch_q4_umma(cfg, a, xh, xl, gh, gl, um->nchunks, um->chunks, max_chunks, status, nexp * 2 * I, true)) return -1;
+        if (mark) mark(mark_ctx, 0);
+        a.q = (const uint8_t *)dn_q; a.s = dn_s; a.KD = I; a.OUT = D;
+        if (sw_launch_q4_umma(cfg, a, gh, gl, slots, nullptr, um->nchunks, um->chunks, max_chunks, status, nexp * D, false)) return -1;
+        if (mark) mark(mark_ctx, 1);
+        return 0;
+    }
     if (path > 0) {
         // sums: [rows_x] row sums of x, then [max_rows, parts] partial row sums of the packed SiLU*up rows
         float *xsum = sums, *ypart = sums + ((rows_x + 63) & ~63);
@@ -289,7 +320,7 @@ static int sw_expert_stage(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
     a.gexp = c->r.gexp; a.gbeg = c->r.gbeg; a.gcnt = c->r.gcnt; a.G = c->r.G; a.grow = c->r.grow;
     a.expert_lo = lo; a.expert_cnt = cnt;
     a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K;
-    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, nullptr, nullptr))
+    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, nullptr, nullptr, &c->um))
         return sw_fail("expert launch failed");
     return 0;
 }
@@ -394,7 +425,7 @@ extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
     a.expert_lo = lo; a.expert_cnt = cnt;
     a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K;
     auto mark = [](void *p, int which) { MarkCtx *m = (MarkCtx *)p; sw_prof_mark(m->c, which == 0 ? SW_ST_GATEUP : SW_ST_DOWN, m->st); };
-    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, mark, &mc))
+    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, mark, &mc, &c->um))
         return sw_fail("expert launch failed");
     if (overlap) {
         SW_CUDA(cudaStreamWaitEvent(st, c->ev_join, 0));

@@ -1,0 +1,434 @@
+// Grouped int4 expert GEMM on the 5th-generation tensor cores (tcgen05 + TMEM)
+// for groups with many token rows (prefill, large decode batches).
+//
+// CTA tile: M = 128 weight rows x N <= 128 token rows of one expert group, K in
+// stages of 64 columns.  Ten warps, four roles:
+//   warp 8      TMA producer: per stage one/two 2D tiles of raw int4 weights
+//               (128 rows x 32 B) and the fp16 hi and lo activation tiles
+//               (R rows x 128 B, 128B swizzle = the K-major canonical layout the
+//               tensor core reads) into a ring of shared-memory stages
+//   warps 0-3   dequantise: thread r turns the 32 raw bytes of tile row r into 64
+//               exact fp16 integers (nibble-8) and stores them as one swizzled
+//               128-byte row of a double-buffered A tile
+//   warp 9      one thread issues tcgen05.mma (kind::f16, f32 accumulate in TMEM):
+//               per 16-column step one MMA against the hi tile and one against
+//               the lo tile (x = hi + lo); tcgen05.commit releases the buffers
+//   warps 4-7   epilogue: tcgen05.ld the accumulator (two accumulators alternate,
+//               so the next tile's MMAs overlap this epilogue), apply the per-row
+//               scales and SiLU(gate)*up or store the f32 slot rows
+// For gate/up, tile row 2j is gate row j and tile row 2j+1 is up row j, so the two
+// halves of an output meet in neighbouring lanes of the epilogue.
+//
+// Activations for this kernel are fp16 hi/lo arrays [rows, K] whose columns are
+// permuted inside every group of eight to 0,4,1,5,2,6,3,7 -- the order in which
+// the nibble masks deliver a weight word -- so a dequantised word is one 16-byte
+// chunk of the A tile.  The token rows of gate/up are gathered into packed-slot
+// order by k_umma_gather (the reference gathers too, c/laguna.c:742-743).
+//
+// All mbarrier waits are bounded; on a timeout the CTA raises an abort flag, sets
+// SW_ST_TIMEOUT in the status word and still frees its tensor memory.
+#include "sw_common.cuh"
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <stdlib.h>
+
+#define UM_STAGES 4
+#define UM_RAW_A 4096                    // 128 rows x 32 B of int4
+#define UM_BT 16384                      // one activation tile: 128 rows x 128 B
+#define UM_STAGE_BYTES (UM_RAW_A + 2 * UM_BT)
+#define UM_A16 16384                     // dequantised A tile: 128 rows x 64 fp16
+#define UM_WAIT_LIMIT (1u << 24)
+#define UM_THREADS 320
+
+__device__ __forceinline__ unsigned um_s32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void um_bar_init(unsigned bar, unsigned count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory"); }
+__device__ __forceinline__ void um_bar_expect(unsigned bar, unsigned bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory"); }
+__device__ __forceinline__ void um_bar_arrive(unsigned bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory"); }
+__device__ __forceinline__ bool um_bar_wait(unsigned bar, unsigned parity, volatile int *abortp) {
+    for (unsigned it = 0; it < UM_WAIT_LIMIT; it++) {
+        unsigned ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((it & 255) == 255 && *abortp) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void um_tma_2d(unsigned dst, const CUtensorMap *tm, int x, int y, unsigned bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 :: "r"(dst), "l"(tm), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 B apart
+__device__ __forceinline__ uint64_t um_desc(unsigned saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);            // start address
+    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset
+    d |= (uint64_t)1 << 46;                             // descriptor version
+    d |= (uint64_t)2 << 61;                             // SWIZZLE_128B
+    return d;
+}
+__device__ __forceinline__ void um_mma(unsigned d_tmem, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void um_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ void um_ld32(unsigned taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+// 8 nibbles -> 8 fp16 (nibble-8) in the order c0,c4,c1,c5,c2,c6,c3,c7
+__device__ __forceinline__ uint4 um_dq(uint32_t w) {
+    const uint32_t MAGIC = 0x64006400u, C1032 = 0x64086408u, C16TH = 0x2C002C00u, CM72 = 0xD480D480u;
+    const uint32_t l0 = (w & 0x000F000Fu) | MAGIC, h0 = (w & 0x00F000F0u) | MAGIC;
+    const uint32_t w2 = w >> 8;
+    const uint32_t l1 = (w2 & 0x000F000Fu) | MAGIC, h1 = (w2 & 0x00F000F0u) | MAGIC;
+    uint4 o;
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(o.x) : "r"(l0), "r"(C1032));
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(o.y) : "r"(h0), "r"(C16TH), "r"(CM72));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(o.z) : "r"(l1), "r"(C1032));
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(o.w) : "r"(h1), "r"(C16TH), "r"(CM72));
+    return o;
+}
+__device__ __forceinline__ int um_perm8(int col) { const int j = col & 7; return (col & ~7) | ((j & 3) * 2 + (j >> 2)); }
+__device__ __forceinline__ void um_split(float v, __half &hi, __half &lo) {
+    v = fminf(fmaxf(v, -65504.f), 65504.f);
+    hi = __float2half_rn(v);
+    lo = __float2half_rn(v - __half2float(hi));
+}
+
+// ---------------------------------------------------------------------------
+// xg_hi/xg_lo[slot, :] = fp16 hi/lo of x[grow[slot], :] with the columns of each
+// group of eight in the order 0,4,1,5,2,6,3,7
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+k_umma_gather(const float *__restrict__ x, const int *__restrict__ grow, int P, int KD,
+              __half *__restrict__ hi, __half *__restrict__ lo) {
+    const int cpr = KD >> 3;
+    const size_t n = (size_t)P * cpr;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+        const int slot = (int)(idx / cpr), c8 = (int)(idx - (size_t)slot * cpr);
+        const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)grow[slot] * KD + c8 * 8);
+        const float4 a = src[0], b = src[1];
+        const float v[8] = {a.x, b.x, a.y, b.y, a.z, b.z, a.w, b.w};
+        __half h[8], l[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) um_split(v[i], h[i], l[i]);
+        reinterpret_cast<uint4 *>(hi)[idx] = *reinterpret_cast<uint4 *>(h);
+        reinterpret_cast<uint4 *>(lo)[idx] = *reinterpret_cast<uint4 *>(l);
+    }
+}
+
+// work list: one entry per (group, chunk of <=128 rows): {group index, first row of the chunk inside the group}
+__global__ void __launch_bounds__(1024)
+k_umma_chunks(const int *__restrict__ Gp, const int *__restrict__ gexp, const int *__restrict__ gcnt,
+              int expert_lo, int expert_cnt, int *__restrict__ nchunks, int2 *__restrict__ chunks) {
+    __shared__ int s_scan[1024];
+    const int G = *Gp, tid = threadIdx.x;
+    int c = 0;
+    if (tid < G) { const int e = gexp[tid] - expert_lo; if (e >= 0 && e < expert_cnt) c = (gcnt[tid] + 127) >> 7; }
+    s_scan[tid] = c;
+    __syncthreads();
+    for (int off = 1; off < 1024; off <<= 1) {
+        int v = tid >= off ? s_scan[tid - off] : 0;
+        __syncthreads();
+        s_scan[tid] += v;
+        __syncthreads();
+    }
+    const int base = s_scan[tid] - c;
+    for (int i = 0; i < c; i++) chunks[base + i] = make_int2(tid, i * 128);
+    if (tid == 1023) *nchunks = s_scan[1023];
+}
+
+struct UmArgs {
+    const float *Ws;
+    void *Y0, *Y1;                 // gate/up: fp16 hi, lo [rows, OUT] (permuted columns); down: f32 slots [rows, OUT], unused
+    const int *gexp, *gbeg, *gcnt, *nchunks;
+    const int2 *chunks;
+    int *status;
+    int KD, OUT, expert_lo;
+};
+
+template <bool GATEUP>
+__global__ void __launch_bounds__(UM_THREADS, 1)
+k_q4_umma(const __grid_constant__ CUtensorMap tmW,
+          const __grid_constant__ CUtensorMap tmH16, const __grid_constant__ CUtensorMap tmH32,
+          const __grid_constant__ CUtensorMap tmH64, const __grid_constant__ CUtensorMap tmH128,
+          const __grid_constant__ CUtensorMap tmL16, const __grid_constant__ CUtensorMap tmL32,
+          const __grid_constant__ CUtensorMap tmL64, const __grid_constant__ CUtensorMap tmL128,
+          const UmArgs a) {
+    extern __shared__ unsigned char um_dyn[];
+    __shared__ unsigned long long b_raw_full[UM_STAGES], b_raw_free[UM_STAGES], b_a_full[2], b_a_free[2], b_acc_full[2], b_acc_free[2];
+    __shared__ unsigned s_tmem;
+    __shared__ int s_abort;
+    unsigned char *smem = (unsigned char *)(((uintptr_t)um_dyn + 1023) & ~(uintptr_t)1023);
+    unsigned char *a16 = smem + UM_STAGES * UM_STAGE_BYTES;             // two dequantised A tiles
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int KD = a.KD, OUT = a.OUT;
+    const int nrows_w = GATEUP ? 2 * OUT : OUT;
+    constexpr int OPT = GATEUP ? 64 : 128;                              // outputs per tile
+    const int mtiles = (OUT + OPT - 1) / OPT;
+    const int NST = KD >> 6;                                            // 64-column stages per tile
+    const int items = *a.nchunks * mtiles;
+    volatile int *abortp = &s_abort;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < UM_STAGES; i++) { um_bar_init(um_s32(&b_raw_full[i]), 1); um_bar_init(um_s32(&b_raw_free[i]), 1); }
+        for (int i = 0; i < 2; i++) {
+            um_bar_init(um_s32(&b_a_full[i]), 4); um_bar_init(um_s32(&b_a_free[i]), 1);
+            um_bar_init(um_s32(&b_acc_full[i]), 1); um_bar_init(um_s32(&b_acc_free[i]), 4);
+        }
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {                                                    // tensor memory: two 128-column accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(um_s32(&s_tmem)), "r"(256) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem = s_tmem;
+
+    // item -> (chunk, m-tile): chunks of one group and m-tile are neighbours, so a weight tile is re-read from L2
+    auto decode = [&](int item, int &gi, int &c0, int &mt) {
+        const int ch = item / mtiles; mt = item - ch * mtiles;
+        const int2 c = a.chunks[ch]; gi = c.x; c0 = c.y;
+    };
+
+    if (warp == 8) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            unsigned kk = 0;
+            for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
+                int gi, c0, mt; decode(item, gi, c0, mt);
+                const int e = a.gexp[gi] - a.expert_lo, n = min(128, a.gcnt[gi] - c0), row0 = a.gbeg[gi] + c0;
+                const int R = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : 128;
+                const CUtensorMap *th = R == 16 ? &tmH16 : R == 32 ? &tmH32 : R == 64 ? &tmH64 : &tmH128;
+                const CUtensorMap *tl = R == 16 ? &tmL16 : R == 32 ? &tmL32 : R == 64 ? &tmL64 : &tmL128;
+                const int wrow = e * nrows_w + mt * OPT;
+                for (int st = 0; st < NST; st++, kk++) {
+                    const int s = kk % UM_STAGES;
+                    if (kk >= UM_STAGES && !um_bar_wait(um_s32(&b_raw_free[s]), ((kk / UM_STAGES) - 1) & 1, abortp)) {
+                        atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break;
+                    }
+                    unsigned char *sp = smem + s * UM_STAGE_BYTES;
+                    const unsigned bar = um_s32(&b_raw_full[s]);
+                    um_bar_expect(bar, (unsigned)UM_RAW_A + 2u * (unsigned)R * 128u);
+                    if (GATEUP) {
+                        um_tma_2d(um_s32(sp), &tmW, st * 32, wrow, bar);                      // 64 gate rows
+                        um_tma_2d(um_s32(sp + UM_RAW_A / 2), &tmW, st * 32, wrow + OUT, bar); // 64 up rows
+                    } else {
+                        um_tma_2d(um_s32(sp), &tmW, st * 32, wrow, bar);
+                    }
+                    um_tma_2d(um_s32(sp + UM_RAW_A), th, st * 64, row0, bar);
+                    um_tma_2d(um_s32(sp + UM_RAW_A + UM_BT), tl, st * 64, row0, bar);
+                }
+            }
+        }
+    } else if (warp == 9) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            unsigned kk = 0, tile = 0;
+            for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, tile++) {
+                int gi, c0, mt; decode(item, gi, c0, mt);
+                const int n = min(128, a.gcnt[gi] - c0);
+                const int N = (n + 15) & ~15;
+                const unsigned idesc = (1u << 4) | ((unsigned)(N >> 3) << 17) | ((128u >> 4) << 24);   // f32 accum, f16 x f16, K-major
+                const unsigned acc = tile & 1, d_tmem = tmem + acc * 128;
+                if (tile >= 2 && !um_bar_wait(um_s32(&b_acc_free[acc]), ((tile >> 1) - 1) & 1, abortp)) {
+                    atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int st = 0; st < NST; st++, kk++) {
+                    const int s = kk % UM_STAGES, b = kk & 1;
+                    if (!um_bar_wait(um_s32(&b_a_full[b]), (kk >> 1) & 1, abortp)) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t da = um_desc(um_s32(a16 + b * UM_A16));
+                    const uint64_t dh = um_desc(um_s32(smem + s * UM_STAGE_BYTES + UM_RAW_A));
+                    const uint64_t dl = um_desc(um_s32(smem + s * UM_STAGE_BYTES + UM_RAW_A + UM_BT));
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {                       // 16 columns = 32 bytes per step
+                        um_mma(d_tmem, da + 2 * k, dh + 2 * k, idesc, (st | k) ? 1u : 0u);
+                        um_mma(d_tmem, da + 2 * k, dl + 2 * k, idesc, 1u);
+                    }
+                    um_commit(um_s32(&b_a_free[b]));
+                    um_commit(um_s32(&b_raw_free[s]));
+                }
+                if (*abortp) break;
+                um_commit(um_s32(&b_acc_full[acc]));
+            }
+        }
+    } else if (warp < 4) {
+        // ------------------------------ dequantise ------------------------------
+        const int r = threadIdx.x;                                      // tile row 0..127
+        unsigned kk = 0;
+        for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
+            for (int st = 0; st < NST; st++, kk++) {
+                const int s = kk % UM_STAGES, b = kk & 1;
+                bool ok = um_bar_wait(um_s32(&b_raw_full[s]), (kk / UM_STAGES) & 1, abortp);
+                if (ok && kk >= 2) ok = um_bar_wait(um_s32(&b_a_free[b]), ((kk >> 1) - 1) & 1, abortp);
+                if (!ok) { if (lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; } break; }
+                const unsigned char *raw = smem + s * UM_STAGE_BYTES;
+                const uint4 *src = GATEUP ? reinterpret_cast<const uint4 *>(raw + (r & 1) * (UM_RAW_A / 2) + (r >> 1) * 32)
+                                          : reinterpret_cast<const uint4 *>(raw + r * 32);
+                const uint4 w0 = src[0], w1 = src[1];
+                unsigned char *dst = a16 + b * UM_A16 + r * 128;
+                const int x7 = r & 7;
+                *reinterpret_cast<uint4 *>(dst + ((0 ^ x7) << 4)) = um_dq(w0.x);
+                *reinterpret_cast<uint4 *>(dst + ((1 ^ x7) << 4)) = um_dq(w0.y);
+                *reinterpret_cast<uint4 *>(dst + ((2 ^ x7) << 4)) = um_dq(w0.z);
+                *reinterpret_cast<uint4 *>(dst + ((3 ^ x7) << 4)) = um_dq(w0.w);
+                *reinterpret_cast<uint4 *>(dst + ((4 ^ x7) << 4)) = um_dq(w1.x);
+                *reinterpret_cast<uint4 *>(dst + ((5 ^ x7) << 4)) = um_dq(w1.y);
+                *reinterpret_cast<uint4 *>(dst + ((6 ^ x7) << 4)) = um_dq(w1.z);
+                *reinterpret_cast<uint4 *>(dst + ((7 ^ x7) << 4)) = um_dq(w1.w);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic stores -> tensor-core reads
+                __syncwarp();
+                if (lane == 0) um_bar_arrive(um_s32(&b_a_full[b]));
+            }
+        }
+    } else {
+        // ------------------------------ epilogue (warps 4-7) ------------------------------
+        const int q = warp & 3;                                         // TMEM lane quarter of this warp
+        const int trow = q * 32 + lane;                                 // tile row held by this thread
+        unsigned tile = 0;
+        for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, tile++) {
+            int gi, c0, mt; decode(item, gi, c0, mt);
+            const int e = a.gexp[gi] - a.expert_lo, n = min(128, a.gcnt[gi] - c0), row0 = a.gbeg[gi] + c0;
+            const float *ws = a.Ws + (size_t)e * nrows_w;
+            const unsigned acc = tile & 1;
+            if (!um_bar_wait(um_s32(&b_acc_full[acc]), (tile >> 1) & 1, abortp)) {
+                if (lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; }
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float sc;                                                   // scale of this thread's weight row
+            int o;                                                      // output index of this thread's row
+            if (GATEUP) { o = mt * 64 + (trow >> 1); sc = o < OUT ? ws[(trow & 1) * OUT + o] : 0.f; }
+            else        { o = mt * 128 + trow;       sc = o < OUT ? ws[o] : 0.f; }
+            for (int cb = 0; cb < n; cb += 32) {
+                float v[32];
+                um_ld32(tmem + acc * 128 + cb + ((unsigned)(q * 32) << 16), v);
+                if (GATEUP) {
+                    __half *Yh = reinterpret_cast<__half *>(a.Y0), *Yl = reinterpret_cast<__half *>(a.Y1);
+                    const int pcol = um_perm8(o);
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const float mine = v[j] * sc;
+                        const float other = __shfl_xor_sync(SW_FULL_MASK, mine, 1);   // even lanes: gate, odd lanes: up
+                        if (!(lane & 1) && cb + j < n && o < OUT) {
+                            const float y = (mine / (1.f + expf(-mine))) * other;
+                            __half hi, lo; um_split(y, hi, lo);
+                            const size_t pos = (size_t)(row0 + cb + j) * OUT + pcol;
+                            Yh[pos] = hi; Yl[pos] = lo;
+                        }
+                    }
+                } else {
+                    float *Y = reinterpret_cast<float *>(a.Y0);
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (cb + j < n && o < OUT) Y[(size_t)(row0 + cb + j) * OUT + o] = v[j] * sc;
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) um_bar_arrive(um_s32(&b_acc_free[acc]));
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 9) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(256) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*um_encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static um_encode_fn um_get_encode() {
+    static um_encode_fn fn = nullptr; static bool tried = false;
+    if (!tried) {
+        tried = true; void *p = nullptr; cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = (um_encode_fn)p;
+        else cudaGetLastError();
+    }
+    return fn;
+}
+static int um_make_map(CUtensorMap *m, CUtensorMapDataType dt, int esize, const void *ptr, long long inner, long long rows,
+                       int box_inner, int box_rows, CUtensorMapSwizzle sw) {
+    um_encode_fn enc = um_get_encode();
+    if (!enc) return -1;
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)inner * esize};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return enc(m, dt, 2, (void *)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -1;
+}
+
+bool sw_umma_available() { return um_get_encode() != nullptr; }
+
+int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow, int P, int KD, void *hi, void *lo) {
+    if (P <= 0) return 0;
+    size_t n = (size_t)P * (KD / 8);
+    long long grid = (long long)((n + 255) / 256);
+    if (grid > (long long)c.num_sms * 16) grid = (long long)c.num_sms * 16;
+    k_umma_gather<<<(unsigned)grid, 256, 0, c.stream>>>(x, grow, P, KD, (__half *)hi, (__half *)lo);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int sw_launch_umma_chunks(const SwLaunchCfg &c, const SwQ4Args &a, int *nchunks, void *chunks) {
+    k_umma_chunks<<<1, 1024, 0, c.stream>>>(a.G, a.gexp, a.gcnt, a.expert_lo, a.expert_cnt, nchunks, (int2 *)chunks);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// act_hi/act_lo: fp16 [max_rows, KD] in packed-slot order (permuted columns).
+// gate/up: Y0/Y1 = fp16 hi/lo [max_rows, OUT]; down: Y0 = f32 [max_rows, OUT].
+int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_hi, const void *act_lo, void *Y0, void *Y1,
+                      const int *nchunks, const void *chunks, int max_chunks, int *status, long long wrows_total, bool gateup) {
+    if (a.max_rows <= 0) return 0;
+    if (a.KD % 64 || a.OUT <= 0 || ((uintptr_t)a.q & 15)) return -1;
+    CUtensorMap tw, th[4], tl[4];
+    if (um_make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.q, a.KD / 2, wrows_total, 32, gateup ? 64 : 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
+    const int R[4] = {16, 32, 64, 128};
+    for (int i = 0; i < 4; i++) {
+        if (um_make_map(&th[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act_hi, a.KD, a.max_rows, 64, R[i], CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+        if (um_make_map(&tl[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act_lo, a.KD, a.max_rows, 64, R[i], CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+    }
+    constexpr int SMEM = UM_STAGES * UM_STAGE_BYTES + 2 * UM_A16 + 1024;
+    static bool attr = false;
+    if (!attr) {
+        if (cudaFuncSetAttribute(k_q4_umma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(k_q4_umma<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
+        attr = true;
+    }
+    UmArgs ka;
+    ka.Ws = a.s; ka.Y0 = Y0; ka.Y1 = Y1; ka.gexp = a.gexp; ka.gbeg = a.gbeg; ka.gcnt = a.gcnt; ka.nchunks = nchunks;
+    ka.chunks = (const int2 *)chunks; ka.status = status; ka.KD = a.KD; ka.OUT = a.OUT; ka.expert_lo = a.expert_lo;
+    const int mtiles = (a.OUT + (gateup ? 64 : 128) - 1) / (gateup ? 64 : 128);
+    long long items = (long long)max_chunks * mtiles;
+    long long grid = c.num_sms;                        // one CTA per SM (shared memory and tensor memory are sized for that)
+    if (grid > items) grid = items;
+    if (grid < 1) grid = 1;
+    if (gateup) k_q4_umma<true><<<(unsigned)grid, UM_THREADS, SMEM, c.stream>>>(tw, th[0], th[1], th[2], th[3], tl[0], tl[1], tl[2], tl[3], ka);
+    else k_q4_umma<false><<<(unsigned)grid, UM_THREADS, SMEM, c.stream>>>(tw, th[0], th[1], th[2], th[3], tl[0], tl[1], tl[2], tl[3], ka);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}

@@ -75,6 +75,18 @@ def test_scaled_configs(orc, base, kw, T):
     run_case(case, orc)
 
 
+@pytest.mark.parametrize("base,kw,T", [
+    ("c3", dict(D=512, I=256, SI=128, E=32, K=4), 512),      # Zipf-skewed: groups from a few rows to several 128-row chunks
+    ("c5", dict(D=512, I=128, SI=128, E=64, K=8), 160),      # ~20 rows per expert: 32-row tiles
+    ("c1", dict(D=256, I=128, E=8, K=2), 700),                # softmax, no shared, 175 rows per expert
+])
+def test_large_groups_take_the_tensor_memory_path(orc, base, kw, T):
+    """Groups averaging >= 12 rows run the tcgen05/TMEM grouped GEMM; same parity bars."""
+    case = synth_case(base, corr_bias_std=0.01, T=T, **kw)
+    assert T * case.cfg.K >= 12 * case.cfg.E
+    run_case(case, orc)
+
+
 def test_graph_replay_matches_eager(orc):
     case = synth_case("c2", D=512, E=64, K=6, I=128, SI=128, T=12)
     blk, layer, desc = make_block(case)
