@@ -329,9 +329,21 @@ static int sw_expert_stage(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
 // widths are multiples of 32; `pk` is scratch for the packed copy of x, sglu holds
 // the packed (or f32) intermediate.
 static int sw_shared_run(const SwLaunchCfg &cfg, const SwMoeLayer *L, const float *x, int T, void *pk, float *sglu, float *spart,
-                         float **so, int *so_slices, void (*mark)(void *, int), void *mark_ctx) {
+                         float **so, int *so_slices, void (*mark)(void *, int), void *mark_ctx, int *status = nullptr) {
     static int force_simt = -1;
     if (force_simt < 0) { const char *e = getenv("SW_FORCE_SIMT"); force_simt = (e && *e && *e != '0') ? 1 : 0; }
+    if (!force_simt && T >= 128 && L->D % 64 == 0 && L->SI % 64 == 0 && sw_umma_available() && status) {
+        // many rows: dense tcgen05 GEMMs; pk holds the planar bf16 hi|lo copy of x, sglu the planar hi|lo SiLU*up rows
+        __nv_bfloat16 *xh = (__nv_bfloat16 *)pk, *xl = xh + (size_t)T * L->D;
+        __nv_bfloat16 *gh = (__nv_bfloat16 *)sglu, *gl = gh + (size_t)T * L->SI;
+        if (sw_launch_pack_bf16_planar(cfg, x, xh, xl, T, L->D)) return -1;
+        if (sw_launch_bf16_umma(cfg, L->sh_gate, L->sh_up, xh, xl, gh, gl, T, L->D, L->SI, status, true)) return -1;
+        if (mark) mark(mark_ctx, 0);
+        if (sw_launch_bf16_umma(cfg, L->sh_down, nullptr, gh, gl, spart, nullptr, T, L->SI, L->D, status, false)) return -1;
+        if (mark) mark(mark_ctx, 1);
+        *so = spart; *so_slices = 1;
+        return 0;
+    }
     if (!force_simt && L->D % 32 == 0 && L->SI % 32 == 0) {
         const int ks1 = sw_shared_slices(cfg.num_sms, (L->SI + 7) / 8, L->D);
         const int ks2 = sw_shared_slices(cfg.num_sms, (L->D + 15) / 16, L->SI);
@@ -356,7 +368,7 @@ static int sw_shared_run(const SwLaunchCfg &cfg, const SwMoeLayer *L, const floa
 
 static int sw_shared_stage(SwMoeCtx *c, const SwMoeLayer *L, const float *x, int T, cudaStream_t st, float **so, int *so_slices) {
     SwLaunchCfg cfg{c->num_sms, st};
-    if (sw_shared_run(cfg, L, x, T, c->spk, c->sglu, c->so, so, so_slices, nullptr, nullptr)) return sw_fail("shared expert launch failed");
+    if (sw_shared_run(cfg, L, x, T, c->spk, c->sglu, c->so, so, so_slices, nullptr, nullptr, c->r.status)) return sw_fail("shared expert launch failed");
     return 0;
 }
 
@@ -410,7 +422,7 @@ extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
         SwLaunchCfg acfg{c->num_sms, c->aux};
         SW_CUDA(cudaEventRecord(c->ev_fork, st));
         SW_CUDA(cudaStreamWaitEvent(c->aux, c->ev_fork, 0));
-        if (sw_shared_run(acfg, L, x, T, c->spk, c->sglu, c->so, &so, &so_slices, nullptr, nullptr)) return sw_fail("shared expert launch failed");
+        if (sw_shared_run(acfg, L, x, T, c->spk, c->sglu, c->so, &so, &so_slices, nullptr, nullptr, c->r.status)) return sw_fail("shared expert launch failed");
         SW_CUDA(cudaEventRecord(c->ev_join, c->aux));
     }
 
@@ -431,7 +443,7 @@ extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
         SW_CUDA(cudaStreamWaitEvent(st, c->ev_join, 0));
         sw_prof_mark(c, SW_ST_SH_GATEUP, st); sw_prof_mark(c, SW_ST_SH_DOWN, st);
     } else if (has_shared) {
-        if (sw_shared_run(cfg, L, x, T, c->spk, c->sglu, c->so, &so, &so_slices, smark, &mc)) return sw_fail("shared expert launch failed");
+        if (sw_shared_run(cfg, L, x, T, c->spk, c->sglu, c->so, &so, &so_slices, smark, &mc, c->r.status)) return sw_fail("shared expert launch failed");
     } else {
         sw_prof_mark(c, SW_ST_SH_GATEUP, st); sw_prof_mark(c, SW_ST_SH_DOWN, st);
     }

@@ -79,6 +79,9 @@ int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow,
 int sw_launch_umma_chunks(const SwLaunchCfg &c, const SwQ4Args &a, int *nchunks, void *chunks);
 int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_hi, const void *act_lo, void *Y0, void *Y1,
                       const int *nchunks, const void *chunks, int max_chunks, int *status, long long wrows_total, bool gateup);
+int sw_launch_pack_bf16_planar(const SwLaunchCfg &c, const float *x, void *hi, void *lo, int rows, int KD);
+int sw_launch_bf16_umma(const SwLaunchCfg &c, const void *W0, const void *W1, const void *act_hi, const void *act_lo,
+                        void *Y0, void *Y1, int T, int KD, int O, int *status, bool gateup);
 int sw_launch_pack_bf16(const SwLaunchCfg &c, const float *x, void *xp, int rows, int KD);
 int sw_shared_slices(int num_sms, int mblocks, int KD);
 int sw_launch_bf16_mma(const SwLaunchCfg &c, const void *W0, const void *W1, const void *XP, float *part,

@@ -269,12 +269,17 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
                 for (int j = 0; j < 2; j++) {
                     tok[j] = c0 + 2 * t + j;
                     const bool ok = own && tok[j] < c0 + ntok;
+                    // row sum of the token's activations: the 8 lanes that share t split the partial
+                    // sums between them (k = g, g+8, ...) and add up in a fixed tree
                     float sx = 0.f;
                     if (ok) {
                         const int rid = GATEUP ? a.grow[beg + tok[j]] : beg + tok[j];
                         const float *ps = a.xsum + (size_t)rid * a.xsum_parts;
-                        for (int k = 0; k < a.xsum_parts; k++) sx += ps[k];
+                        for (int k = g; k < a.xsum_parts; k += 8) sx += ps[k];
                     }
+                    sx += __shfl_xor_sync(SW_FULL_MASK, sx, 4);
+                    sx += __shfl_xor_sync(SW_FULL_MASK, sx, 8);
+                    sx += __shfl_xor_sync(SW_FULL_MASK, sx, 16);
                     corr[j] = 8.f * sx;
                     if (!ok) tok[j] = -1;
                 }

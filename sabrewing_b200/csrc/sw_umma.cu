@@ -2,18 +2,18 @@
 // for groups with many token rows (prefill, large decode batches).
 //
 // CTA tile: M = 128 weight rows x N <= 128 token rows of one expert group, K in
-// stages of 64 columns.  Ten warps, four roles:
-//   warp 8      TMA producer: per stage one/two 2D tiles of raw int4 weights
+// stages of 64 columns.  Fourteen warps, four roles:
+//   warp 12     TMA producer: per stage one/two 2D tiles of raw int4 weights
 //               (128 rows x 32 B) and the fp16 hi and lo activation tiles
 //               (R rows x 128 B, 128B swizzle = the K-major canonical layout the
 //               tensor core reads) into a ring of shared-memory stages
-//   warps 0-3   dequantise: thread r turns the 32 raw bytes of tile row r into 64
-//               exact fp16 integers (nibble-8) and stores them as one swizzled
-//               128-byte row of a double-buffered A tile
-//   warp 9      one thread issues tcgen05.mma (kind::f16, f32 accumulate in TMEM):
+//   warps 0-7   dequantise: two threads per tile row turn its 32 raw bytes into 64
+//               exact fp16 integers (nibble-8) and store them as one swizzled
+//               128-byte row of one of four A tiles in flight
+//   warp 13     one thread issues tcgen05.mma (kind::f16, f32 accumulate in TMEM):
 //               per 16-column step one MMA against the hi tile and one against
 //               the lo tile (x = hi + lo); tcgen05.commit releases the buffers
-//   warps 4-7   epilogue: tcgen05.ld the accumulator (two accumulators alternate,
+//   warps 8-11  epilogue: tcgen05.ld the accumulator (two accumulators alternate,
 //               so the next tile's MMAs overlap this epilogue), apply the per-row
 //               scales and SiLU(gate)*up or store the f32 slot rows
 // For gate/up, tile row 2j is gate row j and tile row 2j+1 is up row j, so the two
@@ -38,7 +38,9 @@
 #define UM_STAGE_BYTES (UM_RAW_A + 2 * UM_BT)
 #define UM_A16 16384                     // dequantised A tile: 128 rows x 64 fp16
 #define UM_WAIT_LIMIT (1u << 24)
-#define UM_THREADS 320
+#define UM_ABUF 4                        // dequantised A tiles in flight
+#define UM_DQ_WARPS 8
+#define UM_THREADS ((UM_DQ_WARPS + 4 + 2) * 32)
 
 __device__ __forceinline__ unsigned um_s32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void um_bar_init(unsigned bar, unsigned count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory"); }
@@ -167,11 +169,11 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
           const __grid_constant__ CUtensorMap tmL64, const __grid_constant__ CUtensorMap tmL128,
           const UmArgs a) {
     extern __shared__ unsigned char um_dyn[];
-    __shared__ unsigned long long b_raw_full[UM_STAGES], b_raw_free[UM_STAGES], b_a_full[2], b_a_free[2], b_acc_full[2], b_acc_free[2];
+    __shared__ unsigned long long b_raw_full[UM_STAGES], b_raw_free[UM_STAGES], b_a_full[UM_ABUF], b_a_free[UM_ABUF], b_acc_full[2], b_acc_free[2];
     __shared__ unsigned s_tmem;
     __shared__ int s_abort;
     unsigned char *smem = (unsigned char *)(((uintptr_t)um_dyn + 1023) & ~(uintptr_t)1023);
-    unsigned char *a16 = smem + UM_STAGES * UM_STAGE_BYTES;             // two dequantised A tiles
+    unsigned char *a16 = smem + UM_STAGES * UM_STAGE_BYTES;             // UM_ABUF dequantised A tiles
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KD = a.KD, OUT = a.OUT;
     const int nrows_w = GATEUP ? 2 * OUT : OUT;
@@ -183,14 +185,12 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < UM_STAGES; i++) { um_bar_init(um_s32(&b_raw_full[i]), 1); um_bar_init(um_s32(&b_raw_free[i]), 1); }
-        for (int i = 0; i < 2; i++) {
-            um_bar_init(um_s32(&b_a_full[i]), 4); um_bar_init(um_s32(&b_a_free[i]), 1);
-            um_bar_init(um_s32(&b_acc_full[i]), 1); um_bar_init(um_s32(&b_acc_free[i]), 4);
-        }
+        for (int i = 0; i < UM_ABUF; i++) { um_bar_init(um_s32(&b_a_full[i]), UM_DQ_WARPS); um_bar_init(um_s32(&b_a_free[i]), 1); }
+        for (int i = 0; i < 2; i++) { um_bar_init(um_s32(&b_acc_full[i]), 1); um_bar_init(um_s32(&b_acc_free[i]), 4); }
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 9) {                                                    // tensor memory: two 128-column accumulators
+    if (warp == UM_DQ_WARPS + 5) {                                      // tensor memory: two 128-column accumulators
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(um_s32(&s_tmem)), "r"(256) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -205,7 +205,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
         const int2 c = a.chunks[ch]; gi = c.x; c0 = c.y;
     };
 
-    if (warp == 8) {
+    if (warp == UM_DQ_WARPS + 4) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             unsigned kk = 0;
@@ -235,7 +235,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
                 }
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == UM_DQ_WARPS + 5) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
             unsigned kk = 0, tile = 0;
@@ -250,8 +250,8 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 for (int st = 0; st < NST; st++, kk++) {
-                    const int s = kk % UM_STAGES, b = kk & 1;
-                    if (!um_bar_wait(um_s32(&b_a_full[b]), (kk >> 1) & 1, abortp)) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
+                    const int s = kk % UM_STAGES, b = kk % UM_ABUF;
+                    if (!um_bar_wait(um_s32(&b_a_full[b]), (kk / UM_ABUF) & 1, abortp)) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t da = um_desc(um_s32(a16 + b * UM_A16));
                     const uint64_t dh = um_desc(um_s32(smem + s * UM_STAGE_BYTES + UM_RAW_A));
@@ -268,37 +268,32 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
                 um_commit(um_s32(&b_acc_full[acc]));
             }
         }
-    } else if (warp < 4) {
+    } else if (warp < UM_DQ_WARPS) {
         // ------------------------------ dequantise ------------------------------
-        const int r = threadIdx.x;                                      // tile row 0..127
+        const int r = threadIdx.x >> 1, h = threadIdx.x & 1;            // tile row 0..127, which 16 raw bytes of it
         unsigned kk = 0;
         for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
             for (int st = 0; st < NST; st++, kk++) {
-                const int s = kk % UM_STAGES, b = kk & 1;
+                const int s = kk % UM_STAGES, b = kk % UM_ABUF;
                 bool ok = um_bar_wait(um_s32(&b_raw_full[s]), (kk / UM_STAGES) & 1, abortp);
-                if (ok && kk >= 2) ok = um_bar_wait(um_s32(&b_a_free[b]), ((kk >> 1) - 1) & 1, abortp);
+                if (ok && kk >= UM_ABUF) ok = um_bar_wait(um_s32(&b_a_free[b]), ((kk / UM_ABUF) - 1) & 1, abortp);
                 if (!ok) { if (lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; } break; }
                 const unsigned char *raw = smem + s * UM_STAGE_BYTES;
-                const uint4 *src = GATEUP ? reinterpret_cast<const uint4 *>(raw + (r & 1) * (UM_RAW_A / 2) + (r >> 1) * 32)
-                                          : reinterpret_cast<const uint4 *>(raw + r * 32);
-                const uint4 w0 = src[0], w1 = src[1];
+                const uint4 w = GATEUP ? *reinterpret_cast<const uint4 *>(raw + (r & 1) * (UM_RAW_A / 2) + (r >> 1) * 32 + h * 16)
+                                       : *reinterpret_cast<const uint4 *>(raw + r * 32 + h * 16);
                 unsigned char *dst = a16 + b * UM_A16 + r * 128;
-                const int x7 = r & 7;
-                *reinterpret_cast<uint4 *>(dst + ((0 ^ x7) << 4)) = um_dq(w0.x);
-                *reinterpret_cast<uint4 *>(dst + ((1 ^ x7) << 4)) = um_dq(w0.y);
-                *reinterpret_cast<uint4 *>(dst + ((2 ^ x7) << 4)) = um_dq(w0.z);
-                *reinterpret_cast<uint4 *>(dst + ((3 ^ x7) << 4)) = um_dq(w0.w);
-                *reinterpret_cast<uint4 *>(dst + ((4 ^ x7) << 4)) = um_dq(w1.x);
-                *reinterpret_cast<uint4 *>(dst + ((5 ^ x7) << 4)) = um_dq(w1.y);
-                *reinterpret_cast<uint4 *>(dst + ((6 ^ x7) << 4)) = um_dq(w1.z);
-                *reinterpret_cast<uint4 *>(dst + ((7 ^ x7) << 4)) = um_dq(w1.w);
+                const int x7 = r & 7, c0 = h * 4;
+                *reinterpret_cast<uint4 *>(dst + (((c0 + 0) ^ x7) << 4)) = um_dq(w.x);
+                *reinterpret_cast<uint4 *>(dst + (((c0 + 1) ^ x7) << 4)) = um_dq(w.y);
+                *reinterpret_cast<uint4 *>(dst + (((c0 + 2) ^ x7) << 4)) = um_dq(w.z);
+                *reinterpret_cast<uint4 *>(dst + (((c0 + 3) ^ x7) << 4)) = um_dq(w.w);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic stores -> tensor-core reads
                 __syncwarp();
                 if (lane == 0) um_bar_arrive(um_s32(&b_a_full[b]));
             }
         }
     } else {
-        // ------------------------------ epilogue (warps 4-7) ------------------------------
+        // ------------------------------ epilogue (four warps, one TMEM lane quarter each) ------------------------------
         const int q = warp & 3;                                         // TMEM lane quarter of this warp
         const int trow = q * 32 + lane;                                 // tile row held by this thread
         unsigned tile = 0;
@@ -348,7 +343,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 9) {
+    if (warp == UM_DQ_WARPS + 5) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(256) : "memory");
     }
@@ -412,7 +407,7 @@ int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_h
         if (um_make_map(&th[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act_hi, a.KD, a.max_rows, 64, R[i], CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
         if (um_make_map(&tl[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act_lo, a.KD, a.max_rows, 64, R[i], CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
     }
-    constexpr int SMEM = UM_STAGES * UM_STAGE_BYTES + 2 * UM_A16 + 1024;
+    constexpr int SMEM = UM_STAGES * UM_STAGE_BYTES + UM_ABUF * UM_A16 + 1024;
     static bool attr = false;
     if (!attr) {
         if (cudaFuncSetAttribute(k_q4_umma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
@@ -429,6 +424,219 @@ int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_h
     if (grid < 1) grid = 1;
     if (gateup) k_q4_umma<true><<<(unsigned)grid, UM_THREADS, SMEM, c.stream>>>(tw, th[0], th[1], th[2], th[3], tl[0], tl[1], tl[2], tl[3], ka);
     else k_q4_umma<false><<<(unsigned)grid, UM_THREADS, SMEM, c.stream>>>(tw, th[0], th[1], th[2], th[3], tl[0], tl[1], tl[2], tl[3], ka);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// ===========================================================================
+// Dense bf16 shared expert on tcgen05 for many token rows (prefill).
+// Same pipeline without the dequantise stage: the bf16 weight tile arrives by TMA
+// already in the layout the tensor core reads (64 columns x 128 rows, 128B
+// swizzle); the activations are two bf16 terms (x = hi + lo) in planar [T, K]
+// arrays.  Gate rows fill tile rows 0..63 and up rows 64..127, so the epilogue
+// warps of the upper half hand their values to the lower half through shared
+// memory.  Work item = (m-tile, chunk of 128 token rows).
+// ===========================================================================
+#define UB_STAGES 4
+#define UB_STAGE_BYTES (3 * UM_BT)
+#define UB_THREADS (6 * 32)
+
+__global__ void __launch_bounds__(256)
+k_pack_bf16_planar(const float *__restrict__ x, __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo, size_t n8) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n8; idx += (size_t)gridDim.x * blockDim.x) {
+        const float4 *src = reinterpret_cast<const float4 *>(x) + idx * 2;
+        const float4 a = src[0], b = src[1];
+        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        __nv_bfloat16 h[8], l[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) { h[i] = __float2bfloat16_rn(v[i]); l[i] = __float2bfloat16_rn(v[i] - __bfloat162float(h[i])); }
+        reinterpret_cast<uint4 *>(hi)[idx] = *reinterpret_cast<uint4 *>(h);
+        reinterpret_cast<uint4 *>(lo)[idx] = *reinterpret_cast<uint4 *>(l);
+    }
+}
+
+struct UbArgs { void *Y0, *Y1; int T, KD, O; int *status; };
+
+template <bool GATEUP>
+__global__ void __launch_bounds__(UB_THREADS, 1)
+k_bf16_umma(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmW1,
+            const __grid_constant__ CUtensorMap tmH, const __grid_constant__ CUtensorMap tmL, const UbArgs a) {
+    extern __shared__ unsigned char um_dyn[];
+    __shared__ unsigned long long b_full[UB_STAGES], b_free[UB_STAGES], b_acc_full[2], b_acc_free[2];
+    __shared__ unsigned s_tmem;
+    __shared__ int s_abort;
+    __shared__ float s_ex[64][33];                                       // up values of one 32-column block
+    unsigned char *smem = (unsigned char *)(((uintptr_t)um_dyn + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int T = a.T, KD = a.KD, O = a.O;
+    constexpr int OPT = GATEUP ? 64 : 128;
+    const int mtiles = (O + OPT - 1) / OPT, chunks = (T + 127) >> 7;
+    const int items = mtiles * chunks;
+    const int NST = KD >> 6;
+    volatile int *abortp = &s_abort;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < UB_STAGES; i++) { um_bar_init(um_s32(&b_full[i]), 1); um_bar_init(um_s32(&b_free[i]), 1); }
+        for (int i = 0; i < 2; i++) { um_bar_init(um_s32(&b_acc_full[i]), 1); um_bar_init(um_s32(&b_acc_free[i]), 4); }
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(um_s32(&s_tmem)), "r"(256) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem = s_tmem;
+
+    if (warp == 4) {
+        if (lane == 0) {                                                 // TMA producer
+            unsigned kk = 0;
+            for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
+                const int ci = item / mtiles, mt = item - ci * mtiles;   // m-tiles of one chunk are neighbours: the chunk stays in L2
+                for (int st = 0; st < NST; st++, kk++) {
+                    const int s = kk % UB_STAGES;
+                    if (kk >= UB_STAGES && !um_bar_wait(um_s32(&b_free[s]), ((kk / UB_STAGES) - 1) & 1, abortp)) {
+                        atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break;
+                    }
+                    unsigned char *sp = smem + s * UB_STAGE_BYTES;
+                    const unsigned bar = um_s32(&b_full[s]);
+                    um_bar_expect(bar, 3u * UM_BT);
+                    if (GATEUP) {
+                        um_tma_2d(um_s32(sp), &tmW0, st * 64, mt * 64, bar);
+                        um_tma_2d(um_s32(sp + UM_BT / 2), &tmW1, st * 64, mt * 64, bar);
+                    } else {
+                        um_tma_2d(um_s32(sp), &tmW0, st * 64, mt * 128, bar);
+                    }
+                    um_tma_2d(um_s32(sp + UM_BT), &tmH, st * 64, ci * 128, bar);
+                    um_tma_2d(um_s32(sp + 2 * UM_BT), &tmL, st * 64, ci * 128, bar);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {                                                 // MMA issuer
+            unsigned kk = 0, tile = 0;
+            for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, tile++) {
+                const int ci = item / mtiles;
+                const int n = min(128, T - ci * 128), N = (n + 15) & ~15;
+                const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(N >> 3) << 17) | ((128u >> 4) << 24);  // f32 accum, bf16 x bf16
+                const unsigned acc = tile & 1, d_tmem = tmem + acc * 128;
+                if (tile >= 2 && !um_bar_wait(um_s32(&b_acc_free[acc]), ((tile >> 1) - 1) & 1, abortp)) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int st = 0; st < NST; st++, kk++) {
+                    const int s = kk % UB_STAGES;
+                    if (!um_bar_wait(um_s32(&b_full[s]), (kk / UB_STAGES) & 1, abortp)) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned char *sp = smem + s * UB_STAGE_BYTES;
+                    const uint64_t da = um_desc(um_s32(sp)), dh = um_desc(um_s32(sp + UM_BT)), dl = um_desc(um_s32(sp + 2 * UM_BT));
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        um_mma(d_tmem, da + 2 * k, dh + 2 * k, idesc, (st | k) ? 1u : 0u);
+                        um_mma(d_tmem, da + 2 * k, dl + 2 * k, idesc, 1u);
+                    }
+                    um_commit(um_s32(&b_free[s]));
+                }
+                if (*abortp) break;
+                um_commit(um_s32(&b_acc_full[acc]));
+            }
+        }
+    } else {
+        // epilogue warps 0-3: warp q owns accumulator rows 32q..32q+31
+        const int q = warp, trow = q * 32 + lane;
+        unsigned tile = 0;
+        for (int item = blockIdx.x; item < items; item += gridDim.x, tile++) {
+            const int ci = item / mtiles, mt = item - ci * mtiles;
+            const int n = min(128, T - ci * 128), row0 = ci * 128;
+            const unsigned acc = tile & 1;
+            bool ok = !*abortp && um_bar_wait(um_s32(&b_acc_full[acc]), (tile >> 1) & 1, abortp);
+            if (!ok && lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; }
+            // the four warps stay in step through the named barrier even on an abort
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int cb = 0; cb < 128; cb += 32) {
+                float v[32];
+                if (ok && cb < n) um_ld32(tmem + acc * 128 + cb + ((unsigned)(q * 32) << 16), v);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[j] = 0.f;
+                }
+                if (GATEUP) {
+                    if (q >= 2) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) s_ex[trow - 64][j] = v[j];
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (q < 2 && ok) {
+                        const int o = mt * 64 + trow;
+                        __nv_bfloat16 *Yh = reinterpret_cast<__nv_bfloat16 *>(a.Y0), *Yl = reinterpret_cast<__nv_bfloat16 *>(a.Y1);
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            if (cb + j < n && o < O) {
+                                const float gv = v[j], uv = s_ex[trow][j];
+                                const float y = (gv / (1.f + expf(-gv))) * uv;
+                                const __nv_bfloat16 hi = __float2bfloat16_rn(y), lo = __float2bfloat16_rn(y - __bfloat162float(hi));
+                                const size_t pos = (size_t)(row0 + cb + j) * O + o;
+                                Yh[pos] = hi; Yl[pos] = lo;
+                            }
+                        }
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                } else if (ok) {
+                    float *Y = reinterpret_cast<float *>(a.Y0);
+                    const int o = mt * 128 + trow;
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (cb + j < n && o < O) Y[(size_t)(row0 + cb + j) * O + o] = v[j];
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) um_bar_arrive(um_s32(&b_acc_free[acc]));
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 5) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(256) : "memory");
+    }
+}
+
+int sw_launch_pack_bf16_planar(const SwLaunchCfg &c, const float *x, void *hi, void *lo, int rows, int KD) {
+    if (rows <= 0) return 0;
+    if (KD % 8) return -1;
+    size_t n8 = (size_t)rows * (KD / 8);
+    long long grid = (long long)((n8 + 255) / 256);
+    if (grid > (long long)c.num_sms * 16) grid = (long long)c.num_sms * 16;
+    k_pack_bf16_planar<<<(unsigned)grid, 256, 0, c.stream>>>(x, (__nv_bfloat16 *)hi, (__nv_bfloat16 *)lo, n8);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// W0 (and W1 for gate/up): bf16 [O, KD]; act_hi/lo: bf16 [T, KD]; gate/up -> Y0/Y1 bf16 hi/lo [T, O]; down -> Y0 f32 [T, O]
+int sw_launch_bf16_umma(const SwLaunchCfg &c, const void *W0, const void *W1, const void *act_hi, const void *act_lo,
+                        void *Y0, void *Y1, int T, int KD, int O, int *status, bool gateup) {
+    if (T <= 0 || O <= 0) return 0;
+    if (KD % 64 || (((uintptr_t)W0 | (uintptr_t)(W1 ? W1 : W0)) & 15)) return -1;
+    CUtensorMap tw0, tw1, th, tl;
+    const int wrows = gateup ? 64 : 128;
+    if (um_make_map(&tw0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W0, KD, O, 64, wrows, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+    if (um_make_map(&tw1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, gateup ? W1 : W0, KD, O, 64, wrows, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+    if (um_make_map(&th, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, act_hi, KD, T, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+    if (um_make_map(&tl, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, act_lo, KD, T, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+    constexpr int SMEM = UB_STAGES * UB_STAGE_BYTES + 1024;
+    static bool attr = false;
+    if (!attr) {
+        if (cudaFuncSetAttribute(k_bf16_umma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(k_bf16_umma<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
+        attr = true;
+    }
+    UbArgs ka{Y0, Y1, T, KD, O, status};
+    const int opt = gateup ? 64 : 128;
+    long long items = (long long)((O + opt - 1) / opt) * ((T + 127) / 128);
+    long long grid = c.num_sms < items ? c.num_sms : items;
+    if (gateup) k_bf16_umma<true><<<(unsigned)grid, UB_THREADS, SMEM, c.stream>>>(tw0, tw1, th, tl, ka);
+    else k_bf16_umma<false><<<(unsigned)grid, UB_THREADS, SMEM, c.stream>>>(tw0, tw1, th, tl, ka);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
