@@ -162,7 +162,7 @@ struct UmArgs {
 
 template <bool GATEUP>
 __global__ void __launch_bounds__(UM_THREADS, 1)
-k_q4_umma(const __grid_constant__ CUtensorMap tmW,
+k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmW2, const __grid_constant__ CUtensorMap tmW4,
           const __grid_constant__ CUtensorMap tmH16, const __grid_constant__ CUtensorMap tmH32,
           const __grid_constant__ CUtensorMap tmH64, const __grid_constant__ CUtensorMap tmH128,
           const __grid_constant__ CUtensorMap tmL16, const __grid_constant__ CUtensorMap tmL32,
@@ -185,13 +185,13 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < UM_STAGES; i++) { um_bar_init(um_s32(&b_raw_full[i]), 1); um_bar_init(um_s32(&b_raw_free[i]), 1); }
-        for (int i = 0; i < UM_ABUF; i++) { um_bar_init(um_s32(&b_a_full[i]), UM_DQ_WARPS); um_bar_init(um_s32(&b_a_free[i]), 1); }
+        for (int i = 0; i < UM_ABUF; i++) { um_bar_init(um_s32(&b_a_full[i]), UM_DQ_WARPS / UM_ABUF); um_bar_init(um_s32(&b_a_free[i]), 1); }
         for (int i = 0; i < 2; i++) { um_bar_init(um_s32(&b_acc_full[i]), 1); um_bar_init(um_s32(&b_acc_free[i]), 4); }
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == UM_DQ_WARPS + 5) {                                      // tensor memory: two 128-column accumulators
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(um_s32(&s_tmem)), "r"(256) : "memory");
+    if (warp == UM_DQ_WARPS + 5) {                                      // tensor memory: two 256-column accumulators (hi | lo halves)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(um_s32(&s_tmem)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -205,6 +205,12 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
         const int2 c = a.chunks[ch]; gi = c.x; c0 = c.y;
     };
 
+    // Small token tiles pack several 64-column sub-stages into one ring slot (one barrier round trip and
+    // one weight TMA per 128 or 256 columns): 4 sub-stages for <=16 rows, 2 for <=32, else 1.
+    // Slot layout: [raw int4: 128 rows x 32*KSUB B] then per sub-stage [hi tile: R x 128 B][lo tile: R x 128 B]
+    auto tile_rows = [](int n) { return n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : 128; };
+    auto substages = [&](int R) { return (R == 16 && (NST & 3) == 0) ? 4 : (R <= 32 && (NST & 1) == 0) ? 2 : 1; };
+
     if (warp == UM_DQ_WARPS + 4) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
@@ -212,57 +218,64 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
             for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
                 int gi, c0, mt; decode(item, gi, c0, mt);
                 const int e = a.gexp[gi] - a.expert_lo, n = min(128, a.gcnt[gi] - c0), row0 = a.gbeg[gi] + c0;
-                const int R = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : 128;
+                const int R = tile_rows(n), KSUB = substages(R);
                 const CUtensorMap *th = R == 16 ? &tmH16 : R == 32 ? &tmH32 : R == 64 ? &tmH64 : &tmH128;
                 const CUtensorMap *tl = R == 16 ? &tmL16 : R == 32 ? &tmL32 : R == 64 ? &tmL64 : &tmL128;
+                const CUtensorMap *tw = KSUB == 4 ? &tmW4 : KSUB == 2 ? &tmW2 : &tmW;
                 const int wrow = e * nrows_w + mt * OPT;
-                for (int st = 0; st < NST; st++, kk++) {
+                const unsigned rawA = 4096u * KSUB, bt = (unsigned)R * 128u;
+                for (int sl = 0; sl < NST / KSUB; sl++, kk++) {
                     const int s = kk % UM_STAGES;
                     if (kk >= UM_STAGES && !um_bar_wait(um_s32(&b_raw_free[s]), ((kk / UM_STAGES) - 1) & 1, abortp)) {
                         atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break;
                     }
                     unsigned char *sp = smem + s * UM_STAGE_BYTES;
                     const unsigned bar = um_s32(&b_raw_full[s]);
-                    um_bar_expect(bar, (unsigned)UM_RAW_A + 2u * (unsigned)R * 128u);
+                    um_bar_expect(bar, rawA + 2u * KSUB * bt);
                     if (GATEUP) {
-                        um_tma_2d(um_s32(sp), &tmW, st * 32, wrow, bar);                      // 64 gate rows
-                        um_tma_2d(um_s32(sp + UM_RAW_A / 2), &tmW, st * 32, wrow + OUT, bar); // 64 up rows
+                        um_tma_2d(um_s32(sp), tw, sl * 32 * KSUB, wrow, bar);                 // 64 gate rows
+                        um_tma_2d(um_s32(sp + rawA / 2), tw, sl * 32 * KSUB, wrow + OUT, bar); // 64 up rows
                     } else {
-                        um_tma_2d(um_s32(sp), &tmW, st * 32, wrow, bar);
+                        um_tma_2d(um_s32(sp), tw, sl * 32 * KSUB, wrow, bar);
                     }
-                    um_tma_2d(um_s32(sp + UM_RAW_A), th, st * 64, row0, bar);
-                    um_tma_2d(um_s32(sp + UM_RAW_A + UM_BT), tl, st * 64, row0, bar);
+                    for (int u = 0; u < KSUB; u++) {
+                        um_tma_2d(um_s32(sp + rawA + (2 * u) * bt), th, (sl * KSUB + u) * 64, row0, bar);
+                        um_tma_2d(um_s32(sp + rawA + (2 * u + 1) * bt), tl, (sl * KSUB + u) * 64, row0, bar);
+                    }
                 }
             }
         }
     } else if (warp == UM_DQ_WARPS + 5) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            unsigned kk = 0, tile = 0;
+            unsigned kk = 0, ks = 0, tile = 0;                          // sub-stage, ring-slot and tile counters
             for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, tile++) {
                 int gi, c0, mt; decode(item, gi, c0, mt);
                 const int n = min(128, a.gcnt[gi] - c0);
-                const int N = (n + 15) & ~15;
-                const unsigned idesc = (1u << 4) | ((unsigned)(N >> 3) << 17) | ((128u >> 4) << 24);   // f32 accum, f16 x f16, K-major
-                const unsigned acc = tile & 1, d_tmem = tmem + acc * 128;
+                // hi and lo activation tiles lie back to back, so ONE MMA with N = 2R multiplies both: accumulator
+                // columns [0,R) hold A*hi, [R,2R) hold A*lo.  (A tcgen05.mma of M=128, K=16 occupies the tensor
+                // pipe for ~155 cycles whatever its N up to 256, so the second half of the columns is free.)
+                const int R = tile_rows(n), KSUB = substages(R);
+                const unsigned idesc = (1u << 4) | ((unsigned)((2 * R) >> 3) << 17) | ((128u >> 4) << 24);   // f32 accum, f16 x f16, K-major
+                const unsigned acc = tile & 1, d_tmem = tmem + acc * 256;
                 if (tile >= 2 && !um_bar_wait(um_s32(&b_acc_free[acc]), ((tile >> 1) - 1) & 1, abortp)) {
                     atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned rawA = 4096u * KSUB, bt = (unsigned)R * 128u;
                 for (int st = 0; st < NST; st++, kk++) {
-                    const int s = kk % UM_STAGES, b = kk % UM_ABUF;
+                    const int u = st % KSUB, b = kk % UM_ABUF;
+                    const int s = ks % UM_STAGES;
                     if (!um_bar_wait(um_s32(&b_a_full[b]), (kk / UM_ABUF) & 1, abortp)) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned char *sp = smem + s * UM_STAGE_BYTES;
                     const uint64_t da = um_desc(um_s32(a16 + b * UM_A16));
-                    const uint64_t dh = um_desc(um_s32(smem + s * UM_STAGE_BYTES + UM_RAW_A));
-                    const uint64_t dl = um_desc(um_s32(smem + s * UM_STAGE_BYTES + UM_RAW_A + UM_BT));
+                    const uint64_t db = um_desc(um_s32(sp + rawA + (2 * u) * bt));
 #pragma unroll
-                    for (int k = 0; k < 4; k++) {                       // 16 columns = 32 bytes per step
-                        um_mma(d_tmem, da + 2 * k, dh + 2 * k, idesc, (st | k) ? 1u : 0u);
-                        um_mma(d_tmem, da + 2 * k, dl + 2 * k, idesc, 1u);
-                    }
+                    for (int k = 0; k < 4; k++)                         // 16 columns = 32 bytes per step
+                        um_mma(d_tmem, da + 2 * k, db + 2 * k, idesc, (st | k) ? 1u : 0u);
                     um_commit(um_s32(&b_a_free[b]));
-                    um_commit(um_s32(&b_raw_free[s]));
+                    if (u == KSUB - 1) { um_commit(um_s32(&b_raw_free[s])); ks++; }
                 }
                 if (*abortp) break;
                 um_commit(um_s32(&b_acc_full[acc]));
@@ -270,27 +283,50 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
         }
     } else if (warp < UM_DQ_WARPS) {
         // ------------------------------ dequantise ------------------------------
-        const int r = threadIdx.x >> 1, h = threadIdx.x & 1;            // tile row 0..127, which 16 raw bytes of it
-        unsigned kk = 0;
+        // Four groups of two warps; group g dequantises the sub-stages kk with kk % 4 == g into A tile g, so four
+        // sub-stages are in flight at once (the chain wait -> load -> convert -> store -> fence -> arrive is long).
+        // Thread t of a group owns tile rows t and t+64.
+        const int grp = warp >> 1, tg = threadIdx.x & 63;
+        unsigned kk = 0, slot_base = 0;
         for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
+            int gi, c0, mt; decode(item, gi, c0, mt);
+            const int R = tile_rows(min(128, a.gcnt[gi] - c0)), KSUB = substages(R);
+            const int pitch = 32 * KSUB;                                // bytes per raw row in the slot
+            int rowoff[2];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const int r = tg + 64 * i;
+                rowoff[i] = GATEUP ? (r & 1) * (64 * pitch) + (r >> 1) * pitch : r * pitch;
+            }
             for (int st = 0; st < NST; st++, kk++) {
-                const int s = kk % UM_STAGES, b = kk % UM_ABUF;
-                bool ok = um_bar_wait(um_s32(&b_raw_full[s]), (kk / UM_STAGES) & 1, abortp);
-                if (ok && kk >= UM_ABUF) ok = um_bar_wait(um_s32(&b_a_free[b]), ((kk / UM_ABUF) - 1) & 1, abortp);
+                if ((kk & 3) != (unsigned)grp) continue;
+                const int u = st % KSUB;
+                const unsigned ks = slot_base + st / KSUB;
+                const int s = ks % UM_STAGES;
+                bool ok = um_bar_wait(um_s32(&b_raw_full[s]), (ks / UM_STAGES) & 1, abortp);
+                if (ok && kk >= UM_ABUF) ok = um_bar_wait(um_s32(&b_a_free[grp]), ((kk / UM_ABUF) - 1) & 1, abortp);
                 if (!ok) { if (lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; } break; }
-                const unsigned char *raw = smem + s * UM_STAGE_BYTES;
-                const uint4 w = GATEUP ? *reinterpret_cast<const uint4 *>(raw + (r & 1) * (UM_RAW_A / 2) + (r >> 1) * 32 + h * 16)
-                                       : *reinterpret_cast<const uint4 *>(raw + r * 32 + h * 16);
-                unsigned char *dst = a16 + b * UM_A16 + r * 128;
-                const int x7 = r & 7, c0 = h * 4;
-                *reinterpret_cast<uint4 *>(dst + (((c0 + 0) ^ x7) << 4)) = um_dq(w.x);
-                *reinterpret_cast<uint4 *>(dst + (((c0 + 1) ^ x7) << 4)) = um_dq(w.y);
-                *reinterpret_cast<uint4 *>(dst + (((c0 + 2) ^ x7) << 4)) = um_dq(w.z);
-                *reinterpret_cast<uint4 *>(dst + (((c0 + 3) ^ x7) << 4)) = um_dq(w.w);
+                const unsigned char *raw = smem + s * UM_STAGE_BYTES + u * 32;
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const int r = tg + 64 * i, x7 = r & 7;
+                    const uint4 w0 = *reinterpret_cast<const uint4 *>(raw + rowoff[i]);
+                    const uint4 w1 = *reinterpret_cast<const uint4 *>(raw + rowoff[i] + 16);
+                    unsigned char *dst = a16 + grp * UM_A16 + r * 128;
+                    *reinterpret_cast<uint4 *>(dst + ((0 ^ x7) << 4)) = um_dq(w0.x);
+                    *reinterpret_cast<uint4 *>(dst + ((1 ^ x7) << 4)) = um_dq(w0.y);
+                    *reinterpret_cast<uint4 *>(dst + ((2 ^ x7) << 4)) = um_dq(w0.z);
+                    *reinterpret_cast<uint4 *>(dst + ((3 ^ x7) << 4)) = um_dq(w0.w);
+                    *reinterpret_cast<uint4 *>(dst + ((4 ^ x7) << 4)) = um_dq(w1.x);
+                    *reinterpret_cast<uint4 *>(dst + ((5 ^ x7) << 4)) = um_dq(w1.y);
+                    *reinterpret_cast<uint4 *>(dst + ((6 ^ x7) << 4)) = um_dq(w1.z);
+                    *reinterpret_cast<uint4 *>(dst + ((7 ^ x7) << 4)) = um_dq(w1.w);
+                }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic stores -> tensor-core reads
                 __syncwarp();
-                if (lane == 0) um_bar_arrive(um_s32(&b_a_full[b]));
+                if (lane == 0) um_bar_arrive(um_s32(&b_a_full[grp]));
             }
+            slot_base += NST / KSUB;
         }
     } else {
         // ------------------------------ epilogue (four warps, one TMEM lane quarter each) ------------------------------
@@ -311,9 +347,13 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
             int o;                                                      // output index of this thread's row
             if (GATEUP) { o = mt * 64 + (trow >> 1); sc = o < OUT ? ws[(trow & 1) * OUT + o] : 0.f; }
             else        { o = mt * 128 + trow;       sc = o < OUT ? ws[o] : 0.f; }
+            const int R = tile_rows(n);
             for (int cb = 0; cb < n; cb += 32) {
-                float v[32];
-                um_ld32(tmem + acc * 128 + cb + ((unsigned)(q * 32) << 16), v);
+                float v[32], p[32];
+                um_ld32(tmem + acc * 256 + cb + ((unsigned)(q * 32) << 16), v);          // A * hi
+                um_ld32(tmem + acc * 256 + R + cb + ((unsigned)(q * 32) << 16), p);      // A * lo
+#pragma unroll
+                for (int j = 0; j < 32; j++) v[j] += p[j];
                 if (GATEUP) {
                     __half *Yh = reinterpret_cast<__half *>(a.Y0), *Yl = reinterpret_cast<__half *>(a.Y1);
                     const int pcol = um_perm8(o);
@@ -345,7 +385,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
     __syncthreads();
     if (warp == UM_DQ_WARPS + 5) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(256) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(512) : "memory");
     }
 }
 
@@ -400,8 +440,10 @@ int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_h
                       const int *nchunks, const void *chunks, int max_chunks, int *status, long long wrows_total, bool gateup) {
     if (a.max_rows <= 0) return 0;
     if (a.KD % 64 || a.OUT <= 0 || ((uintptr_t)a.q & 15)) return -1;
-    CUtensorMap tw, th[4], tl[4];
+    CUtensorMap tw, tw2, tw4, th[4], tl[4];
     if (um_make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.q, a.KD / 2, wrows_total, 32, gateup ? 64 : 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
+    if (um_make_map(&tw2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.q, a.KD / 2, wrows_total, 64, gateup ? 64 : 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
+    if (um_make_map(&tw4, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.q, a.KD / 2, wrows_total, 128, gateup ? 64 : 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
     const int R[4] = {16, 32, 64, 128};
     for (int i = 0; i < 4; i++) {
         if (um_make_map(&th[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act_hi, a.KD, a.max_rows, 64, R[i], CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
@@ -422,8 +464,8 @@ int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_h
     long long grid = c.num_sms;                        // one CTA per SM (shared memory and tensor memory are sized for that)
     if (grid > items) grid = items;
     if (grid < 1) grid = 1;
-    if (gateup) k_q4_umma<true><<<(unsigned)grid, UM_THREADS, SMEM, c.stream>>>(tw, th[0], th[1], th[2], th[3], tl[0], tl[1], tl[2], tl[3], ka);
-    else k_q4_umma<false><<<(unsigned)grid, UM_THREADS, SMEM, c.stream>>>(tw, th[0], th[1], th[2], th[3], tl[0], tl[1], tl[2], tl[3], ka);
+    if (gateup) k_q4_umma<true><<<(unsigned)grid, UM_THREADS, SMEM, c.stream>>>(tw, tw2, tw4, th[0], th[1], th[2], th[3], tl[0], tl[1], tl[2], tl[3], ka);
+    else k_q4_umma<false><<<(unsigned)grid, UM_THREADS, SMEM, c.stream>>>(tw, tw2, tw4, th[0], th[1], th[2], th[3], tl[0], tl[1], tl[2], tl[3], ka);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
@@ -482,7 +524,7 @@ k_bf16_umma(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CU
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 5) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(um_s32(&s_tmem)), "r"(256) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(um_s32(&s_tmem)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -519,9 +561,9 @@ k_bf16_umma(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CU
             unsigned kk = 0, tile = 0;
             for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, tile++) {
                 const int ci = item / mtiles;
-                const int n = min(128, T - ci * 128), N = (n + 15) & ~15;
-                const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(N >> 3) << 17) | ((128u >> 4) << 24);  // f32 accum, bf16 x bf16
-                const unsigned acc = tile & 1, d_tmem = tmem + acc * 128;
+                // hi and lo tiles are adjacent: one N=256 MMA per step, columns [0,128) = A*hi, [128,256) = A*lo
+                const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);  // f32 accum, bf16 x bf16
+                const unsigned acc = tile & 1, d_tmem = tmem + acc * 256;
                 if (tile >= 2 && !um_bar_wait(um_s32(&b_acc_free[acc]), ((tile >> 1) - 1) & 1, abortp)) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 for (int st = 0; st < NST; st++, kk++) {
@@ -529,12 +571,9 @@ k_bf16_umma(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CU
                     if (!um_bar_wait(um_s32(&b_full[s]), (kk / UB_STAGES) & 1, abortp)) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const unsigned char *sp = smem + s * UB_STAGE_BYTES;
-                    const uint64_t da = um_desc(um_s32(sp)), dh = um_desc(um_s32(sp + UM_BT)), dl = um_desc(um_s32(sp + 2 * UM_BT));
+                    const uint64_t da = um_desc(um_s32(sp)), db = um_desc(um_s32(sp + UM_BT));
 #pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        um_mma(d_tmem, da + 2 * k, dh + 2 * k, idesc, (st | k) ? 1u : 0u);
-                        um_mma(d_tmem, da + 2 * k, dl + 2 * k, idesc, 1u);
-                    }
+                    for (int k = 0; k < 4; k++) um_mma(d_tmem, da + 2 * k, db + 2 * k, idesc, (st | k) ? 1u : 0u);
                     um_commit(um_s32(&b_free[s]));
                 }
                 if (*abortp) break;
@@ -555,8 +594,13 @@ k_bf16_umma(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CU
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             for (int cb = 0; cb < 128; cb += 32) {
                 float v[32];
-                if (ok && cb < n) um_ld32(tmem + acc * 128 + cb + ((unsigned)(q * 32) << 16), v);
-                else {
+                if (ok && cb < n) {
+                    float p[32];
+                    um_ld32(tmem + acc * 256 + cb + ((unsigned)(q * 32) << 16), v);
+                    um_ld32(tmem + acc * 256 + 128 + cb + ((unsigned)(q * 32) << 16), p);
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[j] += p[j];
+                } else {
 #pragma unroll
                     for (int j = 0; j < 32; j++) v[j] = 0.f;
                 }
@@ -598,7 +642,7 @@ k_bf16_umma(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CU
     __syncthreads();
     if (warp == 5) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(256) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(512) : "memory");
     }
 }
 
