@@ -155,7 +155,7 @@ int  sw_moe_finish(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer
  * scratch with cudaMalloc on demand, c/backend_cuda_laguna.cu:471-493): router
  * logits -> gate -> top-k -> combine weights for T <= 8 rows, n_experts <= 512,
  * D <= 8192 (D % 32 == 0).  x [T,D] f32, sel [T*K] int32 and w [T*K] f32 are device
- * buffers owned by the caller; the working memory is a fixed ~1.1 MB array inside
+ * buffers owned by the caller; the working memory is a fixed ~2.1 MB array inside
  * the library image that every GPU loading the library keeps until exit.  Meant
  * for hosts that cannot allocate when they need a routing decision (all free
  * device memory already given away, or no tolerance for the device-wide

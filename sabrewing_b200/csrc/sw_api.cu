@@ -124,7 +124,7 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
         T * D * 4,            // spk
         P * D * 4,            // um.xg: gathered fp16 hi + lo token rows
         (P / 128 + E + 64) * 8 + 256,   // um.chunks + nchunks
-        ((size_t)((D + 255) / 256) * (T < 128 ? T : 128) + ((size_t)c->num_sms * 16 * 256 + E - 1) / E + T + 64) * E * 8   // rpart
+        ((size_t)((D + 127) / 128) * (T < 128 ? T : 128) + ((size_t)c->num_sms * 32 * 256 + E - 1) / E + T + 64) * E * 8   // rpart
     };
     size_t total = 0; for (size_t s : sizes) total += sw_align(s);
     if (cudaMalloc(&c->block, total) != cudaSuccess) {

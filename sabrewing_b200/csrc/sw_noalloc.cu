@@ -8,7 +8,7 @@
 // implies.  For them this one entry point takes caller-owned input and output
 // buffers and keeps its working memory in a fixed array that is part of the
 // library image: every GPU that loads the library reserves SW_STATIC_BYTES
-// (about 1.1 MB) until the process exits.
+// (about 2.1 MB) until the process exits.
 //
 // It is ONE kernel: every CTA writes fp64 partial router logits for its slice of
 // the contraction into the fixed array, takes a ticket from a counter in the same
@@ -37,7 +37,7 @@
 #define SW_STATIC_MAX_T 8
 #define SW_STATIC_MAX_E 512
 #define SW_STATIC_MAX_D 8192
-#define SW_STATIC_MAX_SLICES (SW_STATIC_MAX_D / 256)
+#define SW_STATIC_MAX_SLICES (SW_STATIC_MAX_D / 128)      // sw_router_slices never cuts finer than 128 columns
 #define SW_STATIC_PART_BYTES ((size_t)SW_STATIC_MAX_SLICES * SW_STATIC_MAX_T * SW_STATIC_MAX_E * 8)
 #define SW_STATIC_BYTES (SW_STATIC_PART_BYTES + 256)
 
@@ -202,6 +202,7 @@ extern "C" int sw_moe_route_static(const SwMoeDesc *d, const SwMoeLayer *L, cons
     }
     const int E = d->n_experts;
     const int KS = sw_router_slices(g_static_dev[dev].sms, T, L->D, E);      // same slicing as sw_moe_route
+    if (KS > SW_STATIC_MAX_SLICES) return sw_noalloc_fail("route_static: slice count exceeds the fixed scratch array");
     const int slice = ((L->D + KS - 1) / KS + 31) & ~31;
     double *part = (double *)g_static_dev[dev].ptr;
     unsigned *ticket = (unsigned *)((unsigned char *)g_static_dev[dev].ptr + SW_STATIC_PART_BYTES);

@@ -95,31 +95,33 @@ __device__ __forceinline__ void sw_dmma(double (&c)[2], double a, double b) {
                  : "+d"(c[0]), "+d"(c[1]) : "d"(a), "d"(b));
 }
 
-template <typename WT>
+// NT = token n-tiles (of 8 rows) per warp item: 4 for large batches (weights re-used across 32 rows), 1 for
+// small batches, where more, shorter warp items hide the latency of the dependent fp64 MMA chains.
+template <typename WT, int NT>
 __global__ void __launch_bounds__(128)
 k_router_dmma(const float *__restrict__ x, const WT *__restrict__ W, double *__restrict__ part,
               int T, int D, int E, int KS, int slice) {
     const int lane = threadIdx.x & 31, r = lane >> 2, c = lane & 3;
     const int warps_total = gridDim.x * 4, wid = blockIdx.x * 4 + (threadIdx.x >> 5);
-    const int etiles = (E + 7) >> 3, passes = (T + 31) >> 5;
+    const int etiles = (E + 7) >> 3, passes = (T + 8 * NT - 1) / (8 * NT);
     const int items = etiles * passes * KS;
     for (int item = wid; item < items; item += warps_total) {
         const int ks = item % KS, rest = item / KS, et = rest % etiles, ps = rest / etiles;
         const int k0 = ks * slice, k1 = min(D, k0 + slice);
         const int e = min(et * 8 + r, E - 1);
         const WT *wr = W + (size_t)e * D + c * 8;
-        const float *xr[4];
+        const float *xr[NT];
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++) xr[nt] = x + (size_t)min(ps * 32 + nt * 8 + r, T - 1) * D + c * 8;
-        const int nt_used = min(4, (T - ps * 32 + 7) >> 3);
-        double acc[4][2];
+        for (int nt = 0; nt < NT; nt++) xr[nt] = x + (size_t)min(ps * 8 * NT + nt * 8 + r, T - 1) * D + c * 8;
+        const int nt_used = min(NT, (T - ps * 8 * NT + 7) >> 3);
+        double acc[NT][2];
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++) { acc[nt][0] = 0.0; acc[nt][1] = 0.0; }
+        for (int nt = 0; nt < NT; nt++) { acc[nt][0] = 0.0; acc[nt][1] = 0.0; }
         for (int k = k0; k < k1; k += 32) {
             float wv[8];
             sw_load8(wr + k, wv);
 #pragma unroll
-            for (int nt = 0; nt < 4; nt++) {
+            for (int nt = 0; nt < NT; nt++) {
                 if (nt < nt_used) {
                     float xv[8];
                     sw_load8(xr[nt] + k, xv);
@@ -131,11 +133,11 @@ k_router_dmma(const float *__restrict__ x, const WT *__restrict__ W, double *__r
         // C[row = expert r][col = token 2c, 2c+1]
         const int eo = et * 8 + r;
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++) {
+        for (int nt = 0; nt < NT; nt++) {
             if (nt >= nt_used || eo >= E) continue;
 #pragma unroll
             for (int j = 0; j < 2; j++) {
-                const int t = ps * 32 + nt * 8 + 2 * c + j;
+                const int t = ps * 8 * NT + nt * 8 + 2 * c + j;
                 if (t < T) part[((size_t)ks * T + t) * E + eo] = acc[nt][j];
             }
         }
@@ -144,9 +146,11 @@ k_router_dmma(const float *__restrict__ x, const WT *__restrict__ W, double *__r
 
 // Number of column slices the DMMA router uses for (T, E, D); the top-k kernel sums this many partials.
 int sw_router_slices(int num_sms, int T, int D, int E) {
-    const int etiles = (E + 7) / 8, passes = (T + 31) / 32;
-    int want = (num_sms * 16 + etiles * passes - 1) / (etiles * passes);
-    int maxs = (D + 255) / 256;
+    const int nt = T <= 64 ? 1 : 4;
+    const int etiles = (E + 7) / 8, passes = (T + 8 * nt - 1) / (8 * nt);
+    int want = (num_sms * 32 + etiles * passes - 1) / (etiles * passes);
+    int maxs = (D + 127) / 128;
+    if (nt == 4 && maxs > (D + 255) / 256) maxs = (D + 255) / 256;
     return want < 1 ? 1 : want > maxs ? maxs : want;
 }
 
@@ -154,13 +158,19 @@ int sw_launch_router_dmma(const SwLaunchCfg &c, const float *x, const void *W, i
                           int T, int D, int E, int KS) {
     if (T <= 0) return 0;
     if (D % 32) return -1;
-    const int etiles = (E + 7) / 8, passes = (T + 31) / 32;
+    const int nt = T <= 64 ? 1 : 4;
+    const int etiles = (E + 7) / 8, passes = (T + 8 * nt - 1) / (8 * nt);
     int slice = ((D + KS - 1) / KS + 31) & ~31;
     long long items = (long long)etiles * passes * KS, need = (items + 3) / 4;
     long long grid = (long long)c.num_sms * 8;
     if (grid > need) grid = need;
-    if (w_dtype == 1) k_router_dmma<__nv_bfloat16><<<(unsigned)grid, 128, 0, c.stream>>>(x, (const __nv_bfloat16 *)W, part, T, D, E, KS, slice);
-    else k_router_dmma<float><<<(unsigned)grid, 128, 0, c.stream>>>(x, (const float *)W, part, T, D, E, KS, slice);
+    if (w_dtype == 1) {
+        if (nt == 1) k_router_dmma<__nv_bfloat16, 1><<<(unsigned)grid, 128, 0, c.stream>>>(x, (const __nv_bfloat16 *)W, part, T, D, E, KS, slice);
+        else k_router_dmma<__nv_bfloat16, 4><<<(unsigned)grid, 128, 0, c.stream>>>(x, (const __nv_bfloat16 *)W, part, T, D, E, KS, slice);
+    } else {
+        if (nt == 1) k_router_dmma<float, 1><<<(unsigned)grid, 128, 0, c.stream>>>(x, (const float *)W, part, T, D, E, KS, slice);
+        else k_router_dmma<float, 4><<<(unsigned)grid, 128, 0, c.stream>>>(x, (const float *)W, part, T, D, E, KS, slice);
+    }
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
