@@ -109,6 +109,9 @@ typedef struct {
     const void  *dn_q; const float *dn_s;
     const void  *sh_gate, *sh_up, *sh_down;   /* bf16 [SI,D], [SI,D], [D,SI] or NULL */
     int expert_lo, expert_cnt; /* resident expert range; expert_cnt<=0 means all */
+    int gs;                    /* 0: one f32 scale per weight row (c/moe_quant.h:13-14).  >0 (multiple of 32):
+                                  one scale per gs columns, gu_s [E*2I, ceil(D/gs)], dn_s [E*D, ceil(I/gs)]
+                                  -- the reference's group-scaled int4, c/quant.h:167-202 */
 } SwMoeLayer;
 
 typedef struct SwMoeCtx SwMoeCtx;

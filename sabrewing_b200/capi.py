@@ -26,7 +26,7 @@ class SwMoeLayer(C.Structure):
                 ("router_w", C.c_void_p), ("corr_bias", C.c_void_p), ("logit_bias", C.c_void_p),
                 ("gu_q", C.c_void_p), ("gu_s", C.c_void_p), ("dn_q", C.c_void_p), ("dn_s", C.c_void_p),
                 ("sh_gate", C.c_void_p), ("sh_up", C.c_void_p), ("sh_down", C.c_void_p),
-                ("expert_lo", C.c_int), ("expert_cnt", C.c_int)]
+                ("expert_lo", C.c_int), ("expert_cnt", C.c_int), ("gs", C.c_int)]
 
 
 # name -> (restype, argtypes); every symbol include/sabrewing_b200.h declares

@@ -179,6 +179,7 @@ static int sw_check(const SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, 
         if (L->SI <= 0 || L->SI > c->maxSI || L->SI % 8) return sw_fail("SI=%d must be a multiple of 8 and <= %d", L->SI, c->maxSI);
         if (!L->sh_gate || !L->sh_up || !L->sh_down) return sw_fail("shared expert weights missing");
     }
+    if (L->gs < 0 || (L->gs > 0 && L->gs % 32)) return sw_fail("gs=%d must be 0 or a multiple of 32", L->gs);
     if (!L->router_w || !L->gu_q || !L->gu_s || !L->dn_q || !L->dn_s) return sw_fail("layer weights missing");
     if (L->router_dtype != SW_DTYPE_F32 && L->router_dtype != SW_DTYPE_BF16) return sw_fail("router_dtype=%d unknown", L->router_dtype);
     return 0;
@@ -221,7 +222,7 @@ static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, 
                           const void *dn_q, const float *dn_s, const float *x, int rows_x, void *xp,
                           float *glu, float *slots, float *sums, int *status, int D, int I,
                           void (*mark)(void *, int), void *mark_ctx, const SwUmmaScratch *um = nullptr) {
-    int path = sw_expert_path(D, I, a.max_rows, a.max_groups);
+    int path = a.gs > 0 ? 0 : sw_expert_path(D, I, a.max_rows, a.max_groups);   // group scales: CUDA-core kernels
     if (path >= 2 && (((uintptr_t)gu_q | (uintptr_t)dn_q) & 15)) path = 1;    // TMA wants 16-byte aligned blobs
     if (path == 3 && !um) path = 2;
     if (path == 3) {
@@ -285,6 +286,11 @@ static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, 
 static int sw_logits_topk(SwMoeCtx *c, const SwLaunchCfg &cfg, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, int T,
                           bool mark) {
     const int E = d->n_experts, K = d->topk;
+    // few pairs: the last CTA of the top-k kernel groups them (one launch less on the critical path);
+    // many pairs: the 1024-thread dispatch kernel
+    const bool fuse = (long long)T * K <= 4096;
+    const SwRouting *dr = fuse ? &c->r : nullptr;
+    unsigned *ticket = fuse ? (unsigned *)(c->r.status + 16) : nullptr;
     static int force_simt = -1;
     if (force_simt < 0) { const char *e = getenv("SW_FORCE_SIMT"); force_simt = (e && *e && *e != '0') ? 1 : 0; }
     if (!force_simt && L->D % 32 == 0) {
@@ -292,22 +298,22 @@ static int sw_logits_topk(SwMoeCtx *c, const SwLaunchCfg &cfg, const SwMoeDesc *
         if (sw_launch_router_dmma(cfg, x, L->router_w, L->router_dtype, c->rpart, T, L->D, E, KS)) return sw_fail("router launch failed");
         if (mark) sw_prof_mark(c, SW_ST_LOGITS, cfg.stream);
         if (sw_launch_route_topk(cfg, c->r.scores, c->rpart, KS, L->logit_bias, L->corr_bias, d->use_corr_bias, d->route_act,
-                                 d->norm_topk, T, E, K, c->r.sel, c->r.w)) return sw_fail("route_topk launch failed");
+                                 d->norm_topk, T, E, K, c->r.sel, c->r.w, dr, ticket)) return sw_fail("route_topk launch failed");
     } else {
         if (sw_launch_router_logits(cfg, x, L->router_w, L->router_dtype, L->logit_bias, c->r.scores, T, L->D, E)) return sw_fail("router_logits launch failed");
         if (mark) sw_prof_mark(c, SW_ST_LOGITS, cfg.stream);
         if (sw_launch_route_topk(cfg, c->r.scores, nullptr, 0, nullptr, L->corr_bias, d->use_corr_bias, d->route_act,
-                                 d->norm_topk, T, E, K, c->r.sel, c->r.w)) return sw_fail("route_topk launch failed");
+                                 d->norm_topk, T, E, K, c->r.sel, c->r.w, dr, ticket)) return sw_fail("route_topk launch failed");
     }
     if (mark) sw_prof_mark(c, SW_ST_TOPK, cfg.stream);
+    if (!fuse && sw_launch_dispatch(cfg, c->r, T, K, E)) return sw_fail("dispatch launch failed");
     return 0;
 }
 
 static int sw_route_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, int T, cudaStream_t st) {
     SwLaunchCfg cfg{c->num_sms, st};
     const int E = d->n_experts, K = d->topk;
-    if (sw_logits_topk(c, cfg, d, L, x, T, false)) return -1;
-    if (sw_launch_dispatch(cfg, c->r, T, K, E)) return sw_fail("dispatch launch failed");
+    if (sw_logits_topk(c, cfg, d, L, x, T, false)) return -1;      // the top-k kernel's last CTA also runs the dispatch
     c->last_stream = st; c->lastT = T; c->lastK = K; c->lastE = E;
     return 0;
 }
@@ -319,7 +325,7 @@ static int sw_expert_stage(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
     SwQ4Args a{};
     a.gexp = c->r.gexp; a.gbeg = c->r.gbeg; a.gcnt = c->r.gcnt; a.G = c->r.G; a.grow = c->r.grow;
     a.expert_lo = lo; a.expert_cnt = cnt;
-    a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K;
+    a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K; a.gs = L->gs;
     if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, nullptr, nullptr, &c->um))
         return sw_fail("expert launch failed");
     return 0;
@@ -427,15 +433,14 @@ extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
     }
 
     sw_prof_mark(c, -1, st);
-    if (sw_logits_topk(c, cfg, d, L, x, T, true)) return -1;
-    if (sw_launch_dispatch(cfg, c->r, T, K, E)) return sw_fail("dispatch launch failed");
+    if (sw_logits_topk(c, cfg, d, L, x, T, true)) return -1;       // the top-k kernel's last CTA also runs the dispatch
     sw_prof_mark(c, SW_ST_DISPATCH, st);
     c->last_stream = st; c->lastT = T; c->lastK = K; c->lastE = E;
 
     SwQ4Args a{};
     a.gexp = c->r.gexp; a.gbeg = c->r.gbeg; a.gcnt = c->r.gcnt; a.G = c->r.G; a.grow = c->r.grow;
     a.expert_lo = lo; a.expert_cnt = cnt;
-    a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K;
+    a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K; a.gs = L->gs;
     auto mark = [](void *p, int which) { MarkCtx *m = (MarkCtx *)p; sw_prof_mark(m->c, which == 0 ? SW_ST_GATEUP : SW_ST_DOWN, m->st); };
     if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, mark, &mc, &c->um))
         return sw_fail("expert launch failed");

@@ -42,7 +42,8 @@ int sw_launch_router_dmma(const SwLaunchCfg &c, const float *x, const void *W, i
 // part != NULL: logits are first formed as (float)(sum of KS fp64 partials [KS][T][E]) + lbias
 int sw_launch_route_topk(const SwLaunchCfg &c, float *scores, const double *part, int KS, const float *lbias,
                          const float *corr_bias, int use_bias,
-                         int route_act, int norm_topk, int T, int E, int K, int *sel, float *w);
+                         int route_act, int norm_topk, int T, int E, int K, int *sel, float *w,
+                         const SwRouting *dr = nullptr, unsigned *ticket = nullptr);
 int sw_launch_dispatch(const SwLaunchCfg &c, const SwRouting &r, int T, int K, int E);
 
 // sw_experts.cu
@@ -55,6 +56,7 @@ struct SwQ4Args {
     int expert_lo, expert_cnt;
     int max_groups;    // upper bound on *G known on the host
     int max_rows;      // upper bound on rows of all groups together (T*K)
+    int gs;            // 0: one scale per row; >0: one scale per gs columns (CUDA-core kernels only)
 };
 int sw_launch_q4_gateup(const SwLaunchCfg &c, const SwQ4Args &a);
 int sw_launch_q4_down(const SwLaunchCfg &c, const SwQ4Args &a);

@@ -20,14 +20,18 @@
 // grouping never changes a result bit (the reference's grouped-vs-per-token bar,
 // c/laguna.c:1620-1657).
 // ---------------------------------------------------------------------------
-template <bool GATEUP, int NC>
+// GS: scales are per group of `gs` columns (gs % 32 == 0), laid out [row, ceil(KD/gs)] like the reference's
+// group-scaled int4 (c/quant.h:167-202): each 32-column unit's partial dot is multiplied by its group's
+// scale before it is accumulated, and there is no final per-row multiply.
+template <bool GATEUP, int NC, bool GS>
 __global__ void __launch_bounds__(256)
 k_q4_group(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
            const float *__restrict__ X, float *__restrict__ Y,
            const int *__restrict__ gexp, const int *__restrict__ gbeg, const int *__restrict__ gcnt,
            const int *__restrict__ Gp, const int *__restrict__ grow,
-           int KD, int OUT, int rows_per_item, int expert_lo, int expert_cnt) {
+           int KD, int OUT, int rows_per_item, int expert_lo, int expert_cnt, int gs) {
     extern __shared__ float4 xs4[];              // [NC][8*UP] float4
+    const int ng = GS ? (KD + gs - 1) / gs : 1;  // scales per weight row
     const int U = KD >> 5;                       // 32-column units per row
     const int UP = U + 1;                        // padded stride between the 8 float4 planes
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -43,7 +47,7 @@ k_q4_group(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
         if (e < 0 || e >= expert_cnt) continue;
         const int n = gcnt[g], beg = gbeg[g];
         const uint8_t *wq = Wq + (size_t)e * nrows_w * rowbytes;
-        const float *ws = Ws + (size_t)e * nrows_w;
+        const float *ws = Ws + (size_t)e * nrows_w * ng;
         const int r_lo = rb * rows_per_item, r_hi = min(r_lo + rows_per_item, OUT);
 
         for (int c0 = 0; c0 < n; c0 += NC) {
@@ -65,7 +69,7 @@ k_q4_group(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
             constexpr int RW = 4;
             constexpr int OW = GATEUP ? 2 : 4;   // outputs per warp pass
             for (int o0 = r_lo + warp * OW; o0 < r_hi; o0 += 8 * OW) {
-                const uint8_t *rp[RW]; bool rv[RW];
+                const uint8_t *rp[RW]; bool rv[RW]; const float *rs[RW];
 #pragma unroll
                 for (int r = 0; r < RW; r++) {
                     int row, oi;
@@ -73,6 +77,7 @@ k_q4_group(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
                     else        { oi = o0 + r;       row = oi; }
                     rv[r] = oi < r_hi;
                     rp[r] = wq + (size_t)(rv[r] ? row : 0) * rowbytes;
+                    rs[r] = ws + (size_t)(rv[r] ? row : 0) * ng;
                 }
                 float acc[RW][NC];
 #pragma unroll
@@ -81,6 +86,16 @@ k_q4_group(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
                     for (int c = 0; c < NC; c++) acc[r][c] = 0.f;
 
                 for (int u = lane; u < U; u += 32) {
+                    float sgrp[RW], keep[RW][NC];
+                    if (GS) {
+                        const int g = (u * 32) / gs;
+#pragma unroll
+                        for (int r = 0; r < RW; r++) {
+                            sgrp[r] = rs[r][g];
+#pragma unroll
+                            for (int c = 0; c < NC; c++) { keep[r][c] = acc[r][c]; acc[r][c] = 0.f; }
+                        }
+                    }
                     uint4 wv[RW];
 #pragma unroll
                     for (int r = 0; r < RW; r++)
@@ -108,6 +123,12 @@ k_q4_group(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
                             }
                         }
                     }
+                    if (GS) {
+#pragma unroll
+                        for (int r = 0; r < RW; r++)
+#pragma unroll
+                            for (int c = 0; c < NC; c++) acc[r][c] = fmaf(acc[r][c], sgrp[r], keep[r][c]);
+                    }
                 }
 #pragma unroll
                 for (int r = 0; r < RW; r++)
@@ -124,7 +145,7 @@ k_q4_group(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
                         for (int p = 0; p < 2; p++) {
                             const int oi = o0 + p;
                             if (oi < r_hi) {
-                                const float sg = ws[oi], su = ws[OUT + oi];
+                                const float sg = GS ? 1.f : ws[oi], su = GS ? 1.f : ws[OUT + oi];
 #pragma unroll
                                 for (int c = 0; c < NC; c++) if (c < nc) {
                                     float gv = acc[p][c] * sg, uv = acc[2 + p][c] * su;
@@ -137,7 +158,7 @@ k_q4_group(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
                         for (int r = 0; r < RW; r++) {
                             const int oi = o0 + r;
                             if (oi < r_hi) {
-                                const float s = ws[oi];
+                                const float s = GS ? 1.f : ws[oi];
 #pragma unroll
                                 for (int c = 0; c < NC; c++) if (c < nc)
                                     Y[(size_t)(beg + c0 + c) * OUT + oi] = acc[r][c] * s;
@@ -158,11 +179,12 @@ static int sw_launch_q4(const SwLaunchCfg &c, const SwQ4Args &a) {
     const int U = a.KD / 32;
     size_t smem = (size_t)NC * 8 * (U + 1) * sizeof(float4);
     if (smem > 220 * 1024) return -1;
-    auto kern = k_q4_group<GATEUP, NC>;
-    static size_t attr_smem = 0;
-    if (smem > attr_smem) {
+    if (a.gs < 0 || (a.gs > 0 && a.gs % 32)) return -1;
+    auto kern = a.gs > 0 ? k_q4_group<GATEUP, NC, true> : k_q4_group<GATEUP, NC, false>;
+    static size_t attr_smem[2] = {0, 0};
+    if (smem > attr_smem[a.gs > 0]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -1;
-        attr_smem = smem;
+        attr_smem[a.gs > 0] = smem;
     }
     // rows per work item: enough items to fill the machine a few times over, but
     // never below one pass of the 8 warps.
@@ -176,7 +198,7 @@ static int sw_launch_q4(const SwLaunchCfg &c, const SwQ4Args &a) {
     if (grid > items) grid = items;
     if (grid < 1) grid = 1;
     kern<<<(unsigned)grid, 256, smem, c.stream>>>(a.q, a.s, a.X, a.Y, a.gexp, a.gbeg, a.gcnt, a.G, a.grow,
-                                                  a.KD, a.OUT, rpi, a.expert_lo, a.expert_cnt);
+                                                  a.KD, a.OUT, rpi, a.expert_lo, a.expert_cnt, a.gs);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

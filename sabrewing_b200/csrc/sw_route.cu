@@ -176,6 +176,101 @@ int sw_launch_router_dmma(const SwLaunchCfg &c, const float *x, const void *W, i
 }
 
 // ---------------------------------------------------------------------------
+// Dispatch: stable counting sort of the T*K (row, expert) pairs by expert, done
+// by ONE CTA of NTH threads.  Each warp owns a contiguous segment of the flat
+// pair index, so a per-warp histogram followed by an exclusive scan over
+// (expert, warp) gives every warp the first slot of its pairs for each expert;
+// walking the segment in order with __match_any ranks keeps pairs of one expert
+// in ascending flat index -- the reference's order (c/laguna.c:709-723).
+// sm: (NTH/32 + 2) * E ints of shared memory.
+// ---------------------------------------------------------------------------
+template <int NTH>
+__device__ __forceinline__ void sw_dispatch_block(int *sm, const int *sel, int npairs, int K, int E, int T,
+                                                  int *Gout, int *gexp, int *gbeg, int *gcnt, int *grow, int *rowof, int *status) {
+    constexpr int NW = NTH / 32;
+    int *wh = sm;                    // [NW][E] per-warp histogram -> per-warp running slot offset
+    int *pos = sm + NW * E;          // [E] first slot of expert e
+    int *cnt = pos + E;              // [E]
+    __shared__ int s_wsum[32], s_gsum[32];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    for (int i = tid; i < NW * E; i += NTH) wh[i] = 0;
+    __syncthreads();
+
+    int seg = (npairs + NW - 1) / NW;
+    seg = (seg + 31) & ~31;
+    const int s0 = min(warp * seg, npairs), s1 = min(s0 + seg, npairs);
+    for (int i = s0 + lane; i < s1; i += 32) {
+        int e = __ldcg(sel + i);
+        if (e < 0 || e >= E) { atomicOr(status, SW_ST_BAD_EXPERT); continue; }
+        atomicAdd(&wh[warp * E + e], 1);
+    }
+    __syncthreads();
+
+    // per expert: total and exclusive prefix over warps
+    for (int e = tid; e < E; e += NTH) {
+        int run = 0;
+        for (int wv = 0; wv < NW; wv++) { int c = wh[wv * E + e]; wh[wv * E + e] = run; run += c; }
+        cnt[e] = run;
+    }
+    __syncthreads();
+
+    // exclusive scan over experts of cnt (slots) and of cnt>0 (group index): every thread owns a run of CH experts
+    const int CH = (E + NTH - 1) / NTH;
+    const int e0 = tid * CH, e1 = min(E, e0 + CH);
+    int c = 0, nz = 0;
+    for (int e = e0; e < e1; e++) { c += cnt[e]; nz += cnt[e] > 0 ? 1 : 0; }
+    int sc = c, sg = nz;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        int a = __shfl_up_sync(SW_FULL_MASK, sc, off), b = __shfl_up_sync(SW_FULL_MASK, sg, off);
+        if (lane >= off) { sc += a; sg += b; }
+    }
+    if (lane == 31) { s_wsum[warp] = sc; s_gsum[warp] = sg; }
+    __syncthreads();
+    if (warp == 0) {
+        int a = lane < NW ? s_wsum[lane] : 0, b = lane < NW ? s_gsum[lane] : 0;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            int ua = __shfl_up_sync(SW_FULL_MASK, a, off), ub = __shfl_up_sync(SW_FULL_MASK, b, off);
+            if (lane >= off) { a += ua; b += ub; }
+        }
+        s_wsum[lane] = a; s_gsum[lane] = b;      // inclusive over warps
+    }
+    __syncthreads();
+    {
+        int excl = (warp ? s_wsum[warp - 1] : 0) + sc - c, gidx = (warp ? s_gsum[warp - 1] : 0) + sg - nz;
+        for (int e = e0; e < e1; e++) {
+            const int ce = cnt[e];
+            pos[e] = excl;
+            if (ce > 0) { gexp[gidx] = e; gbeg[gidx] = excl; gcnt[gidx] = ce; gidx++; }
+            excl += ce;
+        }
+        if (tid == 0) *Gout = s_gsum[31];
+    }
+    __syncthreads();
+
+    // stable scatter
+    for (int base = s0; base < s1; base += 32) {
+        int i = base + lane;
+        int e = i < s1 ? __ldcg(sel + i) : -1;
+        bool ok = e >= 0 && e < E;
+        unsigned peers = __match_any_sync(SW_FULL_MASK, ok ? e : -1 - lane);
+        int off = ok ? wh[warp * E + e] : 0;
+        __syncwarp();
+        if (ok) {
+            int rank = __popc(peers & ((1u << lane) - 1));
+            int slot = pos[e] + off + rank;
+            int row = i / K;
+            if (row >= T) atomicOr(status, SW_ST_BAD_ROW);
+            else { grow[slot] = row; rowof[i] = slot; }
+            if (rank == 0) wh[warp * E + e] = off + __popc(peers);
+        }
+        __syncwarp();
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Gate activation + top-k + combine weights: one warp per token.
 // exp/log1p are evaluated in fp64 and rounded to f32, which reproduces a
 // correctly rounded expf; every other operation is the reference's f32 sequence.
@@ -190,8 +285,10 @@ __global__ void __launch_bounds__(256)
 k_route_topk(float *__restrict__ scores, const double *__restrict__ part, int KS, const float *__restrict__ lbias,
              const float *__restrict__ corr_bias, int use_bias,
              int route_act, int norm_topk, int T, int E, int K,
-             int *__restrict__ sel, float *__restrict__ w) {
+             int *__restrict__ sel, float *__restrict__ w, SwRouting dr, unsigned *ticket) {
+    extern __shared__ int sw_dyn_i[];
     __shared__ float s_sc[SW_MAX_EXPERTS], s_sb[SW_MAX_EXPERTS];
+    __shared__ int s_last;
     __shared__ float s_redf[8];
     __shared__ double s_redd[8];
     const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -202,8 +299,19 @@ k_route_topk(float *__restrict__ scores, const double *__restrict__ part, int KS
     for (int e = tid; e < E; e += 256) {
         float v;
         if (part) {
+            // slice partials are loaded eight at a time (independent loads) and added in slice order
             double a = 0.0;
-            for (int ks = 0; ks < KS; ks++) a += part[((size_t)ks * T + t) * E + e];
+            const double *pp = part + (size_t)t * E + e;
+            const size_t stride = (size_t)T * E;
+            int ks = 0;
+            for (; ks + 8 <= KS; ks += 8) {
+                double p[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) p[i] = pp[(size_t)(ks + i) * stride];
+#pragma unroll
+                for (int i = 0; i < 8; i++) a += p[i];
+            }
+            for (; ks < KS; ks++) a += pp[(size_t)ks * stride];
             v = (float)a;
             if (lbias) v += lbias[e];
         } else v = r[e];
@@ -249,8 +357,7 @@ k_route_topk(float *__restrict__ scores, const double *__restrict__ part, int KS
         s_sb[e] = sc + (ub ? corr_bias[e] : 0.f);
     }
     __syncthreads();
-    if (warp != 0) return;
-
+    if (warp == 0) {
     // K rounds of arg-max over score+bias, strict >, ties to the lower id.
     uint32_t used = 0;                           // bit j: this lane's element lane+32j is taken
     float wsel = 0.f;                            // lane a keeps weight of rank a
@@ -285,26 +392,42 @@ k_route_topk(float *__restrict__ scores, const double *__restrict__ part, int KS
         wsel = wsel / sm;
     }
     if (lane < K) w[(size_t)t * K + lane] = wsel;
+    }
+    if (!ticket) return;
+
+    // The CTA that finishes last groups all T*K pairs by expert (saves a launch on the critical path).
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(ticket, 1u) == gridDim.x - 1) ? 1 : 0;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (tid == 0) *ticket = 0;                   // every other CTA has drawn its ticket: ready for the next call
+    sw_dispatch_block<256>(sw_dyn_i, dr.sel, T * K, K, E, T, dr.G, dr.gexp, dr.gbeg, dr.gcnt, dr.grow, dr.rowof, dr.status);
 }
 
+// dr/ticket non-null: the last CTA also runs the dispatch (ticket must be zero before the first call; it is
+// left at zero again).
 int sw_launch_route_topk(const SwLaunchCfg &c, float *scores, const double *part, int KS, const float *lbias,
                          const float *corr_bias, int use_bias,
-                         int route_act, int norm_topk, int T, int E, int K, int *sel, float *w) {
+                         int route_act, int norm_topk, int T, int E, int K, int *sel, float *w,
+                         const SwRouting *dr, unsigned *ticket) {
     if (T <= 0) return 0;
     if (E > SW_MAX_EXPERTS || K > SW_MAX_TOPK || K > E || K <= 0) return -1;
-    k_route_topk<<<T, 256, 0, c.stream>>>(scores, part, KS, lbias, corr_bias, use_bias, route_act, norm_topk, T, E, K, sel, w);
+    static bool attr_done = false;
+    if (!attr_done) {
+        if (cudaFuncSetAttribute(k_route_topk, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024) != cudaSuccess) return -1;
+        attr_done = true;
+    }
+    SwRouting none{};
+    const bool fuse = dr && ticket;
+    size_t smem = fuse ? (size_t)(256 / 32 + 2) * E * sizeof(int) : 0;
+    k_route_topk<<<T, 256, smem, c.stream>>>(scores, part, KS, lbias, corr_bias, use_bias, route_act, norm_topk, T, E, K, sel, w,
+                                             fuse ? *dr : none, fuse ? ticket : nullptr);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
-// ---------------------------------------------------------------------------
-// Dispatch: stable counting sort of the T*K (row, expert) pairs by expert.
-// One CTA.  Each warp owns a contiguous segment of the flat pair index, so a
-// per-warp histogram followed by an exclusive scan over (expert, warp) gives
-// every warp the first slot of its pairs for each expert; walking the segment
-// in order with __match_any ranks keeps pairs of one expert in ascending flat
-// index -- the reference's order.
-// ---------------------------------------------------------------------------
 #define SW_DISPATCH_THREADS 1024
 
 __global__ void __launch_bounds__(SW_DISPATCH_THREADS)
@@ -312,89 +435,12 @@ k_dispatch(const int *__restrict__ sel, int npairs, int K, int E, int T,
            int *__restrict__ Gout, int *__restrict__ gexp, int *__restrict__ gbeg, int *__restrict__ gcnt,
            int *__restrict__ grow, int *__restrict__ rowof, int *__restrict__ status) {
     extern __shared__ int sm[];
-    const int NW = SW_DISPATCH_THREADS / 32;
-    int *wh = sm;                    // [NW][E] per-warp histogram -> per-warp running slot offset
-    int *pos = sm + NW * E;          // [E] first slot of expert e
-    int *cnt = pos + E;              // [E]
-    __shared__ int s_wsum[32], s_gsum[32];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-
-    for (int i = tid; i < NW * E; i += SW_DISPATCH_THREADS) wh[i] = 0;
-    __syncthreads();
-
-    int seg = (npairs + NW - 1) / NW;
-    seg = (seg + 31) & ~31;
-    const int s0 = min(warp * seg, npairs), s1 = min(s0 + seg, npairs);
-    for (int i = s0 + lane; i < s1; i += 32) {
-        int e = sel[i];
-        if (e < 0 || e >= E) { atomicOr(status, SW_ST_BAD_EXPERT); continue; }
-        atomicAdd(&wh[warp * E + e], 1);
-    }
-    __syncthreads();
-
-    // per expert: total and exclusive prefix over warps
-    for (int e = tid; e < E; e += SW_DISPATCH_THREADS) {
-        int run = 0;
-        for (int wv = 0; wv < NW; wv++) { int c = wh[wv * E + e]; wh[wv * E + e] = run; run += c; }
-        cnt[e] = run;
-    }
-    __syncthreads();
-
-    // exclusive scan over experts of cnt (slots) and of cnt>0 (group index); E <= 1024 = blockDim
-    int c = tid < E ? cnt[tid] : 0;
-    int nz = c > 0 ? 1 : 0;
-    int sc = c, sg = nz;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-        int a = __shfl_up_sync(SW_FULL_MASK, sc, off), b = __shfl_up_sync(SW_FULL_MASK, sg, off);
-        if (lane >= off) { sc += a; sg += b; }
-    }
-    if (lane == 31) { s_wsum[warp] = sc; s_gsum[warp] = sg; }
-    __syncthreads();
-    if (warp == 0) {
-        int a = s_wsum[lane], b = s_gsum[lane];
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-            int ua = __shfl_up_sync(SW_FULL_MASK, a, off), ub = __shfl_up_sync(SW_FULL_MASK, b, off);
-            if (lane >= off) { a += ua; b += ub; }
-        }
-        s_wsum[lane] = a; s_gsum[lane] = b;      // inclusive over warps
-    }
-    __syncthreads();
-    {
-        int wbase = warp ? s_wsum[warp - 1] : 0, gbase = warp ? s_gsum[warp - 1] : 0;
-        int excl = wbase + sc - c, gidx = gbase + sg - nz;
-        if (tid < E) {
-            pos[tid] = excl;
-            if (nz) { gexp[gidx] = tid; gbeg[gidx] = excl; gcnt[gidx] = c; }
-        }
-        if (tid == 0) *Gout = s_gsum[31];
-    }
-    __syncthreads();
-
-    // stable scatter
-    for (int base = s0; base < s1; base += 32) {
-        int i = base + lane;
-        int e = i < s1 ? sel[i] : -1;
-        bool ok = e >= 0 && e < E;
-        unsigned peers = __match_any_sync(SW_FULL_MASK, ok ? e : -1 - lane);
-        int off = ok ? wh[warp * E + e] : 0;
-        __syncwarp();
-        if (ok) {
-            int rank = __popc(peers & ((1u << lane) - 1));
-            int slot = pos[e] + off + rank;
-            int row = i / K;
-            if (row >= T) atomicOr(status, SW_ST_BAD_ROW);
-            else { grow[slot] = row; rowof[i] = slot; }
-            if (rank == 0) wh[warp * E + e] = off + __popc(peers);
-        }
-        __syncwarp();
-    }
+    sw_dispatch_block<SW_DISPATCH_THREADS>(sm, sel, npairs, K, E, T, Gout, gexp, gbeg, gcnt, grow, rowof, status);
 }
 
 int sw_launch_dispatch(const SwLaunchCfg &c, const SwRouting &r, int T, int K, int E) {
     if (T <= 0) return 0;
-    if (E > SW_DISPATCH_THREADS) return -1;
+    if (E > SW_MAX_EXPERTS) return -1;
     size_t smem = (size_t)(SW_DISPATCH_THREADS / 32 + 2) * E * sizeof(int);
     static bool attr_done = false;
     if (!attr_done) {

@@ -52,9 +52,9 @@ def _dev(t, device, dtype=None):
 class MoeLayer:
     """Device-resident weights of one layer (optionally one expert-parallel shard of it)."""
 
-    def __init__(self, D, I, SI, arrays, device, router="bf16", expert_lo=0, expert_cnt=0, n_experts=None):
+    def __init__(self, D, I, SI, arrays, device, router="bf16", expert_lo=0, expert_cnt=0, n_experts=None, gs=0):
         a = arrays
-        self.D, self.I, self.SI = D, I, SI
+        self.D, self.I, self.SI, self.gs = D, I, SI, gs
         self.device = torch.device(device)
         if router == "bf16":
             self.router_w = _dev(a["router_bf16"], device); self.router_dtype = capi.DTYPE_BF16
@@ -64,7 +64,7 @@ class MoeLayer:
         self.logit_bias = _dev(a.get("logit_bias"), device)
         self.expert_lo, self.expert_cnt = expert_lo, expert_cnt
         gu_q, gu_s, dn_q, dn_s = a["gu_q"], a["gu_s"], a["dn_q"], a["dn_s"]
-        if expert_cnt > 0:       # keep only the rows of the resident experts
+        if expert_cnt > 0:       # keep only the rows of the resident experts (scales are [rows] or [rows, groups])
             lo, hi = expert_lo, expert_lo + expert_cnt
             gu_q, gu_s = gu_q[lo * 2 * I:hi * 2 * I], gu_s[lo * 2 * I:hi * 2 * I]
             dn_q, dn_s = dn_q[lo * D:hi * D], dn_s[lo * D:hi * D]
@@ -80,7 +80,7 @@ class MoeLayer:
         p = self._p
         return capi.SwMoeLayer(self.D, self.I, self.SI, self.router_dtype, p(self.router_w), p(self.corr_bias),
                                p(self.logit_bias), p(self.gu_q), p(self.gu_s), p(self.dn_q), p(self.dn_s),
-                               p(self.sh_gate), p(self.sh_up), p(self.sh_down), self.expert_lo, self.expert_cnt)
+                               p(self.sh_gate), p(self.sh_up), p(self.sh_down), self.expert_lo, self.expert_cnt, self.gs)
 
     def expert_bytes(self):
         return sum(t.numel() * t.element_size() for t in (self.gu_q, self.gu_s, self.dn_q, self.dn_s))

@@ -32,7 +32,7 @@ def test_struct_layouts_match_reference_descriptor():
     assert [f[0] for f in capi.SwMoeDesc._fields_] == ["n_experts", "topk", "route_act", "use_corr_bias",
                                                      "norm_topk", "route_scale", "shared_mode"]
     assert C.sizeof(capi.SwMoeDesc) == 28
-    assert C.sizeof(capi.SwMoeLayer) == 16 + 10 * 8 + 8
+    assert C.sizeof(capi.SwMoeLayer) == 16 + 10 * 8 + 16      # 4 ints, 10 pointers, 3 ints + padding
 
 
 def test_calls_fail_cleanly_without_a_device():

@@ -22,7 +22,7 @@ def make_block(case, max_tokens=None):
     from sabrewing_b200.moe_block import MoeBlock, MoeLayer, desc_from_config
     cfg = case.cfg
     blk = MoeBlock("cuda:0", max_tokens or max(case.x.shape[0], 1), cfg.E, cfg.K, cfg.D, cfg.I, cfg.SI)
-    layer = MoeLayer(cfg.D, cfg.I, cfg.SI, case.a, "cuda:0")
+    layer = MoeLayer(cfg.D, cfg.I, cfg.SI, case.a, "cuda:0", gs=cfg.gs)
     return blk, layer, desc_from_config(cfg)
 
 
@@ -84,6 +84,14 @@ def test_large_groups_take_the_tensor_memory_path(orc, base, kw, T):
     """Groups averaging >= 12 rows run the tcgen05/TMEM grouped GEMM; same parity bars."""
     case = synth_case(base, corr_bias_std=0.01, T=T, **kw)
     assert T * case.cfg.K >= 12 * case.cfg.E
+    run_case(case, orc)
+
+
+@pytest.mark.parametrize("gs,kw", [(64, dict(D=256, I=128, SI=64, E=16, K=4)), (128, dict(D=512, I=256, SI=64, E=16, K=4)),
+                                   (64, dict(D=160, I=96, SI=32, E=8, K=2))])       # last: partial final groups
+def test_group_scaled_int4(orc, gs, kw):
+    """One scale per gs columns (the reference's fmt=4 container, c/quant.h:167-202), checked against the CPU checker."""
+    case = synth_case("c2", corr_bias_std=0.01, T=21, gs=gs, **kw)
     run_case(case, orc)
 
 
