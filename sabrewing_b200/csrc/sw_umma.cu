@@ -285,18 +285,21 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
         // ------------------------------ dequantise ------------------------------
         // Four groups of two warps; group g dequantises the sub-stages kk with kk % 4 == g into A tile g, so four
         // sub-stages are in flight at once (the chain wait -> load -> convert -> store -> fence -> arrive is long).
-        // Thread t of a group owns tile rows t and t+64.
+        // A thread converts four 16-byte pieces q = tg + 64*i of the raw tile; consecutive lanes read consecutive
+        // pieces (no bank conflicts on the loads).  Piece q is half (q & 1) of raw row q/2.
         const int grp = warp >> 1, tg = threadIdx.x & 63;
         unsigned kk = 0, slot_base = 0;
         for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
             int gi, c0, mt; decode(item, gi, c0, mt);
             const int R = tile_rows(min(128, a.gcnt[gi] - c0)), KSUB = substages(R);
             const int pitch = 32 * KSUB;                                // bytes per raw row in the slot
-            int rowoff[2];
+            int rawoff[4], dstoff[4];
 #pragma unroll
-            for (int i = 0; i < 2; i++) {
-                const int r = tg + 64 * i;
-                rowoff[i] = GATEUP ? (r & 1) * (64 * pitch) + (r >> 1) * pitch : r * pitch;
+            for (int i = 0; i < 4; i++) {
+                const int q = tg + 64 * i, rr = q >> 1, h = q & 1;      // raw row 0..127 (gate rows 0..63 then up rows), half
+                const int trow = GATEUP ? 2 * (rr & 63) + (rr >> 6) : rr;   // tile row: gate j -> 2j, up j -> 2j+1
+                rawoff[i] = rr * pitch + h * 16;
+                dstoff[i] = trow * 128 + (((h * 4) ^ (trow & 7)) << 4);  // chunk (4h + j) goes to (4h + j) ^ (trow & 7)
             }
             for (int st = 0; st < NST; st++, kk++) {
                 if ((kk & 3) != (unsigned)grp) continue;
@@ -307,20 +310,25 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
                 if (ok && kk >= UM_ABUF) ok = um_bar_wait(um_s32(&b_a_free[grp]), ((kk / UM_ABUF) - 1) & 1, abortp);
                 if (!ok) { if (lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; } break; }
                 const unsigned char *raw = smem + s * UM_STAGE_BYTES + u * 32;
+                unsigned char *dstb = a16 + grp * UM_A16;
+                uint4 w[4];
 #pragma unroll
-                for (int i = 0; i < 2; i++) {
-                    const int r = tg + 64 * i, x7 = r & 7;
-                    const uint4 w0 = *reinterpret_cast<const uint4 *>(raw + rowoff[i]);
-                    const uint4 w1 = *reinterpret_cast<const uint4 *>(raw + rowoff[i] + 16);
-                    unsigned char *dst = a16 + grp * UM_A16 + r * 128;
-                    *reinterpret_cast<uint4 *>(dst + ((0 ^ x7) << 4)) = um_dq(w0.x);
-                    *reinterpret_cast<uint4 *>(dst + ((1 ^ x7) << 4)) = um_dq(w0.y);
-                    *reinterpret_cast<uint4 *>(dst + ((2 ^ x7) << 4)) = um_dq(w0.z);
-                    *reinterpret_cast<uint4 *>(dst + ((3 ^ x7) << 4)) = um_dq(w0.w);
-                    *reinterpret_cast<uint4 *>(dst + ((4 ^ x7) << 4)) = um_dq(w1.x);
-                    *reinterpret_cast<uint4 *>(dst + ((5 ^ x7) << 4)) = um_dq(w1.y);
-                    *reinterpret_cast<uint4 *>(dst + ((6 ^ x7) << 4)) = um_dq(w1.z);
-                    *reinterpret_cast<uint4 *>(dst + ((7 ^ x7) << 4)) = um_dq(w1.w);
+                for (int i = 0; i < 4; i++) w[i] = *reinterpret_cast<const uint4 *>(raw + rawoff[i]);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    // (4h + j) ^ x7 == ((4h) ^ x7) ^ j for j < 4: the four chunks of a half are the base slot xor j
+                    // In the gate/up tile four consecutive raw rows land on tile rows 2j, 2j+2, 2j+4, 2j+6, whose
+                    // slots would collide pairwise; rows 2 and 3 of each four store their chunks in the order
+                    // 1,0,3,2 instead (jx), which makes the eight lanes of a quarter warp hit eight different slots.
+                    unsigned char *d = dstb + (dstoff[i] & ~0x7F);
+                    const int jx = GATEUP ? (dstoff[i] >> 9) & 1 : 0;
+                    const int base = ((dstoff[i] >> 4) & 7) ^ jx;
+                    const unsigned w0 = jx ? w[i].y : w[i].x, w1 = jx ? w[i].x : w[i].y;
+                    const unsigned w2 = jx ? w[i].w : w[i].z, w3 = jx ? w[i].z : w[i].w;
+                    *reinterpret_cast<uint4 *>(d + ((base ^ 0) << 4)) = um_dq(w0);
+                    *reinterpret_cast<uint4 *>(d + ((base ^ 1) << 4)) = um_dq(w1);
+                    *reinterpret_cast<uint4 *>(d + ((base ^ 2) << 4)) = um_dq(w2);
+                    *reinterpret_cast<uint4 *>(d + ((base ^ 3) << 4)) = um_dq(w3);
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic stores -> tensor-core reads
                 __syncwarp();
