@@ -57,7 +57,7 @@ struct SwMoeCtx {
     int maxT = 0, maxE = 0, maxK = 0, maxD = 0, maxI = 0, maxSI = 0;
     cudaStream_t stream = nullptr, last_stream = nullptr;
     cudaStream_t aux = nullptr;                 // the shared expert runs here, beside routing and the routed experts
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_pack = nullptr;
     SwRouting r{};
     float *glu = nullptr, *slots = nullptr, *sglu = nullptr, *so = nullptr, *routed = nullptr;
     float *dx = nullptr, *dout = nullptr, *hx = nullptr, *hout = nullptr;
@@ -103,7 +103,8 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
     if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaStreamCreateWithFlags(&c->aux, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess) { delete c; return sw_cuda_fail(cudaGetLastError(), "cudaStreamCreate"); }
+        cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_pack, cudaEventDisableTiming) != cudaSuccess) { delete c; return sw_cuda_fail(cudaGetLastError(), "cudaStreamCreate"); }
 
     const size_t T = max_tokens, E = max_experts, K = max_topk, D = max_D, I = max_I, SI = max_SI, P = T * K;
     size_t sizes[] = {
@@ -155,6 +156,7 @@ extern "C" void sw_moe_ctx_destroy(SwMoeCtx *c) {
     if (c->aux) { cudaStreamSynchronize(c->aux); cudaStreamDestroy(c->aux); }
     if (c->ev_fork) cudaEventDestroy(c->ev_fork);
     if (c->ev_join) cudaEventDestroy(c->ev_join);
+    if (c->ev_pack) cudaEventDestroy(c->ev_pack);
     if (c->block) cudaFree(c->block);
     if (c->hx) cudaFreeHost(c->hx);
     if (c->hout) cudaFreeHost(c->hout);
@@ -218,13 +220,21 @@ static int sw_expert_path(int D, int I, int rows, int groups) {
     return 2;
 }
 
-static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, const float *gu_s,
-                          const void *dn_q, const float *dn_s, const float *x, int rows_x, void *xp,
-                          float *glu, float *slots, float *sums, int *status, int D, int I,
-                          void (*mark)(void *, int), void *mark_ctx, const SwUmmaScratch *um = nullptr) {
+// Which expert kernels a call will use: 0 CUDA cores, 1 mma.sync + cp.async, 2 mma.sync + TMA, 3 tcgen05.
+static int sw_resolve_path(const SwQ4Args &a, const void *gu_q, const void *dn_q, int D, int I, const SwUmmaScratch *um) {
     int path = a.gs > 0 ? 0 : sw_expert_path(D, I, a.max_rows, a.max_groups);   // group scales: CUDA-core kernels
     if (path >= 2 && (((uintptr_t)gu_q | (uintptr_t)dn_q) & 15)) path = 1;    // TMA wants 16-byte aligned blobs
     if (path == 3 && !um) path = 2;
+    return path;
+}
+
+// x_packed: the packed copy of x (xp) and its row sums are already in flight or done (the caller ordered them
+// before this call's stream position).
+static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, const float *gu_s,
+                          const void *dn_q, const float *dn_s, const float *x, int rows_x, void *xp,
+                          float *glu, float *slots, float *sums, int *status, int D, int I,
+                          void (*mark)(void *, int), void *mark_ctx, const SwUmmaScratch *um = nullptr, bool x_packed = false) {
+    const int path = sw_resolve_path(a, gu_q, dn_q, D, I, um);
     if (path == 3) {
         // tcgen05 path: gather + split the token rows in packed-slot order, build the chunk list, two grouped GEMMs
         const long long nexp = a.expert_cnt > 4096 ? 4096 : a.expert_cnt;
@@ -244,7 +254,7 @@ static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, 
     if (path > 0) {
         // sums: [rows_x] row sums of x, then [max_rows, parts] partial row sums of the packed SiLU*up rows
         float *xsum = sums, *ypart = sums + ((rows_x + 63) & ~63);
-        if (sw_launch_pack_act(cfg, x, xp, xsum, rows_x, D)) return -1;
+        if (!x_packed && sw_launch_pack_act(cfg, x, xp, xsum, rows_x, D)) return -1;
         const long long nexp = a.expert_cnt > 4096 ? 4096 : a.expert_cnt;   // bounds the tensor map when the caller gave no count
         a.q = (const uint8_t *)gu_q; a.s = gu_s; a.KD = D; a.OUT = I;
         int parts;
@@ -424,10 +434,25 @@ extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
     // The shared expert depends only on x: outside stage profiling it runs on the
     // context's second stream, forked here and joined before the combine.
     const bool overlap = has_shared && !c->prof_on;
-    if (overlap) {
+    SwQ4Args a{};
+    a.gexp = c->r.gexp; a.gbeg = c->r.gbeg; a.gcnt = c->r.gcnt; a.G = c->r.G; a.grow = c->r.grow;
+    a.expert_lo = lo; a.expert_cnt = cnt;
+    a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K; a.gs = L->gs;
+    // Packing x for the mma.sync kernels depends only on x too: it goes first on the second stream, off the
+    // router -> top-k -> experts chain.
+    const int path = sw_resolve_path(a, L->gu_q, L->dn_q, L->D, L->I, &c->um);
+    const bool prepack = !c->prof_on && (path == 1 || path == 2);
+    if (overlap || prepack) {
         SwLaunchCfg acfg{c->num_sms, c->aux};
         SW_CUDA(cudaEventRecord(c->ev_fork, st));
         SW_CUDA(cudaStreamWaitEvent(c->aux, c->ev_fork, 0));
+        if (prepack) {
+            if (sw_launch_pack_act(acfg, x, c->xp, c->sums, T, L->D)) return sw_fail("pack launch failed");
+            SW_CUDA(cudaEventRecord(c->ev_pack, c->aux));
+        }
+    }
+    if (overlap) {
+        SwLaunchCfg acfg{c->num_sms, c->aux};
         if (sw_shared_run(acfg, L, x, T, c->spk, c->sglu, c->so, &so, &so_slices, nullptr, nullptr, c->r.status)) return sw_fail("shared expert launch failed");
         SW_CUDA(cudaEventRecord(c->ev_join, c->aux));
     }
@@ -437,12 +462,9 @@ extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
     sw_prof_mark(c, SW_ST_DISPATCH, st);
     c->last_stream = st; c->lastT = T; c->lastK = K; c->lastE = E;
 
-    SwQ4Args a{};
-    a.gexp = c->r.gexp; a.gbeg = c->r.gbeg; a.gcnt = c->r.gcnt; a.G = c->r.G; a.grow = c->r.grow;
-    a.expert_lo = lo; a.expert_cnt = cnt;
-    a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K; a.gs = L->gs;
     auto mark = [](void *p, int which) { MarkCtx *m = (MarkCtx *)p; sw_prof_mark(m->c, which == 0 ? SW_ST_GATEUP : SW_ST_DOWN, m->st); };
-    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, mark, &mc, &c->um))
+    if (prepack) SW_CUDA(cudaStreamWaitEvent(st, c->ev_pack, 0));
+    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, mark, &mc, &c->um, prepack))
         return sw_fail("expert launch failed");
     if (overlap) {
         SW_CUDA(cudaStreamWaitEvent(st, c->ev_join, 0));

@@ -335,17 +335,33 @@ k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const 
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
         const int t = (int)(idx / D4), i4 = (int)(idx - (size_t)t * D4);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int a = 0; a < K; a++) {
-            const int e = sel[t * K + a] - expert_lo;
-            if (e < 0 || e >= expert_cnt) continue;
-            const float wa = w[t * K + a];
-            const float4 v = reinterpret_cast<const float4 *>(slots + (size_t)rowof[t * K + a] * D)[i4];
-            acc.x = fmaf(wa, v.x, acc.x); acc.y = fmaf(wa, v.y, acc.y);
-            acc.z = fmaf(wa, v.z, acc.z); acc.w = fmaf(wa, v.w, acc.w);
+        // eight ranks at a time: indices first, then all slot rows (independent loads), then the FMAs in rank order
+        for (int a0 = 0; a0 < K; a0 += 8) {
+            float wa[8]; int slot[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int a = a0 + j;
+                slot[j] = -1; wa[j] = 0.f;
+                if (a < K) {
+                    const int e = sel[t * K + a] - expert_lo;
+                    if (e >= 0 && e < expert_cnt) { slot[j] = rowof[t * K + a]; wa[j] = w[t * K + a]; }
+                }
+            }
+            float4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (slot[j] >= 0) v[j] = reinterpret_cast<const float4 *>(slots + (size_t)slot[j] * D)[i4];
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (slot[j] >= 0) {
+                    acc.x = fmaf(wa[j], v[j].x, acc.x); acc.y = fmaf(wa[j], v[j].y, acc.y);
+                    acc.z = fmaf(wa[j], v[j].z, acc.z); acc.w = fmaf(wa[j], v[j].w, acc.w);
+                }
         }
         if (mode & 1) { acc.x *= route_scale; acc.y *= route_scale; acc.z *= route_scale; acc.w *= route_scale; }
         if (mode & 2) {
             float4 s = reinterpret_cast<const float4 *>(add)[idx];
+#pragma unroll 8
             for (int k = 1; k < add_slices; k++) {
                 const float4 s2 = reinterpret_cast<const float4 *>(add)[(size_t)k * n + idx];
                 s.x += s2.x; s.y += s2.y; s.z += s2.z; s.w += s2.w;

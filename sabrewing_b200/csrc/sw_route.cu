@@ -277,6 +277,54 @@ __device__ __forceinline__ void sw_dispatch_block(int *sm, const int *sel, int n
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float sw_expf_cr(float v) { return (float)exp((double)v); }
 
+// K selection rounds by one warp (the reference's moe_topk, c/moe_arch.h:64-89): arg-max of score+bias with strict >
+// from -1e30f, ties to the lower id, an expert is taken once; if nothing compares greater (all NaN or <= -1e30f) the
+// lowest id not yet taken.  Lane l keeps the values of experts l, l+32, ... in registers; a round is a local scan, a
+// warp max over an order-preserving integer key and a warp min over the ids that hold that maximum.
+template <int NJ>
+__device__ __forceinline__ void sw_topk_warp(const float *s_sb, const float *s_sc, int E, int K, int norm_topk,
+                                             int *sel_t, float *w_t) {
+    const int lane = threadIdx.x & 31;
+    float v[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; j++) {
+        const int e = lane + 32 * j;
+        v[j] = e < E ? s_sb[e] + 0.0f : __int_as_float(0x7fc00000);     // -0 -> +0; past the end: NaN, never greater
+    }
+    uint32_t used = 0;                           // bit j: this lane's expert lane+32j is taken
+    float wsel = 0.f;                            // lane a keeps the weight of rank a
+    for (int a = 0; a < K; a++) {
+        float bv = -1e30f; int bj = -1;
+#pragma unroll
+        for (int j = 0; j < NJ; j++) if (v[j] > bv) { bv = v[j]; bj = j; }
+        const uint32_t bits = __float_as_uint(bv);
+        const uint32_t key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+        const uint32_t kmax = __reduce_max_sync(SW_FULL_MASK, key);
+        const uint32_t cand = (bj >= 0 && key == kmax) ? (uint32_t)(lane + 32 * bj) : 0xffffffffu;
+        uint32_t best = __reduce_min_sync(SW_FULL_MASK, cand);
+        if (best == 0xffffffffu) {               // nothing compared greater: lowest id not taken yet
+            uint32_t c = 0xffffffffu;
+#pragma unroll
+            for (int j = NJ - 1; j >= 0; j--) if (lane + 32 * j < E && !(used & (1u << j))) c = (uint32_t)(lane + 32 * j);
+            best = __reduce_min_sync(SW_FULL_MASK, c);
+            if (best == 0xffffffffu) best = 0;
+        }
+        if ((int)(best & 31) == lane) {
+            used |= 1u << (best >> 5);
+#pragma unroll
+            for (int j = 0; j < NJ; j++) if (j == (int)(best >> 5)) v[j] = __int_as_float(0x7fc00000);
+        }
+        if (lane == a) wsel = s_sc[best];
+        if (lane == 0) sel_t[a] = (int)best;
+    }
+    if (norm_topk) {                             // float sum in rank order, then divide
+        float sm = 0.f;
+        for (int a = 0; a < K; a++) sm += __shfl_sync(SW_FULL_MASK, wsel, a);
+        wsel = wsel / sm;
+    }
+    if (lane < K) w_t[lane] = wsel;
+}
+
 // One CTA of 256 threads per token.  Phase 1 (all threads, one expert each per
 // pass): logits from the fp64 slice partials (or as given), gate activation,
 // score and score+bias into shared memory.  Phase 2 (warp 0): the K selection
@@ -299,11 +347,18 @@ k_route_topk(float *__restrict__ scores, const double *__restrict__ part, int KS
     for (int e = tid; e < E; e += 256) {
         float v;
         if (part) {
-            // slice partials are loaded eight at a time (independent loads) and added in slice order
+            // slice partials are loaded 32 or eight at a time (independent loads) and added in slice order
             double a = 0.0;
             const double *pp = part + (size_t)t * E + e;
             const size_t stride = (size_t)T * E;
             int ks = 0;
+            for (; ks + 32 <= KS; ks += 32) {
+                double p[32];
+#pragma unroll
+                for (int i = 0; i < 32; i++) p[i] = pp[(size_t)(ks + i) * stride];
+#pragma unroll
+                for (int i = 0; i < 32; i++) a += p[i];
+            }
             for (; ks + 8 <= KS; ks += 8) {
                 double p[8];
 #pragma unroll
@@ -358,40 +413,10 @@ k_route_topk(float *__restrict__ scores, const double *__restrict__ part, int KS
     }
     __syncthreads();
     if (warp == 0) {
-    // K rounds of arg-max over score+bias, strict >, ties to the lower id.
-    uint32_t used = 0;                           // bit j: this lane's element lane+32j is taken
-    float wsel = 0.f;                            // lane a keeps weight of rank a
-    for (int a = 0; a < K; a++) {
-        float bv = -1e30f; int best = -1;
-        int j = 0;
-        for (int e = lane; e < E; e += 32, j++) {
-            if (used & (1u << j)) continue;
-            const float s = s_sb[e];
-            if (s > bv) { bv = s; best = e; }
-        }
-#pragma unroll
-        for (int off = 16; off; off >>= 1) {
-            float ov = __shfl_xor_sync(SW_FULL_MASK, bv, off);
-            int oi = __shfl_xor_sync(SW_FULL_MASK, best, off);
-            if (oi >= 0 && (best < 0 || ov > bv || (ov == bv && oi < best))) { bv = ov; best = oi; }
-        }
-        if (best < 0) {                          // nothing finite: lowest unselected id
-            int cand = 0x7fffffff; j = 0;
-            for (int e = lane; e < E; e += 32, j++) if (!(used & (1u << j))) { cand = e; break; }
-#pragma unroll
-            for (int off = 16; off; off >>= 1) { int o = __shfl_xor_sync(SW_FULL_MASK, cand, off); if (o < cand) cand = o; }
-            best = cand == 0x7fffffff ? 0 : cand;
-        }
-        if ((best & 31) == lane) used |= 1u << (best >> 5);
-        if (lane == a) wsel = s_sc[best];
-        if (lane == 0) sel[(size_t)t * K + a] = best;
-    }
-    if (norm_topk) {                             // float sum in rank order, then divide
-        float sm = 0.f;
-        for (int a = 0; a < K; a++) sm += __shfl_sync(SW_FULL_MASK, wsel, a);
-        wsel = wsel / sm;
-    }
-    if (lane < K) w[(size_t)t * K + lane] = wsel;
+        const int nj = (E + 31) >> 5;
+        if (nj <= 8) sw_topk_warp<8>(s_sb, s_sc, E, K, norm_topk, sel + (size_t)t * K, w + (size_t)t * K);
+        else if (nj <= 16) sw_topk_warp<16>(s_sb, s_sc, E, K, norm_topk, sel + (size_t)t * K, w + (size_t)t * K);
+        else sw_topk_warp<32>(s_sb, s_sc, E, K, norm_topk, sel + (size_t)t * K, w + (size_t)t * K);
     }
     if (!ticket) return;
 
