@@ -65,6 +65,17 @@ int    lag_cuda_moe_group(float *acc, const float *x,
                           const int *gexp, const int *gbeg, const int *gcnt, int G,
                           const int *grow, const int *rowof, const float *w,
                           int S, int K, int I, int D);
+/* c/backend_cuda_laguna.h:83-84 -- fp4: W device e2m1 codes [O,I/2] (low nibble = even column), es device
+ * ue8m0 exponent bytes [O,I/32]; value = lut[code] * 2^(es-127).  I % 32 == 0. */
+int    lag_cuda_matmul_fp4(float *y, const float *x, const void *packed,
+                           const void *es, int S, int I, int O);
+/* c/backend_cuda_laguna.h:93-98 -- out[D] = sum_k w[k]*expert(sel[k], x) over a resident fp4 layer, one token,
+ * SwiGLU clamped asymmetrically (gate <= limit, |up| <= limit); experts are added in the order given. */
+int    lag_cuda_moe_experts_fp4(float *out, const float *x,
+                                const void *gu_q, const void *gu_es,
+                                const void *dn_q, const void *dn_es,
+                                const int *sel, const float *w, int K,
+                                int I, int D, float limit);
 
 /* ------------------------------------------------------------------------- */
 /* 2. Descriptor-level device-resident MoE block                              */

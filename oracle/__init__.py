@@ -95,6 +95,23 @@ class _Lib:
         f(_ptr(y), _ptr(x), _ptr(packed), _ptr(scale), C.c_int(S), C.c_int(I), C.c_int(O), C.c_int(exact))
         return y
 
+    def matmul_fp4(self, x, packed, es, exact=1):
+        """y[S,O] for e2m1 codes `packed` [O, I/2] and ue8m0 exponents `es` [O, I/32]."""
+        S, I = x.shape; O = packed.shape[0]
+        y = np.empty((S, O), np.float32)
+        f = self.fn("matmul_fp4"); f.restype = None
+        f(_ptr(y), _ptr(x), _ptr(packed), _ptr(es), C.c_int(S), C.c_int(I), C.c_int(O), C.c_int(exact))
+        return y
+
+    def experts_fp4(self, x, gu_q, gu_es, dn_q, dn_es, sel, w, I, D, limit, exact=1):
+        """out[D] = sum_a w[a] * fp4 expert sel[a] of one token x[D] with the clamped SwiGLU."""
+        out = np.empty(D, np.float32); h = np.empty(2 * I + D, np.float32)
+        sel = np.ascontiguousarray(sel, np.int32); w = np.ascontiguousarray(w, np.float32)
+        f = self.fn("experts_fp4"); f.restype = None
+        f(_ptr(out), _ptr(x), _ptr(gu_q), _ptr(gu_es), _ptr(dn_q), _ptr(dn_es), _ptr(sel), _ptr(w),
+          C.c_int(len(sel)), C.c_int(I), C.c_int(D), C.c_float(limit), C.c_int(exact), _ptr(h))
+        return out
+
     def matmul_i4_grouped(self, x, q4, scale, gs, exact=0):
         S, I = x.shape; O = q4.shape[0]
         y = np.empty((S, O), np.float32)

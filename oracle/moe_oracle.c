@@ -138,6 +138,73 @@ ORC_API void orc_matmul_q4(float *y, const float *x, const uint8_t *packed, cons
     }
 }
 
+/* fp4: e2m1 codes, two per byte (low nibble = even column), one ue8m0 exponent byte per 32 input
+ * columns: value = lut[nibble] * 2^(es[o, col/32] - 127)  (c/moe_quant.h:219-257). */
+static const float orc_fp4_lut[16] = { 0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f,
+                                       -0.0f, -0.5f, -1.0f, -1.5f, -2.0f, -3.0f, -4.0f, -6.0f };
+/* 0xFF (the format's NaN) decodes to 0, 0 to the denormal 2^-127 (c/moe_quant.h:250-256). */
+static inline float orc_ue8m0(uint8_t e) {
+    if (e == 0xFF) return 0.f;
+    if (e == 0) return 5.8774717541114375e-39f;
+    uint32_t u = (uint32_t)e << 23; float f; memcpy(&f, &u, 4); return f;
+}
+/* y[S,O] = x[S,I] * dequant(packed, es)^T.  exact: the double-accumulate loop of
+ * c/moe_quant.h:289-301 (per byte: (x0*lut0 + x1*lut1) * scale, added in column order);
+ * exact=0: a plain float port with one partial sum per 32-column block. */
+ORC_API void orc_matmul_fp4(float *y, const float *x, const uint8_t *packed, const uint8_t *es,
+                            int S, int I, int O, int exact) {
+    #pragma omp parallel for schedule(static) if ((int64_t)S * O >= 512)
+    for (int o = 0; o < O; o++) {
+        const uint8_t *p = packed + (int64_t)o * (I / 2);
+        const uint8_t *e = es + (int64_t)o * (I / 32);
+        for (int s = 0; s < S; s++) {
+            const float *xs = x + (int64_t)s * I;
+            if (exact) {
+                double a = 0;
+                for (int c = 0; c < I / 2; c++) {
+                    uint8_t b = p[c];
+                    double sc = orc_ue8m0(e[(2 * c) / 32]);
+                    a += ((double)xs[2 * c] * orc_fp4_lut[b & 0xF] + (double)xs[2 * c + 1] * orc_fp4_lut[b >> 4]) * sc;
+                }
+                y[(int64_t)s * O + o] = (float)a;
+            } else {
+                float a = 0;
+                for (int blk = 0; blk < I / 32; blk++) {
+                    float part = 0, sc = orc_ue8m0(e[blk]);
+                    for (int c = blk * 16; c < blk * 16 + 16; c++) {
+                        uint8_t b = p[c];
+                        part += xs[2 * c] * orc_fp4_lut[b & 0xF] + xs[2 * c + 1] * orc_fp4_lut[b >> 4];
+                    }
+                    a += part * sc;
+                }
+                y[(int64_t)s * O + o] = a;
+            }
+        }
+    }
+}
+
+/* K routed fp4 experts of one token, DeepSeek-V4's clamped SwiGLU (c/deepseek.c:820-842):
+ * gate clamped from above at limit, up clamped to [-limit, limit]; the experts' outputs are
+ * added as out += w[a]*y_a in the order given (c/deepseek.c:1571, c/backend_cuda_laguna.cu:389-395).
+ * h: scratch of 2*I + D floats. */
+ORC_API void orc_experts_fp4(float *out, const float *x, const uint8_t *gu_q, const uint8_t *gu_es,
+                             const uint8_t *dn_q, const uint8_t *dn_es, const int *sel, const float *w,
+                             int K, int I, int D, float limit, int exact, float *h) {
+    float *g = h, *u = h + I, *tmp = h + 2 * I;
+    for (int i = 0; i < D; i++) out[i] = 0.f;
+    for (int a = 0; a < K; a++) {
+        const int64_t e = sel[a];
+        orc_matmul_fp4(g, x, gu_q + e * 2 * I * (D / 2), gu_es + e * 2 * I * (D / 32), 1, D, 2 * I, exact);
+        for (int i = 0; i < I; i++) {
+            float gi = g[i] > limit ? limit : g[i];
+            float ui = u[i] > limit ? limit : (u[i] < -limit ? -limit : u[i]);
+            g[i] = orc_silu(gi) * ui;
+        }
+        orc_matmul_fp4(tmp, g, dn_q + e * D * (I / 2), dn_es + e * D * (I / 32), 1, I, D, exact);
+        for (int i = 0; i < D; i++) out[i] += w[a] * tmp[i];
+    }
+}
+
 /* int4 with one scale per gs inputs: y = sum_g scale[o,g] * sum_{i in g} x_i*(nib_i-8)
  * (c/quant.h:167-202; double form follows the plain reference in
  * c/tests/test_i4_grouped.c:30-54, which multiplies the scale into every term). */

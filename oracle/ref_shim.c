@@ -94,6 +94,26 @@ REF_API int ref_moe_block_rows(const RefLayer *r, const float *x, float *hout, i
 REF_API void ref_matmul_f32(float *y, const float *x, const float *W, int S, int I, int O, int exact) { matmul_f32(y, x, W, S, I, O, exact); }
 REF_API void ref_matmul_bf16(float *y, const float *x, const uint16_t *W, int S, int I, int O, int exact) { matmul_bf16_k(y, x, W, S, I, O, 0, exact); }
 REF_API void ref_matmul_q4(float *y, const float *x, const uint8_t *p, const float *sc, int S, int I, int O, int exact) { matmul_q4_kb(y, x, p, sc, S, I, O, MOE_Q4_F32, exact); }
+REF_API void ref_matmul_fp4(float *y, const float *x, const uint8_t *p, const uint8_t *es, int S, int I, int O, int exact) { matmul_fp4_kb(y, x, p, es, S, I, O, exact); }
+/* The K-expert loop of the reference's fp4 GPU self-test (c/deepseek.c:1557-1572), which is moe_row's
+ * (c/deepseek.c:820-842), over the reference's own matmul_fp4_k and siluf.  h: 2*I + D floats. */
+REF_API void ref_experts_fp4(float *out, const float *x, const uint8_t *gu, const uint8_t *gue, const uint8_t *dn,
+                             const uint8_t *dne, const int *sel, const float *w, int K, int I, int D, float lim,
+                             int exact, float *h) {
+    float *g = h, *u = h + I, *tmp = h + 2 * I;
+    for (int i = 0; i < D; i++) out[i] = 0;
+    for (int a = 0; a < K; a++) {
+        int e = sel[a];
+        matmul_fp4_k(g, x, gu + (size_t)e * 2 * I * (D / 2), gue + (size_t)e * 2 * I * (D / 32), D, 2 * I, exact);
+        for (int i = 0; i < I; i++) {
+            float gi = g[i] > lim ? lim : g[i];
+            float ui = u[i] > lim ? lim : (u[i] < -lim ? -lim : u[i]);
+            g[i] = siluf(gi) * ui;
+        }
+        matmul_fp4_k(tmp, g, dn + (size_t)e * D * (I / 2), dne + (size_t)e * D * (I / 32), I, D, exact);
+        for (int i = 0; i < D; i++) out[i] += w[a] * tmp[i];
+    }
+}
 REF_API void ref_softmax_row(float *x, int n) { softmax_row(x, n); }
 REF_API void ref_topk(const float *score, const float *bias, int use_bias, int E, int K, int *sel) { moe_topk(score, bias, use_bias, E, K, sel); }
 REF_API void ref_rmsnorm_rows(float *out, const float *x, const float *w, int S, int D, float eps) {

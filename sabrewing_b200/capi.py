@@ -44,6 +44,8 @@ SIGNATURES = {
     "lag_cuda_expert_q4": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "lag_cuda_moe_experts": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
     "lag_cuda_moe_group": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i]),
+    "lag_cuda_matmul_fp4": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i]),
+    "lag_cuda_moe_experts_fp4": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, C.c_float]),
     "sw_moe_ctx_create": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i]),
     "sw_moe_ctx_destroy": (None, [_vp]),
     "sw_moe_forward": (_i, [_vp, _pd, _pl, _vp, _vp, _i, _vp]),

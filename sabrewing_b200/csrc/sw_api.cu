@@ -745,6 +745,34 @@ extern "C" int lag_cuda_expert_q4(float *out, const float *x, const void *p13, c
     return lag_group_core(out, x, p13, (const float *)s13, p2, (const float *)s2, &zero, &zero, &one, 1, &zero, &zero, &w1, 1, 1, I, D);
 }
 
+// fp4 pair (c/backend_cuda_laguna.h:83-99): same conventions as the int4 calls.
+extern "C" int lag_cuda_matmul_fp4(float *y, const float *x, const void *packed, const void *es, int S, int I, int O) {
+    if (!g_lag.ok || S <= 0 || O <= 0 || I <= 0 || (I & 31)) return -1;          // scale blocks are 32 wide
+    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st};
+    return lag_roundtrip(y, x, (size_t)S * I * 4, (size_t)S * O * 4, [&] {
+        return sw_launch_fp4_rows(cfg, (const float *)g_lag.dx.p, packed, es, (float *)g_lag.dy.p, S, I, O);
+    });
+}
+
+extern "C" int lag_cuda_moe_experts_fp4(float *out, const float *x, const void *gu_q, const void *gu_es,
+                                        const void *dn_q, const void *dn_es, const int *sel, const float *w, int K,
+                                        int I, int D, float limit) {
+    if (!g_lag.ok || K < 0 || K > 4096 || I <= 0 || D <= 0 || (D & 31) || (I & 31)) return -1;
+    if (K > 0 && (!sel || !w)) return -1;
+    const size_t ib = (size_t)(K > 0 ? K : 1) * 8;                                // sel [K] int32, then w [K] f32
+    if (g_lag.didx.ensure(ib) || g_lag.hidx.ensure(ib) || g_lag.dglu.ensure((size_t)(K + 1) * I * 4) ||
+        g_lag.dslot.ensure((size_t)(K + 1) * D * 4)) return -1;
+    if (K > 0) { memcpy(g_lag.hidx.p, sel, (size_t)K * 4); memcpy((char *)g_lag.hidx.p + (size_t)K * 4, w, (size_t)K * 4); }
+    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st};
+    return lag_roundtrip(out, x, (size_t)D * 4, (size_t)D * 4, [&] {
+        if (K > 0 && cudaMemcpyAsync(g_lag.didx.p, g_lag.hidx.p, (size_t)K * 8, cudaMemcpyHostToDevice, g_lag.st) != cudaSuccess) { cudaGetLastError(); return -1; }
+        const int *dsel = (const int *)g_lag.didx.p;
+        const float *dw = (const float *)((const char *)g_lag.didx.p + (size_t)K * 4);
+        return sw_launch_fp4_experts(cfg, (const float *)g_lag.dx.p, gu_q, gu_es, dn_q, dn_es, dsel, dw, K, I, D, limit,
+                                     (float *)g_lag.dglu.p, (float *)g_lag.dslot.p, (float *)g_lag.dy.p);
+    });
+}
+
 extern "C" int lag_cuda_matmul_q4(float *y, const float *x, const void *packed, const void *scale, int S, int I, int O) {
     if (!g_lag.ok || S <= 0 || O <= 0 || I <= 0 || (I % 32)) return -1;
     // a single group of S packed rows through the row-output form of the grouped kernel

@@ -102,3 +102,9 @@ int sw_launch_combine(const SwLaunchCfg &c, const float *slots, const int *rowof
                       float route_scale, int mode, int expert_lo, int expert_cnt);
 int sw_launch_finish(const SwLaunchCfg &c, const float *routed, const float *add, int add_slices, float *out,
                      int T, int D, float route_scale, int has_add);
+// fp4 (e2m1 + ue8m0 block-32) products of the lag_cuda_* tier (sw_fp4.cu)
+int sw_launch_fp4_rows(const SwLaunchCfg &c, const float *x, const void *P, const void *ES, float *y, int S, int I, int O);
+int sw_launch_fp4_experts(const SwLaunchCfg &c, const float *x, const void *gu_q, const void *gu_es, const void *dn_q,
+                          const void *dn_es, const int *sel, const float *w, int K, int I, int D, float limit,
+                          float *glu, float *part, float *out);
+

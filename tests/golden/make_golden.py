@@ -10,7 +10,10 @@ reference produced for them: `ref_out` = hin + MoE(x) from moe_block()
 (c/moe_block.h:18-54) in its exact (double-accumulate) mode, `ref_out_grouped` from
 lag_moe_group (c/laguna.c:689-787) where the layer is expressible by the Laguna
 glue, and kernel-level outputs of matmul_q4_kb / matmul_f32 / matmul_bf16_k /
-softmax_row / moe_topk / quant_row_i4.
+softmax_row / moe_topk / quant_row_i4, and (fp4.npz) of matmul_fp4_kb (c/moe_quant.h:259-340)
+and the clamped fp4 expert loop (c/deepseek.c:820-842).
+
+    python tests/golden/make_golden.py fp4      # only that fixture
 """
 import os
 import sys
@@ -39,10 +42,36 @@ CASES = {
 }
 
 
+def make_fp4(ref):
+    """e2m1 codes with ue8m0 exponents around 127 (and the two special bytes 0 and 0xFF)."""
+    rng = np.random.default_rng(4242)
+    I, O, S = 96, 20, 3
+    q = rng.integers(0, 256, (O, I // 2), dtype=np.uint8)
+    es = rng.integers(120, 132, (O, I // 32), dtype=np.uint8)
+    es[3, 1] = 0; es[7, 0] = 0xFF
+    x = rng.standard_normal((S, I), dtype=np.float32)
+    k = dict(x=x, q=q, es=es, y_exact=ref.matmul_fp4(x, q, es, 1), y_simd=ref.matmul_fp4(x, q, es, 0))
+    # fused experts: E=5 experts, D=64, I=32, K=3 given in a non-sorted order, limit small enough to clamp
+    E, D, I2, lim = 5, 64, 32, 3.0
+    gu_q = rng.integers(0, 256, (E * 2 * I2, D // 2), dtype=np.uint8)
+    gu_es = rng.integers(124, 130, (E * 2 * I2, D // 32), dtype=np.uint8)
+    dn_q = rng.integers(0, 256, (E * D, I2 // 2), dtype=np.uint8)
+    dn_es = rng.integers(124, 130, (E * D, I2 // 32), dtype=np.uint8)
+    xe = rng.standard_normal(D, dtype=np.float32)
+    sel = np.array([4, 0, 2], np.int32); w = np.array([0.5, 0.3, 0.2], np.float32)
+    k.update(e_x=xe, gu_q=gu_q, gu_es=gu_es, dn_q=dn_q, dn_es=dn_es, sel=sel, w=w, limit=np.float32(lim),
+             e_exact=ref.experts_fp4(xe, gu_q, gu_es, dn_q, dn_es, sel, w, I2, D, lim, 1),
+             e_simd=ref.experts_fp4(xe, gu_q, gu_es, dn_q, dn_es, sel, w, I2, D, lim, 0))
+    np.savez_compressed(os.path.join(HERE, "fp4.npz"), **k)
+    print("fp4", sorted(k))
+
+
 def main():
     oracle.build()
     ref = oracle.load_ref()
     assert ref is not None, "reference checkout not available"
+    if sys.argv[1:] == ["fp4"]:
+        return make_fp4(ref)
     for name, (cfg, bstd) in CASES.items():
         a = synth.make_layer(cfg, corr_bias_std=bstd)
         x = synth.make_tokens(cfg)
@@ -83,6 +112,7 @@ def main():
         k["g%d_y" % gs] = ref.matmul_i4_grouped(xg, pq, ps, gs)
     np.savez_compressed(os.path.join(HERE, "kernels.npz"), **k)
     print("kernels", sorted(k))
+    make_fp4(ref)
 
 
 if __name__ == "__main__":

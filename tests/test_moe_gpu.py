@@ -233,6 +233,60 @@ def test_lag_matmuls_match_cpu(orc):
     l.lag_cuda_free(dW)
 
 
+def test_lag_fp4_golden_and_selftest_bars(orc):
+    """The fp4 pair: committed reference fixtures, then the reference self-test's two cases with its bars
+    (c/deepseek.c:1500-1590: matmul max_rel < 1e-3, fused K experts L2rel < 1e-5)."""
+    import os
+    import conftest
+    l = _lag()
+    z = np.load(os.path.join(conftest.GOLDEN, "fp4.npz"))
+    x, q, es = z["x"], z["q"], z["es"]
+    y = np.empty_like(z["y_exact"])
+    dq, de = _up(l, q), _up(l, es)
+    assert l.lag_cuda_matmul_fp4(y.ctypes.data, x.ctypes.data, dq, de, x.shape[0], x.shape[1], q.shape[0]) == 0
+    assert rel_l2(y, z["y_exact"]) < 1e-6
+    l.lag_cuda_free(dq); l.lag_cuda_free(de)
+    D, I = z["gu_q"].shape[1] * 2, z["dn_q"].shape[1] * 2
+    d = [_up(l, z[k]) for k in ("gu_q", "gu_es", "dn_q", "dn_es")]
+    out = np.empty(D, np.float32)
+    sel = np.ascontiguousarray(z["sel"]); w = np.ascontiguousarray(z["w"])
+    assert l.lag_cuda_moe_experts_fp4(out.ctypes.data, z["e_x"].ctypes.data, *d, sel.ctypes.data, w.ctypes.data,
+                                      len(sel), I, D, float(z["limit"])) == 0
+    assert rel_l2(out, z["e_exact"]) < 1e-5
+    for p in d:
+        l.lag_cuda_free(p)
+
+    # the reference's self-test shapes: I=2048, D=4096, E=4, K=3, limit 10, exponents 120..131
+    rng = np.random.default_rng(1234)
+    I, D, E, lim = 2048, 4096, 4, 10.0
+    gu = rng.integers(0, 256, (E * 2 * I, D // 2), dtype=np.uint8)
+    gue = rng.integers(120, 132, (E * 2 * I, D // 32), dtype=np.uint8)
+    dn = rng.integers(0, 256, (E * D, I // 2), dtype=np.uint8)
+    dne = rng.integers(120, 132, (E * D, I // 32), dtype=np.uint8)
+    x = (rng.random((1, D), dtype=np.float32) * 2 - 1)
+    d = [_up(l, a) for a in (gu, gue, dn, dne)]
+    got = np.empty((1, 2 * I), np.float32)
+    assert l.lag_cuda_matmul_fp4(got.ctypes.data, x.ctypes.data, d[0], d[1], 1, D, 2 * I) == 0
+    want = orc.matmul_fp4(x, gu[:2 * I], gue[:2 * I], 1)
+    assert (np.abs(got - want) / (np.abs(want) + 1e-6)).max() < 1e-3
+    # several rows in one call
+    x3 = (rng.random((3, D), dtype=np.float32) * 2 - 1)
+    got3 = np.empty((3, 2 * I), np.float32)
+    assert l.lag_cuda_matmul_fp4(got3.ctypes.data, x3.ctypes.data, d[0], d[1], 3, D, 2 * I) == 0
+    assert rel_l2(got3, orc.matmul_fp4(x3, gu[:2 * I], gue[:2 * I], 1)) < 1e-6
+    sel = np.array([0, 2, 3], np.int32); w = np.array([0.5, 0.3, 0.2], np.float32)
+    out = np.empty(D, np.float32)
+    assert l.lag_cuda_moe_experts_fp4(out.ctypes.data, x.ctypes.data, *d, sel.ctypes.data, w.ctypes.data, 3, I, D, lim) == 0
+    want = orc.experts_fp4(x[0], gu, gue, dn, dne, sel, w, I, D, lim, 1)
+    assert rel_l2(out, want) < 1e-5
+    # K = 0 gives zeros; a width that is not a multiple of 32 is refused
+    assert l.lag_cuda_moe_experts_fp4(out.ctypes.data, x.ctypes.data, *d, sel.ctypes.data, w.ctypes.data, 0, I, D, lim) == 0
+    assert not out.any()
+    assert l.lag_cuda_matmul_fp4(got.ctypes.data, x.ctypes.data, d[0], d[1], 1, D - 16, 8) == -1
+    for p in d:
+        l.lag_cuda_free(p)
+
+
 def test_lag_grouped_is_bit_identical_to_per_token(orc):
     """moe_group vs moe_experts on overlapping selections: max|diff| must be exactly 0."""
     l = _lag()

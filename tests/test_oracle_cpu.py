@@ -93,6 +93,26 @@ def test_empty_expert_groups_are_skipped(orc):
     assert g["G"] == 3 and g["gexp"].tolist() == [1, 5, 9] and g["gcnt"].tolist() == [1, 2, 1]
     assert g["grow"].tolist() == [0, 0, 1, 1] and g["rowof"].tolist() == [1, 0, 2, 3]
 
+def test_fp4_goldens(orc, ref):
+    """fp4 products against fixtures made by the compiled reference (matmul_fp4_kb, the clamped expert loop)."""
+    z = np.load(__import__("os").path.join(__import__("conftest").GOLDEN, "fp4.npz"))
+    assert np.array_equal(orc.matmul_fp4(z["x"], z["q"], z["es"], 1), z["y_exact"])
+    assert rel_l2(orc.matmul_fp4(z["x"], z["q"], z["es"], 0), z["y_exact"]) < 1e-6
+    assert rel_l2(z["y_simd"], z["y_exact"]) < 1e-6
+    I, D = z["dn_q"].shape[1] * 2, z["gu_q"].shape[1] * 2
+    args = (z["e_x"], z["gu_q"], z["gu_es"], z["dn_q"], z["dn_es"], z["sel"], z["w"], I, D, float(z["limit"]))
+    assert np.array_equal(orc.experts_fp4(*args, 1), z["e_exact"])
+    assert rel_l2(orc.experts_fp4(*args, 0), z["e_exact"]) < 1e-5
+    # the fixture really clamps: without the limit the result differs
+    assert rel_l2(orc.experts_fp4(*args[:-1], 1e30, 1), z["e_exact"]) > 1e-3
+    # ue8m0 special bytes: 0xFF contributes nothing, 0 is 2^-127
+    y = orc.matmul_fp4(z["x"], z["q"], z["es"], 1)
+    es2 = z["es"].copy(); es2[7, :] = 0xFF
+    assert np.all(orc.matmul_fp4(z["x"], z["q"], es2, 1)[:, 7] == 0) and np.all(np.isfinite(y))
+    if ref is not None:
+        assert np.array_equal(ref.matmul_fp4(z["x"], z["q"], z["es"], 1), z["y_exact"])
+        assert np.array_equal(ref.experts_fp4(*args, 1), z["e_exact"])
+
 
 @pytest.mark.parametrize("base,kw", [
     ("c2", dict(D=256, E=32, K=6, I=128, SI=64, T=21)),
