@@ -224,7 +224,7 @@ static int sw_expert_path(int D, int I, int rows, int groups) {
 static int sw_resolve_path(const SwQ4Args &a, const void *gu_q, const void *dn_q, int D, int I, const SwUmmaScratch *um) {
     int path = a.gs > 0 ? 0 : sw_expert_path(D, I, a.max_rows, a.max_groups);   // group scales: CUDA-core kernels
     if (path >= 2 && (((uintptr_t)gu_q | (uintptr_t)dn_q) & 15)) path = 1;    // TMA wants 16-byte aligned blobs
-    if (path == 3 && !um) path = 2;
+    if (path == 3 && (!um || I % 128 || D % 256)) path = 2;                   // the tcgen05 kernels walk whole tile pairs
     return path;
 }
 

@@ -35,12 +35,12 @@
 #define UM_STAGES 4
 #define UM_RAW_A 4096                    // 128 rows x 32 B of int4
 #define UM_BT 16384                      // one activation tile: 128 rows x 128 B
-#define UM_STAGE_BYTES (UM_RAW_A + 2 * UM_BT)
+#define UM_STAGE_BYTES (2 * UM_RAW_A + 2 * UM_BT)   // a pair of weight tiles shares the activation tiles of a slot
 #define UM_A16 16384                     // dequantised A tile: 128 rows x 64 fp16
 #define UM_WAIT_LIMIT (1u << 24)
 #define UM_ABUF 4                        // dequantised A tiles in flight
 #define UM_DQ_WARPS 8
-#define UM_THREADS ((UM_DQ_WARPS + 4 + 2) * 32)
+#define UM_THREADS ((UM_DQ_WARPS + 4 + 3) * 32)   // dequant, epilogue, TMA, two MMA issuers
 
 __device__ __forceinline__ unsigned um_s32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void um_bar_init(unsigned bar, unsigned count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory"); }
@@ -162,14 +162,14 @@ struct UmArgs {
 
 template <bool GATEUP>
 __global__ void __launch_bounds__(UM_THREADS, 1)
-k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmW2, const __grid_constant__ CUtensorMap tmW4,
+k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmW2,
           const __grid_constant__ CUtensorMap tmH16, const __grid_constant__ CUtensorMap tmH32,
           const __grid_constant__ CUtensorMap tmH64, const __grid_constant__ CUtensorMap tmH128,
           const __grid_constant__ CUtensorMap tmL16, const __grid_constant__ CUtensorMap tmL32,
           const __grid_constant__ CUtensorMap tmL64, const __grid_constant__ CUtensorMap tmL128,
           const UmArgs a) {
     extern __shared__ unsigned char um_dyn[];
-    __shared__ unsigned long long b_raw_full[UM_STAGES], b_raw_free[UM_STAGES], b_a_full[UM_ABUF], b_a_free[UM_ABUF], b_acc_full[2], b_acc_free[2];
+    __shared__ unsigned long long b_raw_full[UM_STAGES], b_raw_free[UM_STAGES], b_a_full[UM_ABUF], b_a_free[UM_ABUF], b_acc_full[4], b_acc_free[2];
     __shared__ unsigned s_tmem;
     __shared__ int s_abort;
     unsigned char *smem = (unsigned char *)(((uintptr_t)um_dyn + 1023) & ~(uintptr_t)1023);
@@ -177,16 +177,19 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KD = a.KD, OUT = a.OUT;
     const int nrows_w = GATEUP ? 2 * OUT : OUT;
-    constexpr int OPT = GATEUP ? 64 : 128;                              // outputs per tile
-    const int mtiles = (OUT + OPT - 1) / OPT;
+    // A CTA item is a chunk of token rows times a PAIR of 128-row weight tiles that share the chunk's activation tiles:
+    // gate/up: the gate rows of 128 outputs and their up rows; down: two neighbouring tiles (256 outputs).
+    constexpr int OPP = GATEUP ? 128 : 256;                             // outputs per pair
+    const int pairs = OUT / OPP;
     const int NST = KD >> 6;                                            // 64-column stages per tile
-    const int items = *a.nchunks * mtiles;
+    const int items = *a.nchunks * pairs;
     volatile int *abortp = &s_abort;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < UM_STAGES; i++) { um_bar_init(um_s32(&b_raw_full[i]), 1); um_bar_init(um_s32(&b_raw_free[i]), 1); }
+        for (int i = 0; i < UM_STAGES; i++) { um_bar_init(um_s32(&b_raw_full[i]), 1); um_bar_init(um_s32(&b_raw_free[i]), 2); }
         for (int i = 0; i < UM_ABUF; i++) { um_bar_init(um_s32(&b_a_full[i]), UM_DQ_WARPS / UM_ABUF); um_bar_init(um_s32(&b_a_free[i]), 1); }
-        for (int i = 0; i < 2; i++) { um_bar_init(um_s32(&b_acc_full[i]), 1); um_bar_init(um_s32(&b_acc_free[i]), 4); }
+        for (int i = 0; i < 4; i++) um_bar_init(um_s32(&b_acc_full[i]), 1);
+        for (int i = 0; i < 2; i++) um_bar_init(um_s32(&b_acc_free[i]), 4);
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -199,31 +202,32 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem = s_tmem;
 
-    // item -> (chunk, m-tile): chunks of one group and m-tile are neighbours, so a weight tile is re-read from L2
-    auto decode = [&](int item, int &gi, int &c0, int &mt) {
-        const int ch = item / mtiles; mt = item - ch * mtiles;
+    // item -> (chunk, tile pair): the pairs of one chunk are neighbours, so its activation rows stay in L2
+    auto decode = [&](int item, int &gi, int &c0, int &pr) {
+        const int ch = item / pairs; pr = item - ch * pairs;
         const int2 c = a.chunks[ch]; gi = c.x; c0 = c.y;
     };
 
-    // Small token tiles pack several 64-column sub-stages into one ring slot (one barrier round trip and
-    // one weight TMA per 128 or 256 columns): 4 sub-stages for <=16 rows, 2 for <=32, else 1.
-    // Slot layout: [raw int4: 128 rows x 32*KSUB B] then per sub-stage [hi tile: R x 128 B][lo tile: R x 128 B]
+    // Small token tiles pack two 64-column sub-stages into one ring slot (one barrier round trip and one
+    // weight TMA per 128 columns).
+    // Slot layout: [raw int4 of the tile pair: 256 rows x 32*KSUB B] then per sub-stage [hi tile: R x 128 B][lo tile: R x 128 B].
+    // Raw rows: the 128 rows of tile 0 (gate rows), then the 128 rows of tile 1 (up rows).
     auto tile_rows = [](int n) { return n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : 128; };
-    auto substages = [&](int R) { return (R == 16 && (NST & 3) == 0) ? 4 : (R <= 32 && (NST & 1) == 0) ? 2 : 1; };
+    auto substages = [&](int) { return 1; };                           // one 64-column sub-stage per ring slot
 
     if (warp == UM_DQ_WARPS + 4) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             unsigned kk = 0;
             for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
-                int gi, c0, mt; decode(item, gi, c0, mt);
+                int gi, c0, pr; decode(item, gi, c0, pr);
                 const int e = a.gexp[gi] - a.expert_lo, n = min(128, a.gcnt[gi] - c0), row0 = a.gbeg[gi] + c0;
                 const int R = tile_rows(n), KSUB = substages(R);
                 const CUtensorMap *th = R == 16 ? &tmH16 : R == 32 ? &tmH32 : R == 64 ? &tmH64 : &tmH128;
                 const CUtensorMap *tl = R == 16 ? &tmL16 : R == 32 ? &tmL32 : R == 64 ? &tmL64 : &tmL128;
-                const CUtensorMap *tw = KSUB == 4 ? &tmW4 : KSUB == 2 ? &tmW2 : &tmW;
-                const int wrow = e * nrows_w + mt * OPT;
-                const unsigned rawA = 4096u * KSUB, bt = (unsigned)R * 128u;
+                const CUtensorMap *tw = KSUB == 2 ? &tmW2 : &tmW;
+                const int wrow = e * nrows_w + pr * OPP;                 // first weight row of the pair (gate rows for gate/up)
+                const unsigned rawA = 2u * UM_RAW_A * KSUB, bt = (unsigned)R * 128u;
                 for (int sl = 0; sl < NST / KSUB; sl++, kk++) {
                     const int s = kk % UM_STAGES;
                     if (kk >= UM_STAGES && !um_bar_wait(um_s32(&b_raw_free[s]), ((kk / UM_STAGES) - 1) & 1, abortp)) {
@@ -232,12 +236,8 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
                     unsigned char *sp = smem + s * UM_STAGE_BYTES;
                     const unsigned bar = um_s32(&b_raw_full[s]);
                     um_bar_expect(bar, rawA + 2u * KSUB * bt);
-                    if (GATEUP) {
-                        um_tma_2d(um_s32(sp), tw, sl * 32 * KSUB, wrow, bar);                 // 64 gate rows
-                        um_tma_2d(um_s32(sp + rawA / 2), tw, sl * 32 * KSUB, wrow + OUT, bar); // 64 up rows
-                    } else {
-                        um_tma_2d(um_s32(sp), tw, sl * 32 * KSUB, wrow, bar);
-                    }
+                    um_tma_2d(um_s32(sp), tw, sl * 32 * KSUB, wrow, bar);                               // 128 rows
+                    um_tma_2d(um_s32(sp + rawA / 2), tw, sl * 32 * KSUB, wrow + (GATEUP ? OUT : 128), bar); // 128 rows
                     for (int u = 0; u < KSUB; u++) {
                         um_tma_2d(um_s32(sp + rawA + (2 * u) * bt), th, (sl * KSUB + u) * 64, row0, bar);
                         um_tma_2d(um_s32(sp + rawA + (2 * u + 1) * bt), tl, (sl * KSUB + u) * 64, row0, bar);
@@ -245,69 +245,79 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
                 }
             }
         }
-    } else if (warp == UM_DQ_WARPS + 5) {
-        // ------------------------------ MMA issuer ------------------------------
+    } else if (warp >= UM_DQ_WARPS + 5) {
+        // ------------------------------ MMA issuers ------------------------------
+        // Two warps, one thread each: issuer t multiplies tile t of the pair into its own accumulator columns.
+        // A lone thread pays the full latency of every instruction (a barrier test ~100 cycles, a tcgen05.commit ~250,
+        // an MMA issue ~55), so one thread cannot keep up with 8 MMAs per 1024 cycles; two can.
         if (lane == 0) {
-            unsigned kk = 0, ks = 0, tile = 0;                          // sub-stage, ring-slot and tile counters
-            for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, tile++) {
-                int gi, c0, mt; decode(item, gi, c0, mt);
+            const int t = warp - (UM_DQ_WARPS + 5);
+            unsigned ks = 0, nitem = 0;                                  // ring-slot and item counters
+            for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, nitem++) {
+                int gi, c0, pr; decode(item, gi, c0, pr);
                 const int n = min(128, a.gcnt[gi] - c0);
-                // hi and lo activation tiles lie back to back, so ONE MMA with N = 2R multiplies both: accumulator
-                // columns [0,R) hold A*hi, [R,2R) hold A*lo.  (A tcgen05.mma of M=128, K=16 occupies the tensor
-                // pipe for ~155 cycles whatever its N up to 256, so the second half of the columns is free.)
-                const int R = tile_rows(n), KSUB = substages(R);
-                const unsigned idesc = (1u << 4) | ((unsigned)((2 * R) >> 3) << 17) | ((128u >> 4) << 24);   // f32 accum, f16 x f16, K-major
-                const unsigned acc = tile & 1, d_tmem = tmem + acc * 256;
-                if (tile >= 2 && !um_bar_wait(um_s32(&b_acc_free[acc]), ((tile >> 1) - 1) & 1, abortp)) {
+                // Two MMAs of N = R per 16 columns, A*hi then A*lo, accumulate into the SAME R accumulator columns, so a
+                // tile needs 128 columns at most and tensor memory holds two buffers of two tiles: the epilogue of one
+                // item runs under the MMAs of the next.
+                const int R = tile_rows(n);
+                const unsigned idesc = (1u << 4) | ((unsigned)(R >> 3) << 17) | ((128u >> 4) << 24);   // f32 accum, f16 x f16, K-major
+                const unsigned q = nitem & 1, d_tmem = tmem + (q * 2 + t) * 128;
+                if (nitem >= 2 && !um_bar_wait(um_s32(&b_acc_free[q]), ((nitem >> 1) - 1) & 1, abortp)) {
                     atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned rawA = 4096u * KSUB, bt = (unsigned)R * 128u;
-                for (int st = 0; st < NST; st++, kk++) {
-                    const int u = st % KSUB, b = kk % UM_ABUF;
-                    const int s = ks % UM_STAGES;
-                    if (!um_bar_wait(um_s32(&b_a_full[b]), (kk / UM_ABUF) & 1, abortp)) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
+                const unsigned bt = (unsigned)R * 128u;
+                bool ok = true;
+                for (int st = 0; st < NST; st++, ks++) {
+                    const unsigned s = ks % UM_STAGES, kk = 2 * ks + t, b = kk % UM_ABUF;
+                    if (!um_bar_wait(um_s32(&b_a_full[b]), (kk / UM_ABUF) & 1, abortp)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const unsigned char *sp = smem + s * UM_STAGE_BYTES;
                     const uint64_t da = um_desc(um_s32(a16 + b * UM_A16));
-                    const uint64_t db = um_desc(um_s32(sp + rawA + (2 * u) * bt));
+                    const uint64_t dh = um_desc(um_s32(smem + s * UM_STAGE_BYTES + 2 * UM_RAW_A)), dl = um_desc(um_s32(smem + s * UM_STAGE_BYTES + 2 * UM_RAW_A + bt));
 #pragma unroll
-                    for (int k = 0; k < 4; k++)                         // 16 columns = 32 bytes per step
-                        um_mma(d_tmem, da + 2 * k, db + 2 * k, idesc, (st | k) ? 1u : 0u);
-                    um_commit(um_s32(&b_a_free[b]));
-                    if (u == KSUB - 1) { um_commit(um_s32(&b_raw_free[s])); ks++; }
+                    for (int k = 0; k < 4; k++) {                       // 16 columns = 32 bytes per step
+                        um_mma(d_tmem, da + 2 * k, dh + 2 * k, idesc, (st | k) ? 1u : 0u);
+                        um_mma(d_tmem, da + 2 * k, dl + 2 * k, idesc, 1u);
+                    }
+                    // one commit per slot and issuer: when both have arrived the slot returns to the TMA warp and the
+                    // pair's dequantised tiles to the dequantising warps
+                    um_commit(um_s32(&b_raw_free[s]));
                 }
-                if (*abortp) break;
-                um_commit(um_s32(&b_acc_full[acc]));
+                if (!ok) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
+                um_commit(um_s32(&b_acc_full[q * 2 + t]));
             }
         }
     } else if (warp < UM_DQ_WARPS) {
         // ------------------------------ dequantise ------------------------------
-        // Four groups of two warps; group g dequantises the sub-stages kk with kk % 4 == g into A tile g, so four
-        // sub-stages are in flight at once (the chain wait -> load -> convert -> store -> fence -> arrive is long).
-        // A thread converts four 16-byte pieces q = tg + 64*i of the raw tile; consecutive lanes read consecutive
-        // pieces (no bank conflicts on the loads).  Piece q is half (q & 1) of raw row q/2.
-        const int grp = warp >> 1, tg = threadIdx.x & 63;
+        // Four groups of two warps; group g dequantises the (sub-stage, tile) steps kk = 2*st + t with kk % 4 == g into
+        // A tile g, so four steps are in flight at once (the chain wait -> load -> convert -> store -> fence -> arrive
+        // is long); a group always serves the same tile t = g & 1 of the pair.
+        // A thread converts four 16-byte pieces q = tg + 64*i of the tile's raw rows; consecutive lanes read consecutive
+        // pieces (no bank conflicts on the loads).  Piece q is half (q & 1) of the tile's raw row q/2.
+        const int grp = warp >> 1, tg = threadIdx.x & 63, tsel = grp & 1;
         unsigned kk = 0, slot_base = 0;
         for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
-            int gi, c0, mt; decode(item, gi, c0, mt);
+            int gi, c0, pr; decode(item, gi, c0, pr);
             const int R = tile_rows(min(128, a.gcnt[gi] - c0)), KSUB = substages(R);
             const int pitch = 32 * KSUB;                                // bytes per raw row in the slot
             int rawoff[4], dstoff[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const int q = tg + 64 * i, rr = q >> 1, h = q & 1;      // raw row 0..127 (gate rows 0..63 then up rows), half
-                const int trow = GATEUP ? 2 * (rr & 63) + (rr >> 6) : rr;   // tile row: gate j -> 2j, up j -> 2j+1
-                rawoff[i] = rr * pitch + h * 16;
+                const int q = tg + 64 * i, rr = q >> 1, h = q & 1;      // the tile's row 0..127, half
+                const int trow = rr;
+                const int srow = tsel * 128 + rr;                       // row in the slot
+                rawoff[i] = srow * pitch + h * 16;
                 dstoff[i] = trow * 128 + (((h * 4) ^ (trow & 7)) << 4);  // chunk (4h + j) goes to (4h + j) ^ (trow & 7)
             }
-            for (int st = 0; st < NST; st++, kk++) {
+            for (int st2 = 0; st2 < 2 * NST; st2++, kk++) {
                 if ((kk & 3) != (unsigned)grp) continue;
+                const int st = st2 >> 1;
                 const int u = st % KSUB;
                 const unsigned ks = slot_base + st / KSUB;
                 const int s = ks % UM_STAGES;
                 bool ok = um_bar_wait(um_s32(&b_raw_full[s]), (ks / UM_STAGES) & 1, abortp);
-                if (ok && kk >= UM_ABUF) ok = um_bar_wait(um_s32(&b_a_free[grp]), ((kk / UM_ABUF) - 1) & 1, abortp);
+                // A tile grp was last read by the MMAs of the slot two back: wait until that slot is done
+                if (ok && ks >= 2) ok = um_bar_wait(um_s32(&b_raw_free[(ks - 2) % UM_STAGES]), ((ks - 2) / UM_STAGES) & 1, abortp);
                 if (!ok) { if (lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; } break; }
                 const unsigned char *raw = smem + s * UM_STAGE_BYTES + u * 32;
                 unsigned char *dstb = a16 + grp * UM_A16;
@@ -317,18 +327,12 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     // (4h + j) ^ x7 == ((4h) ^ x7) ^ j for j < 4: the four chunks of a half are the base slot xor j
-                    // In the gate/up tile four consecutive raw rows land on tile rows 2j, 2j+2, 2j+4, 2j+6, whose
-                    // slots would collide pairwise; rows 2 and 3 of each four store their chunks in the order
-                    // 1,0,3,2 instead (jx), which makes the eight lanes of a quarter warp hit eight different slots.
                     unsigned char *d = dstb + (dstoff[i] & ~0x7F);
-                    const int jx = GATEUP ? (dstoff[i] >> 9) & 1 : 0;
-                    const int base = ((dstoff[i] >> 4) & 7) ^ jx;
-                    const unsigned w0 = jx ? w[i].y : w[i].x, w1 = jx ? w[i].x : w[i].y;
-                    const unsigned w2 = jx ? w[i].w : w[i].z, w3 = jx ? w[i].z : w[i].w;
-                    *reinterpret_cast<uint4 *>(d + ((base ^ 0) << 4)) = um_dq(w0);
-                    *reinterpret_cast<uint4 *>(d + ((base ^ 1) << 4)) = um_dq(w1);
-                    *reinterpret_cast<uint4 *>(d + ((base ^ 2) << 4)) = um_dq(w2);
-                    *reinterpret_cast<uint4 *>(d + ((base ^ 3) << 4)) = um_dq(w3);
+                    const int base = (dstoff[i] >> 4) & 7;
+                    *reinterpret_cast<uint4 *>(d + ((base ^ 0) << 4)) = um_dq(w[i].x);
+                    *reinterpret_cast<uint4 *>(d + ((base ^ 1) << 4)) = um_dq(w[i].y);
+                    *reinterpret_cast<uint4 *>(d + ((base ^ 2) << 4)) = um_dq(w[i].z);
+                    *reinterpret_cast<uint4 *>(d + ((base ^ 3) << 4)) = um_dq(w[i].w);
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic stores -> tensor-core reads
                 __syncwarp();
@@ -340,52 +344,58 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
         // ------------------------------ epilogue (four warps, one TMEM lane quarter each) ------------------------------
         const int q = warp & 3;                                         // TMEM lane quarter of this warp
         const int trow = q * 32 + lane;                                 // tile row held by this thread
-        unsigned tile = 0;
-        for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, tile++) {
-            int gi, c0, mt; decode(item, gi, c0, mt);
+        unsigned nitem = 0;
+        for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, nitem++) {
+            int gi, c0, pr; decode(item, gi, c0, pr);
             const int e = a.gexp[gi] - a.expert_lo, n = min(128, a.gcnt[gi] - c0), row0 = a.gbeg[gi] + c0;
             const float *ws = a.Ws + (size_t)e * nrows_w;
-            const unsigned acc = tile & 1;
-            if (!um_bar_wait(um_s32(&b_acc_full[acc]), (tile >> 1) & 1, abortp)) {
+            const unsigned qb = nitem & 1;                              // accumulator buffer of this item
+            if (!um_bar_wait(um_s32(&b_acc_full[qb * 2]), (nitem >> 1) & 1, abortp) ||
+                !um_bar_wait(um_s32(&b_acc_full[qb * 2 + 1]), (nitem >> 1) & 1, abortp)) {
                 if (lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; }
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float sc;                                                   // scale of this thread's weight row
-            int o;                                                      // output index of this thread's row
-            if (GATEUP) { o = mt * 64 + (trow >> 1); sc = o < OUT ? ws[(trow & 1) * OUT + o] : 0.f; }
-            else        { o = mt * 128 + trow;       sc = o < OUT ? ws[o] : 0.f; }
-            const int R = tile_rows(n);
-            for (int cb = 0; cb < n; cb += 32) {
-                float v[32], p[32];
-                um_ld32(tmem + acc * 256 + cb + ((unsigned)(q * 32) << 16), v);          // A * hi
-                um_ld32(tmem + acc * 256 + R + cb + ((unsigned)(q * 32) << 16), p);      // A * lo
-#pragma unroll
-                for (int j = 0; j < 32; j++) v[j] += p[j];
-                if (GATEUP) {
-                    __half *Yh = reinterpret_cast<__half *>(a.Y0), *Yl = reinterpret_cast<__half *>(a.Y1);
-                    const int pcol = um_perm8(o);
+            const unsigned t0 = tmem + qb * 256 + ((unsigned)(q * 32) << 16), t1 = t0 + 128;   // tile 0 / tile 1 of this lane
+            if (GATEUP) {
+                // lane r holds gate row r in tile 0 and up row r in tile 1: output o = pair*128 + r
+                const int o = pr * 128 + trow;
+                const float sg = o < OUT ? ws[o] : 0.f, su = o < OUT ? ws[OUT + o] : 0.f;
+                __half *Yh = reinterpret_cast<__half *>(a.Y0), *Yl = reinterpret_cast<__half *>(a.Y1);
+                const int pcol = um_perm8(o);
+                for (int cb = 0; cb < n; cb += 32) {
+                    float g[32], u[32];
+                    um_ld32(t0 + cb, g);
+                    um_ld32(t1 + cb, u);
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
-                        const float mine = v[j] * sc;
-                        const float other = __shfl_xor_sync(SW_FULL_MASK, mine, 1);   // even lanes: gate, odd lanes: up
-                        if (!(lane & 1) && cb + j < n && o < OUT) {
-                            const float y = (mine / (1.f + expf(-mine))) * other;
+                        if (cb + j < n && o < OUT) {
+                            const float gv = g[j] * sg;
+                            const float y = (gv / (1.f + expf(-gv))) * (u[j] * su);
                             __half hi, lo; um_split(y, hi, lo);
                             const size_t pos = (size_t)(row0 + cb + j) * OUT + pcol;
                             Yh[pos] = hi; Yl[pos] = lo;
                         }
                     }
-                } else {
-                    float *Y = reinterpret_cast<float *>(a.Y0);
+                }
+            } else {
+                float *Y = reinterpret_cast<float *>(a.Y0);
 #pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        if (cb + j < n && o < OUT) Y[(size_t)(row0 + cb + j) * OUT + o] = v[j] * sc;
+                for (int t = 0; t < 2; t++) {
+                    const int o = pr * 256 + t * 128 + trow;
+                    const float sc = o < OUT ? ws[o] : 0.f;
+                    for (int cb = 0; cb < n; cb += 32) {
+                        float v[32];
+                        um_ld32((t ? t1 : t0) + cb, v);
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (cb + j < n && o < OUT) Y[(size_t)(row0 + cb + j) * OUT + o] = v[j] * sc;
+                    }
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) um_bar_arrive(um_s32(&b_acc_free[acc]));
+            if (lane == 0) um_bar_arrive(um_s32(&b_acc_free[qb]));
         }
     }
 
@@ -448,10 +458,10 @@ int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_h
                       const int *nchunks, const void *chunks, int max_chunks, int *status, long long wrows_total, bool gateup) {
     if (a.max_rows <= 0) return 0;
     if (a.KD % 64 || a.OUT <= 0 || ((uintptr_t)a.q & 15)) return -1;
-    CUtensorMap tw, tw2, tw4, th[4], tl[4];
-    if (um_make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.q, a.KD / 2, wrows_total, 32, gateup ? 64 : 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
-    if (um_make_map(&tw2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.q, a.KD / 2, wrows_total, 64, gateup ? 64 : 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
-    if (um_make_map(&tw4, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.q, a.KD / 2, wrows_total, 128, gateup ? 64 : 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
+    if ((a.OUT % (gateup ? 128 : 256)) != 0) return -1;                  // whole tile pairs only
+    CUtensorMap tw, tw2, th[4], tl[4];
+    if (um_make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.q, a.KD / 2, wrows_total, 32, 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
+    if (um_make_map(&tw2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.q, a.KD / 2, wrows_total, 64, 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
     const int R[4] = {16, 32, 64, 128};
     for (int i = 0; i < 4; i++) {
         if (um_make_map(&th[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act_hi, a.KD, a.max_rows, 64, R[i], CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
@@ -467,13 +477,13 @@ int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_h
     UmArgs ka;
     ka.Ws = a.s; ka.Y0 = Y0; ka.Y1 = Y1; ka.gexp = a.gexp; ka.gbeg = a.gbeg; ka.gcnt = a.gcnt; ka.nchunks = nchunks;
     ka.chunks = (const int2 *)chunks; ka.status = status; ka.KD = a.KD; ka.OUT = a.OUT; ka.expert_lo = a.expert_lo;
-    const int mtiles = (a.OUT + (gateup ? 64 : 128) - 1) / (gateup ? 64 : 128);
-    long long items = (long long)max_chunks * mtiles;
+    const int pairs = a.OUT / (gateup ? 128 : 256);
+    long long items = (long long)max_chunks * pairs;
     long long grid = c.num_sms;                        // one CTA per SM (shared memory and tensor memory are sized for that)
     if (grid > items) grid = items;
     if (grid < 1) grid = 1;
-    if (gateup) k_q4_umma<true><<<(unsigned)grid, UM_THREADS, SMEM, c.stream>>>(tw, tw2, tw4, th[0], th[1], th[2], th[3], tl[0], tl[1], tl[2], tl[3], ka);
-    else k_q4_umma<false><<<(unsigned)grid, UM_THREADS, SMEM, c.stream>>>(tw, tw2, tw4, th[0], th[1], th[2], th[3], tl[0], tl[1], tl[2], tl[3], ka);
+    if (gateup) k_q4_umma<true><<<(unsigned)grid, UM_THREADS, SMEM, c.stream>>>(tw, tw2, th[0], th[1], th[2], th[3], tl[0], tl[1], tl[2], tl[3], ka);
+    else k_q4_umma<false><<<(unsigned)grid, UM_THREADS, SMEM, c.stream>>>(tw, tw2, th[0], th[1], th[2], th[3], tl[0], tl[1], tl[2], tl[3], ka);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
