@@ -187,7 +187,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < UM_STAGES; i++) { um_bar_init(um_s32(&b_raw_full[i]), 1); um_bar_init(um_s32(&b_raw_free[i]), 2); }
-        for (int i = 0; i < UM_ABUF; i++) { um_bar_init(um_s32(&b_a_full[i]), UM_DQ_WARPS / UM_ABUF); um_bar_init(um_s32(&b_a_free[i]), 1); }
+        for (int i = 0; i < UM_ABUF; i++) { um_bar_init(um_s32(&b_a_full[i]), UM_DQ_WARPS / 2); um_bar_init(um_s32(&b_a_free[i]), 1); }
         for (int i = 0; i < 4; i++) um_bar_init(um_s32(&b_acc_full[i]), 1);
         for (int i = 0; i < 2; i++) um_bar_init(um_s32(&b_acc_free[i]), 4);
         s_abort = 0;
@@ -289,43 +289,41 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
         }
     } else if (warp < UM_DQ_WARPS) {
         // ------------------------------ dequantise ------------------------------
-        // Four groups of two warps; group g dequantises the (sub-stage, tile) steps kk = 2*st + t with kk % 4 == g into
-        // A tile g, so four steps are in flight at once (the chain wait -> load -> convert -> store -> fence -> arrive
-        // is long); a group always serves the same tile t = g & 1 of the pair.
-        // A thread converts four 16-byte pieces q = tg + 64*i of the tile's raw rows; consecutive lanes read consecutive
+        // Two groups of four warps: group t dequantises tile t of every slot into A tile (2*slot + t) % 4.  Four warps
+        // per tile keep the chain wait -> load -> convert -> store -> fence -> arrive short (it sits on the loop
+        // "slot s-2 done -> tile of slot s ready -> MMAs of slot s").
+        // A thread converts two 16-byte pieces q = tg + 128*i of the tile's raw rows; consecutive lanes read consecutive
         // pieces (no bank conflicts on the loads).  Piece q is half (q & 1) of the tile's raw row q/2.
-        const int grp = warp >> 1, tg = threadIdx.x & 63, tsel = grp & 1;
-        unsigned kk = 0, slot_base = 0;
+        const int tsel = warp >> 2, tg = threadIdx.x & 127;
+        unsigned slot_base = 0;
         for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
             int gi, c0, pr; decode(item, gi, c0, pr);
             const int R = tile_rows(min(128, a.gcnt[gi] - c0)), KSUB = substages(R);
             const int pitch = 32 * KSUB;                                // bytes per raw row in the slot
-            int rawoff[4], dstoff[4];
+            int rawoff[2], dstoff[2];
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int q = tg + 64 * i, rr = q >> 1, h = q & 1;      // the tile's row 0..127, half
+            for (int i = 0; i < 2; i++) {
+                const int q = tg + 128 * i, rr = q >> 1, h = q & 1;     // the tile's row 0..127, half
                 const int trow = rr;
                 const int srow = tsel * 128 + rr;                       // row in the slot
                 rawoff[i] = srow * pitch + h * 16;
                 dstoff[i] = trow * 128 + (((h * 4) ^ (trow & 7)) << 4);  // chunk (4h + j) goes to (4h + j) ^ (trow & 7)
             }
-            for (int st2 = 0; st2 < 2 * NST; st2++, kk++) {
-                if ((kk & 3) != (unsigned)grp) continue;
-                const int st = st2 >> 1;
+            for (int st = 0; st < NST; st++) {
                 const int u = st % KSUB;
-                const unsigned ks = slot_base + st / KSUB;
+                const unsigned ks = slot_base + st / KSUB, kk = 2 * ks + tsel, b = kk % UM_ABUF;
                 const int s = ks % UM_STAGES;
                 bool ok = um_bar_wait(um_s32(&b_raw_full[s]), (ks / UM_STAGES) & 1, abortp);
-                // A tile grp was last read by the MMAs of the slot two back: wait until that slot is done
+                // A tile b was last read by the MMAs of the slot two back: wait until that slot is done
                 if (ok && ks >= 2) ok = um_bar_wait(um_s32(&b_raw_free[(ks - 2) % UM_STAGES]), ((ks - 2) / UM_STAGES) & 1, abortp);
                 if (!ok) { if (lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; } break; }
                 const unsigned char *raw = smem + s * UM_STAGE_BYTES + u * 32;
-                unsigned char *dstb = a16 + grp * UM_A16;
-                uint4 w[4];
+                unsigned char *dstb = a16 + b * UM_A16;
+                uint4 w[2];
 #pragma unroll
-                for (int i = 0; i < 4; i++) w[i] = *reinterpret_cast<const uint4 *>(raw + rawoff[i]);
+                for (int i = 0; i < 2; i++) w[i] = *reinterpret_cast<const uint4 *>(raw + rawoff[i]);
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
+                for (int i = 0; i < 2; i++) {
                     // (4h + j) ^ x7 == ((4h) ^ x7) ^ j for j < 4: the four chunks of a half are the base slot xor j
                     unsigned char *d = dstb + (dstoff[i] & ~0x7F);
                     const int base = (dstoff[i] >> 4) & 7;
@@ -336,7 +334,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic stores -> tensor-core reads
                 __syncwarp();
-                if (lane == 0) um_bar_arrive(um_s32(&b_a_full[grp]));
+                if (lane == 0) um_bar_arrive(um_s32(&b_a_full[b]));
             }
             slot_base += NST / KSUB;
         }
