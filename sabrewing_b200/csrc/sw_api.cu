@@ -200,7 +200,7 @@ static void sw_resident(const SwMoeDesc *d, const SwMoeLayer *L, int *lo, int *c
 // SW_EXPERT_PATH=tma|mma|simt overrides.
 // 3 = tcgen05/TMEM grouped GEMM, chosen when groups average SW_UMMA_MIN_ROWS (12) rows or more.
 static int sw_expert_path(int D, int I, int rows, int groups) {
-    static int pref = -1, umma_min = 12;
+    static int pref = -1, umma_min = 16;            // mean rows per group from which the tcgen05 kernels win (measured)
     if (pref < 0) {
         const char *e = getenv("SW_EXPERT_PATH");
         pref = 2;
