@@ -301,7 +301,8 @@ def run_ours(args):
         ach = alg[dom] / (per[dom] * 1e-3) / 1e9
         # DRAM bytes of one launch from an ncu capture of this workload, as a ratio to that launch's algorithmic
         # bytes (the capture and its command are summarised under profiles/); scaled to this run's launch.
-        ncu_ratio = {("c2", 32, "q4_gateup"): 776.06 / 776.67, ("c2", 32, "q4_down"): 395.97 / 389.0}
+        ncu_ratio = {("c2", 32, "q4_gateup"): 776.06 / 776.67, ("c2", 32, "q4_down"): 395.97 / 389.0,
+                     ("c3", 4096, "q4_gateup"): 1929.8 / 1291.3, ("c3", 4096, "q4_down"): 1340.2 / 1364.0}
         ratio = ncu_ratio.get((args.workload, T, dom))
         flops = {"q4_gateup": 4.0 * P * I * D, "q4_down": 2.0 * P * I * D}
         block_bytes = G * (1.5 * I * D + 8 * I + 4 * D) + (3 * SI * D * 2 if SI else 0) + E * D * 2 + 2 * T * D * 4
