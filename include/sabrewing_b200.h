@@ -164,6 +164,11 @@ int  sw_moe_experts(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *laye
                     const float *x, float *routed, int T, void *stream);
 int  sw_moe_finish(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer,
                    const float *x, const float *routed, float *out, int T, void *stream);
+/* Optional: the shared expert of x[T,D] (c/laguna.c:596-602) ahead of time, e.g. on another stream while the
+ * routed rows are exchanged between GPUs.  The result stays in ctx and is consumed by the next sw_moe_finish
+ * with the same T, which then skips its own shared-expert pass; ordering the two streams is the caller's job. */
+int  sw_moe_shared(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer,
+                   const float *x, int T, void *stream);
 
 /* Routing without any allocation (no counterpart in the reference, which sizes its
  * scratch with cudaMalloc on demand, c/backend_cuda_laguna.cu:471-493): router

@@ -67,6 +67,8 @@ struct SwMoeCtx {
     void *spk = nullptr;         // packed bf16 hi/lo copy of x for the shared expert
     float *sums = nullptr;       // row sums of x and partial row sums of the SiLU*up rows
     int lastT = 0, lastK = 0, lastE = 0;
+    // a shared-expert result left by sw_moe_shared for the next sw_moe_finish of the same row count
+    int shared_T = -1, shared_slices = 1; float *shared_so = nullptr;
     void *block = nullptr;      // one device allocation holding all device scratch
     // optional per-stage CUDA-event timing (sw_moe_profile)
     int prof_on = 0, prof_calls = 0;
@@ -407,6 +409,16 @@ extern "C" int sw_moe_experts(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
     return 0;
 }
 
+extern "C" int sw_moe_shared(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, int T, void *stream) {
+    if (sw_check(c, d, L, T)) return -1;
+    c->shared_T = -1;
+    if (T == 0 || d->shared_mode == SW_SHARED_NONE) return 0;
+    float *so = nullptr; int so_slices = 1;
+    if (sw_shared_stage(c, L, x, T, (cudaStream_t)stream, &so, &so_slices)) return -1;
+    c->shared_T = T; c->shared_so = so; c->shared_slices = so_slices;
+    return 0;
+}
+
 extern "C" int sw_moe_finish(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, const float *routed, float *out, int T, void *stream) {
     if (sw_check(c, d, L, T)) return -1;
     if (T == 0) return 0;
@@ -414,7 +426,8 @@ extern "C" int sw_moe_finish(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *
     SwLaunchCfg cfg{c->num_sms, st};
     const int has_shared = d->shared_mode != SW_SHARED_NONE;
     float *so = nullptr; int so_slices = 1;
-    if (has_shared && sw_shared_stage(c, L, x, T, st, &so, &so_slices)) return -1;
+    if (has_shared && c->shared_T == T) { so = c->shared_so; so_slices = c->shared_slices; c->shared_T = -1; }   // left by sw_moe_shared
+    else if (has_shared && sw_shared_stage(c, L, x, T, st, &so, &so_slices)) return -1;
     if (sw_launch_finish(cfg, routed, so, so_slices, out, T, L->D, d->route_scale, has_shared)) return sw_fail("finish launch failed");
     return 0;
 }

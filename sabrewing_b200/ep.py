@@ -31,6 +31,7 @@ class ExpertParallelMoe:
         self.block, self.desc, self.group = block, desc, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self._bufs = {}
+        self._side = None
 
     def _buf(self, name, shape, like):
         b = self._bufs.get(name)
@@ -42,6 +43,16 @@ class ExpertParallelMoe:
     def forward(self, layer, x, out):
         """out[T,D] += MoE(x[T,D]) for this rank's rows; `layer` is this rank's shard."""
         T, D = x.shape
+        # The shared expert needs only this rank's rows: on a second stream it runs beside the exchange and the
+        # routed experts (CUDA block only; the CPU stand-in has no streams).
+        side = None
+        if self.world > 1 and x.is_cuda and hasattr(self.block, "shared"):
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=x.device)
+            side, cur = self._side, torch.cuda.current_stream(x.device)
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                self.block.shared(self.desc, layer, x)
         if self.world == 1:
             X = x
         else:
@@ -55,5 +66,22 @@ class ExpertParallelMoe:
         else:
             routed = self._buf("routed", (T, D), x)
             dist.reduce_scatter_tensor(routed, partial, op=dist.ReduceOp.SUM, group=self.group)
+        if side is not None:
+            torch.cuda.current_stream(x.device).wait_stream(side)
         self.block.finish(self.desc, layer, x, routed, out)
         return out
+
+    def graph(self, layer, x, out):
+        """One step captured into a CUDA graph (kernels of both streams and the two collectives); returns the
+        torch.cuda.CUDAGraph to replay().  x and out are read and written in place on every replay."""
+        s = torch.cuda.Stream(device=x.device)
+        s.wait_stream(torch.cuda.current_stream(x.device))
+        with torch.cuda.stream(s):
+            for _ in range(2):                       # set-up work (attributes, tensor maps, buffers) outside capture
+                self.forward(layer, x, out)
+        torch.cuda.current_stream(x.device).wait_stream(s)
+        torch.cuda.synchronize(x.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.forward(layer, x, out)
+        return g

@@ -180,6 +180,12 @@ class MoeBlock:
                                           x.shape[0], self._stream(stream)), "sw_moe_experts")
         return routed
 
+    def shared(self, desc, layer, x, stream=None):
+        """The shared expert of x ahead of time; the next finish() with as many rows uses it."""
+        d, l = desc.c(), layer.c()
+        self._chk(self.lib.sw_moe_shared(self.ctx, C.byref(d), C.byref(l), x.data_ptr(), x.shape[0], self._stream(stream)),
+                  "sw_moe_shared")
+
     def finish(self, desc, layer, x, routed, out, stream=None):
         d, l = desc.c(), layer.c()
         self._chk(self.lib.sw_moe_finish(self.ctx, C.byref(d), C.byref(l), x.data_ptr(), routed.data_ptr(),

@@ -328,3 +328,29 @@ def test_lag_rejects_odd_shapes():
     l = _lag()
     y = np.zeros(8, np.float32)
     assert l.lag_cuda_matmul_q4(y.ctypes.data, y.ctypes.data, None, None, 1, 6, 2) == -1   # caller falls back to CPU
+
+
+def test_shared_stage_ahead_of_finish(orc):
+    """sw_moe_shared on a second stream, then finish: same result as the one-call block."""
+    case = synth_case("c2", D=512, E=32, K=4, I=128, SI=128, T=24)
+    blk, layer, desc = make_block(case)
+    x = torch.from_numpy(case.x).cuda()
+    want = torch.from_numpy(case.hin).cuda(); blk.forward(desc, layer, x, want)
+    out = torch.from_numpy(case.hin).cuda()
+    routed = torch.empty_like(x)
+    side, cur = torch.cuda.Stream(), torch.cuda.current_stream()
+    side.wait_stream(cur)
+    with torch.cuda.stream(side):
+        blk.shared(desc, layer, x)
+    blk.route(desc, layer, x)
+    blk.experts(desc, layer, x, routed)
+    cur.wait_stream(side)
+    blk.finish(desc, layer, x, routed, out)
+    torch.cuda.synchronize()
+    assert rel_l2(out.cpu().numpy(), want.cpu().numpy()) < 1e-6
+    # a finish without a preceding shared() computes the shared expert itself
+    out2 = torch.from_numpy(case.hin).cuda()
+    blk.finish(desc, layer, x, routed, out2)
+    torch.cuda.synchronize()
+    assert torch.equal(out2, out)
+    blk.close()
