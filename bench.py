@@ -360,8 +360,8 @@ def run_ours(args):
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
         nbytes = T * cfg.D * 4
-        line["e2e"] = {"value": T * n_e2e / dt, "unit": UNIT, "h2d_bytes_per_step": 2 * nbytes, "d2h_bytes_per_step": nbytes,
-                       "steps": n_e2e, "api": "sw_moe_forward_host (host f32 rows in, host f32 rows out, one sync per call)"}
+        line["e2e"] = {"value": T * n_e2e / dt, "unit": UNIT, "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
+                       "steps": n_e2e, "api": "sw_moe_forward_host (pinned host f32 rows up, MoE(x) rows down and added to the host residual, one sync per call)"}
     else:
         # expert-parallel: every rank copies its rows in from pinned memory and its result back out each step
         n_e2e = max(3, min(args.steps, 200))

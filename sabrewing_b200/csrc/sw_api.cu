@@ -432,7 +432,14 @@ extern "C" int sw_moe_finish(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *
     return 0;
 }
 
+// accumulate: out += MoE(x) (the reference's residual add); else out = MoE(x)
+static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, float *out, int T, void *stream, bool accumulate);
+
 extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, float *out, int T, void *stream) {
+    return sw_forward_impl(c, d, L, x, out, T, stream, true);
+}
+
+static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, float *out, int T, void *stream, bool accumulate) {
     if (sw_check(c, d, L, T)) return -1;
     if (T == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
@@ -488,10 +495,17 @@ extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
         sw_prof_mark(c, SW_ST_SH_GATEUP, st); sw_prof_mark(c, SW_ST_SH_DOWN, st);
     }
     if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, so, so_slices, out, T, K, L->D,
-                          d->route_scale, 1 | (has_shared ? 2 : 0) | 4, lo, cnt)) return sw_fail("combine launch failed");
+                          d->route_scale, 1 | (has_shared ? 2 : 0) | (accumulate ? 4 : 0), lo, cnt)) return sw_fail("combine launch failed");
     sw_prof_mark(c, SW_ST_COMBINE, st);
     if (c->prof_on && c->prof_calls < SW_PROF_MAX_CALLS) c->prof_calls++;
     return 0;
+}
+
+// Is p page-locked host memory the device can copy from directly?
+static bool sw_host_pinned(const void *p) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) { cudaGetLastError(); return false; }
+    return at.type == cudaMemoryTypeHost;
 }
 
 extern "C" int sw_moe_forward_host(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x_host, float *out_host, int T) {
@@ -499,13 +513,17 @@ extern "C" int sw_moe_forward_host(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeL
     if (T == 0) return 0;
     if (!x_host || !out_host) return sw_fail("forward_host: null buffer");
     const size_t n = (size_t)T * L->D * sizeof(float);
-    memcpy(c->hx, x_host, n); memcpy(c->hout, out_host, n);
-    SW_CUDA(cudaMemcpyAsync(c->dx, c->hx, n, cudaMemcpyHostToDevice, c->stream));
-    SW_CUDA(cudaMemcpyAsync(c->dout, c->hout, n, cudaMemcpyHostToDevice, c->stream));
-    if (sw_moe_forward(c, d, L, c->dx, c->dout, T, c->stream)) return -1;
+    // x goes up (straight from the caller's buffer when that is page-locked), MoE(x) comes back and is added to the
+    // caller's residual rows on the host: the residual itself never crosses the bus.
+    const float *src = x_host;
+    if (!sw_host_pinned(x_host)) { memcpy(c->hx, x_host, n); src = c->hx; }
+    SW_CUDA(cudaMemcpyAsync(c->dx, src, n, cudaMemcpyHostToDevice, c->stream));
+    if (sw_forward_impl(c, d, L, c->dx, c->dout, T, c->stream, false)) return -1;
     SW_CUDA(cudaMemcpyAsync(c->hout, c->dout, n, cudaMemcpyDeviceToHost, c->stream));
     SW_CUDA(cudaStreamSynchronize(c->stream));
-    memcpy(out_host, c->hout, n);
+    const float *add = c->hout;
+    const size_t cnt = (size_t)T * L->D;
+    for (size_t i = 0; i < cnt; i++) out_host[i] += add[i];
     return 0;
 }
 
