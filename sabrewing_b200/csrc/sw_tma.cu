@@ -153,6 +153,9 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
     extern __shared__ unsigned char sw_dyn[];
     __shared__ unsigned long long s_full[P], s_empty[P];
     __shared__ int s_abort;
+    // 8 * (row sum of the token's activations) for the up to 8 token rows of a pass, written by the producer warp
+    // (ring of 8 passes: the producer is at most P <= 6 passes ahead of the consumers' epilogue)
+    __shared__ float s_corr[8][8];
     unsigned char *smem = (unsigned char *)(((uintptr_t)sw_dyn + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KD = a.KD, OUT = a.OUT;
@@ -179,59 +182,108 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
 
     if (warp == 4) {
         // ------------------------------ producer ------------------------------
-        if (lane == 0) {
-            unsigned it = 0;                            // global stage counter of this CTA
-            for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
-                const int gi = item / rb_per_group, rb = item - gi * rb_per_group;
-                const int e = a.gexp[gi] - a.expert_lo;
-                if (e < 0 || e >= a.expert_cnt) continue;
-                const int n = a.gcnt[gi], beg = a.gbeg[gi];
-                const int row0 = e * nrows_w + rb * OPI;
-                for (int c0 = 0; c0 < n && !*abortp;) {
-                    const bool m8 = n - c0 > 4;
-                    const int ntok = m8 ? min(8, n - c0) : n - c0;
-                    for (int st = 0; st < NST; st++, it++) {
-                        const int slot = it % P;
-                        if (it >= (unsigned)P && !sw_mbar_wait(sw_smem_u32(&s_empty[slot]), ((it / P) - 1) & 1, abortp)) {
-                            atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break;
-                        }
-                        unsigned char *sp = smem + (size_t)slot * STAGE_BYTES;
-                        const unsigned bar = sw_smem_u32(&s_full[slot]);
-                        const int colb = st * 128;                                  // byte column of the stage
-                        const int bcols = min(SW_TMA_STAGE_COLS, KD - st * SW_TMA_STAGE_COLS);
-                        const unsigned bbytes = (unsigned)bcols * 4;
-                        sw_mbar_expect_tx(bar, (unsigned)ABYTES + (unsigned)ntok * bbytes);
-                        if (GATEUP) {
-                            sw_tma_load_2d(sw_smem_u32(sp), &tmW, colb, row0, bar);
-                            sw_tma_load_2d(sw_smem_u32(sp + ABYTES / 2), &tmW, colb, row0 + OUT, bar);
-                        } else {
-                            sw_tma_load_2d(sw_smem_u32(sp), &tmW, colb, row0, bar);
-                            if (MT == 4) sw_tma_load_2d(sw_smem_u32(sp + ABYTES / 2), &tmW, colb, row0 + AROWS / 2, bar);
-                        }
-                        for (int r = 0; r < ntok; r++) {
-                            const int rowid = GATEUP ? a.grow[beg + c0 + r] : beg + c0 + r;
-                            sw_bulk_load(sw_smem_u32(sp + ABYTES + r * SW_TMA_BROW),
-                                         a.XP + (size_t)rowid * xrow_bytes + (size_t)st * (SW_TMA_STAGE_COLS * 4), bbytes, bar);
+        // Lane 0 streams the stages.  All lanes together also fetch the row-sum partials of the pass's token rows
+        // (the epilogue needs 8 * sum(x) per token row to undo the +8 of the unsigned nibbles), add them in a fixed
+        // order and leave the results in s_corr before the pass's LAST stage is announced: the consumers, who wait
+        // for that stage before their epilogue, then find them without touching global memory.
+        unsigned it = 0, pass = 0;                      // global stage and pass counters of this CTA
+        for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
+            const int gi = item / rb_per_group, rb = item - gi * rb_per_group;
+            const int e = a.gexp[gi] - a.expert_lo;
+            if (e < 0 || e >= a.expert_cnt) continue;
+            const int n = a.gcnt[gi], beg = a.gbeg[gi];
+            const int row0 = e * nrows_w + rb * OPI;
+            for (int c0 = 0; c0 < n && !*abortp; pass++) {
+                const bool m8 = n - c0 > 4;
+                const int ntok = m8 ? min(8, n - c0) : n - c0;
+                // partial sums of row r: lane l takes parts l, l+32, ... (ascending); eight rows' loads are in flight at once
+                float v[8];
+#pragma unroll
+                for (int r = 0; r < 8; r++) v[r] = 0.f;
+                for (int k = lane; k < a.xsum_parts; k += 32) {
+                    float ld[8];
+#pragma unroll
+                    for (int r = 0; r < 8; r++) {
+                        ld[r] = 0.f;
+                        if (r < ntok) {
+                            const int rid = GATEUP ? a.grow[beg + c0 + r] : beg + c0 + r;
+                            ld[r] = a.xsum[(size_t)rid * a.xsum_parts + k];
                         }
                     }
-                    c0 += ntok;
+#pragma unroll
+                    for (int r = 0; r < 8; r++) v[r] += ld[r];
                 }
+                bool dead = false;
+                for (int st = 0; st < NST; st++, it++) {
+                    if (st == NST - 1) {
+                        // join: reduce over the lanes in a fixed tree, publish, then announce the last stage
+#pragma unroll
+                        for (int r = 0; r < 8; r++) {
+                            float sx = v[r];
+#pragma unroll
+                            for (int off = 16; off; off >>= 1) sx += __shfl_xor_sync(SW_FULL_MASK, sx, off);
+                            if (lane == 0) s_corr[pass & 7][r] = 8.f * sx;
+                        }
+                        __syncwarp();
+                    }
+                    if (lane == 0) {
+                        const int slot = it % P;
+                        if (it >= (unsigned)P && !sw_mbar_wait(sw_smem_u32(&s_empty[slot]), ((it / P) - 1) & 1, abortp)) {
+                            atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; dead = true;
+                        } else {
+                            unsigned char *sp = smem + (size_t)slot * STAGE_BYTES;
+                            const unsigned bar = sw_smem_u32(&s_full[slot]);
+                            const int colb = st * 128;                                  // byte column of the stage
+                            const int bcols = min(SW_TMA_STAGE_COLS, KD - st * SW_TMA_STAGE_COLS);
+                            const unsigned bbytes = (unsigned)bcols * 4;
+                            sw_mbar_expect_tx(bar, (unsigned)ABYTES + (unsigned)ntok * bbytes);
+                            if (GATEUP) {
+                                sw_tma_load_2d(sw_smem_u32(sp), &tmW, colb, row0, bar);
+                                sw_tma_load_2d(sw_smem_u32(sp + ABYTES / 2), &tmW, colb, row0 + OUT, bar);
+                            } else {
+                                sw_tma_load_2d(sw_smem_u32(sp), &tmW, colb, row0, bar);
+                                if (MT == 4) sw_tma_load_2d(sw_smem_u32(sp + ABYTES / 2), &tmW, colb, row0 + AROWS / 2, bar);
+                            }
+                            for (int r = 0; r < ntok; r++) {
+                                const int rowid = GATEUP ? a.grow[beg + c0 + r] : beg + c0 + r;
+                                sw_bulk_load(sw_smem_u32(sp + ABYTES + r * SW_TMA_BROW),
+                                             a.XP + (size_t)rowid * xrow_bytes + (size_t)st * (SW_TMA_STAGE_COLS * 4), bbytes, bar);
+                            }
+                        }
+                    }
+                    dead = __shfl_sync(SW_FULL_MASK, dead, 0);
+                    if (dead) break;
+                }
+                if (dead) break;
+                c0 += ntok;
             }
         }
     } else {
         // ------------------------------ consumers ------------------------------
         const int g = lane >> 2, t = lane & 3;
         const int rho = (g >> 1) | ((g & 1) << 2);
-        unsigned it = 0;
+        unsigned it = 0, pass = 0;
         for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
             const int gi = item / rb_per_group, rb = item - gi * rb_per_group;
             const int e = a.gexp[gi] - a.expert_lo;
             if (e < 0 || e >= a.expert_cnt) continue;
             const int n = a.gcnt[gi], beg = a.gbeg[gi];
             const float *ws = a.Ws + (size_t)e * nrows_w;
+            // the scales of this thread's rows, requested before the K loop so that the epilogue does not wait for them
+            float sc0[MT], sc1[MT];
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                if (GATEUP) {
+                    const int o = rb * OPI + warp * (8 * MT) + mt * 8 + rho;
+                    sc0[mt] = o < OUT ? ws[o] : 0.f; sc1[mt] = o < OUT ? ws[OUT + o] : 0.f;
+                } else {
+                    const int oa = rb * OPI + warp * (16 * MT) + mt * 16 + rho, ob = oa + 8;
+                    sc0[mt] = oa < OUT ? ws[oa] : 0.f; sc1[mt] = ob < OUT ? ws[ob] : 0.f;
+                }
+            }
             // tile rows of this thread: role "row g" and role "row g+8" of m-tile mt
             // gate/up: A tile = [32*MT gate rows][32*MT up rows]; down: [64*MT rows]
-            for (int c0 = 0; c0 < n && !*abortp;) {
+            for (int c0 = 0; c0 < n && !*abortp; pass++) {
                 const bool m8 = n - c0 > 4;
                 const int ntok = m8 ? min(8, n - c0) : n - c0;
                 const int brow = m8 ? min(g, ntok - 1) : min(g & 3, ntok - 1);
@@ -269,18 +321,7 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
                 for (int j = 0; j < 2; j++) {
                     tok[j] = c0 + 2 * t + j;
                     const bool ok = own && tok[j] < c0 + ntok;
-                    // row sum of the token's activations: the 8 lanes that share t split the partial
-                    // sums between them (k = g, g+8, ...) and add up in a fixed tree
-                    float sx = 0.f;
-                    if (ok) {
-                        const int rid = GATEUP ? a.grow[beg + tok[j]] : beg + tok[j];
-                        const float *ps = a.xsum + (size_t)rid * a.xsum_parts;
-                        for (int k = g; k < a.xsum_parts; k += 8) sx += ps[k];
-                    }
-                    sx += __shfl_xor_sync(SW_FULL_MASK, sx, 4);
-                    sx += __shfl_xor_sync(SW_FULL_MASK, sx, 8);
-                    sx += __shfl_xor_sync(SW_FULL_MASK, sx, 16);
-                    corr[j] = 8.f * sx;
+                    corr[j] = ok ? s_corr[pass & 7][2 * t + j] : 0.f;     // left there by the producer warp
                     if (!ok) tok[j] = -1;
                 }
                 if (GATEUP) {
@@ -290,7 +331,7 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
                     for (int mt = 0; mt < MT; mt++) {
                         const int o = rb * OPI + warp * (8 * MT) + mt * 8 + rho;
                         const bool ov = o < OUT;
-                        const float sg = ov ? ws[o] : 0.f, su = ov ? ws[OUT + o] : 0.f;
+                        const float sg = sc0[mt], su = sc1[mt];
                         const size_t pos = sw_packed_pos_t(ov ? o : 0);
                         const float pre = (o & 1) ? 0.0625f : 1.f;
 #pragma unroll
@@ -320,7 +361,7 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
 #pragma unroll
                     for (int mt = 0; mt < MT; mt++) {
                         const int oa = rb * OPI + warp * (16 * MT) + mt * 16 + rho, ob = oa + 8;
-                        const float sa = oa < OUT ? ws[oa] : 0.f, sb = ob < OUT ? ws[ob] : 0.f;
+                        const float sa = sc0[mt], sb = sc1[mt];
 #pragma unroll
                         for (int j = 0; j < 2; j++) {
                             if (tok[j] < 0) continue;
