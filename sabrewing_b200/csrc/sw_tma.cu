@@ -263,11 +263,17 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
         const int g = lane >> 2, t = lane & 3;
         const int rho = (g >> 1) | ((g & 1) << 2);
         unsigned it = 0, pass = 0;
+        // group of the next item, fetched one item ahead (its L2 round trip then passes under the current item)
+        int nx_e = 0, nx_n = 0, nx_beg = 0;
+        if ((int)blockIdx.x < items) { const int g0 = blockIdx.x / rb_per_group; nx_e = a.gexp[g0]; nx_n = a.gcnt[g0]; nx_beg = a.gbeg[g0]; }
         for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
             const int gi = item / rb_per_group, rb = item - gi * rb_per_group;
-            const int e = a.gexp[gi] - a.expert_lo;
+            const int e = nx_e - a.expert_lo, n = nx_n, beg = nx_beg;
+            if (item + (int)gridDim.x < items) {
+                const int g1 = (item + gridDim.x) / rb_per_group;
+                nx_e = a.gexp[g1]; nx_n = a.gcnt[g1]; nx_beg = a.gbeg[g1];
+            }
             if (e < 0 || e >= a.expert_cnt) continue;
-            const int n = a.gcnt[gi], beg = a.gbeg[gi];
             const float *ws = a.Ws + (size_t)e * nrows_w;
             // the scales of this thread's rows, requested before the K loop so that the epilogue does not wait for them
             float sc0[MT], sc1[MT];
