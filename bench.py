@@ -38,7 +38,6 @@ def parse():
     ap.add_argument("--cpu-reps", type=int, default=12)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch the kernels of every step one by one instead of replaying CUDA graphs")
-    ap.add_argument("--ep-graph", action="store_true", help="N > 1: capture the whole expert-parallel step (collectives included) into one CUDA graph per pair")
     return ap.parse_args()
 
 
@@ -223,21 +222,6 @@ def run_ours(args):
                 if (li - bi) % np.gcd(len(layers), NB) == 0:     # only the pairs (i % L, i % NB) that occur
                     graphs[(li, bi)] = block.graph(desc, layers[li], xs[bi], outs[bi])
         torch.cuda.synchronize()
-    # expert parallel: the whole step (both streams, all-gather, reduce-scatter) as one torch CUDA graph per pair
-    ep_graphs, ep_kernels = {}, 0
-    if ep is not None and args.ep_graph and not args.no_graph:
-        try:
-            for li in range(len(layers)):
-                for bi in range(NB):
-                    if (li - bi) % np.gcd(len(layers), NB) == 0:
-                        c0 = block.lib.sw_launch_count()
-                        ep_graphs[(li, bi)] = ep.graph(layers[li], xs[bi], outs[bi])
-                        ep_kernels = (block.lib.sw_launch_count() - c0) // 3     # two eager runs and the captured one
-            torch.cuda.synchronize()
-        except Exception as e:                                  # capture of the collectives refused: launch eagerly
-            print("graph capture of the expert-parallel step failed (%s); running eagerly" % e, file=sys.stderr, flush=True)
-            ep_graphs = {}
-
     def step(i, use_graph=True):
         li, bi = i % len(layers), i % NB
         layer, x, out = layers[li], xs[bi], outs[bi]
@@ -248,11 +232,7 @@ def run_ours(args):
             else:
                 block.forward(desc, layer, x, out)
         else:
-            g = ep_graphs.get((li, bi)) if use_graph else None
-            if g is not None:
-                g.replay()
-            else:
-                ep.forward(layer, x, out)
+            ep.forward(layer, x, out)
 
     def barrier():
         if world > 1:
@@ -272,8 +252,6 @@ def run_ours(args):
     barrier()
     t_b = time.perf_counter()
     launches = block.lib.sw_launch_count() - l0
-    if ep_graphs:
-        launches += ep_kernels * args.steps              # kernels inside the replayed graphs (counted at capture)
     ms = e0.elapsed_time(e1)
     if world > 1:
         t = torch.tensor([ms], device=dev)
@@ -289,7 +267,7 @@ def run_ours(args):
                        "l2": "inputs larger than L2: steps cycle over %d layers (%.2f GB of expert blobs each per GPU) and %d token batches"
                              % (len(layers), layers[0].expert_bytes() / 1e9, NB),
                        "parallelism": "ep%d" % world if world > 1 else "single",
-                       "launch": "cuda graph replay per step" if (graphs or ep_graphs) else "one launch per kernel"},
+                       "launch": "cuda graph replay per step" if graphs else "one launch per kernel"},
             "clocks": clocks, "gpu_launches": int(launches)}
 
     # ---- roofline of the dominant kernel: per-stage CUDA events over the same steps (1 GPU) ----

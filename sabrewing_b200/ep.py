@@ -70,18 +70,3 @@ class ExpertParallelMoe:
             torch.cuda.current_stream(x.device).wait_stream(side)
         self.block.finish(self.desc, layer, x, routed, out)
         return out
-
-    def graph(self, layer, x, out):
-        """One step captured into a CUDA graph (kernels of both streams and the two collectives); returns the
-        torch.cuda.CUDAGraph to replay().  x and out are read and written in place on every replay."""
-        s = torch.cuda.Stream(device=x.device)
-        s.wait_stream(torch.cuda.current_stream(x.device))
-        with torch.cuda.stream(s):
-            for _ in range(2):                       # set-up work (attributes, tensor maps, buffers) outside capture
-                self.forward(layer, x, out)
-        torch.cuda.current_stream(x.device).wait_stream(s)
-        torch.cuda.synchronize(x.device)
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            self.forward(layer, x, out)
-        return g
