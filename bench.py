@@ -327,7 +327,8 @@ def run_ours(args):
     # ---- end to end through host buffers: pinned x -> H2D, block, D2H of the result, every step ----
     if world == 1:
         hx = [x.numpy() for x in xs_host]
-        ho = [np.zeros_like(h) for h in hx]
+        ho_t = [torch.zeros_like(x).pin_memory() for x in xs_host]      # residual rows, page-locked like the inputs
+        ho = [t.numpy() for t in ho_t]
         n_e2e = max(3, min(args.steps, 200))
         for i in range(3):
             block.forward_host(desc, layers[i % len(layers)], hx[i % NB], ho[i % NB])
@@ -338,8 +339,8 @@ def run_ours(args):
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
         nbytes = T * cfg.D * 4
-        line["e2e"] = {"value": T * n_e2e / dt, "unit": UNIT, "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
-                       "steps": n_e2e, "api": "sw_moe_forward_host (pinned host f32 rows up, MoE(x) rows down and added to the host residual, one sync per call)"}
+        line["e2e"] = {"value": T * n_e2e / dt, "unit": UNIT, "h2d_bytes_per_step": 2 * nbytes, "d2h_bytes_per_step": nbytes,
+                       "steps": n_e2e, "api": "sw_moe_forward_host (page-locked host rows: x up, residual rows up beside the kernels, residual + MoE(x) down; one sync per call)"}
     else:
         # expert-parallel: every rank copies its rows in from pinned memory and its result back out each step
         n_e2e = max(3, min(args.steps, 200))

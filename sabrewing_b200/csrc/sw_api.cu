@@ -56,6 +56,8 @@ struct SwMoeCtx {
     int dev = 0, num_sms = 0;
     int maxT = 0, maxE = 0, maxK = 0, maxD = 0, maxI = 0, maxSI = 0;
     cudaStream_t stream = nullptr, last_stream = nullptr;
+    cudaStream_t cpy = nullptr;              // forward_host: uploads the residual rows beside the kernels
+    cudaEvent_t ev_res = nullptr; bool wait_res = false;   // set while a residual upload must precede the combine
     cudaStream_t aux = nullptr;                 // the shared expert runs here, beside routing and the routed experts
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_pack = nullptr;
     SwRouting r{};
@@ -104,6 +106,8 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
     c->num_sms = prop.multiProcessorCount;
     if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaStreamCreateWithFlags(&c->aux, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&c->cpy, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_res, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&c->ev_pack, cudaEventDisableTiming) != cudaSuccess) { delete c; return sw_cuda_fail(cudaGetLastError(), "cudaStreamCreate"); }
@@ -156,6 +160,8 @@ extern "C" void sw_moe_ctx_destroy(SwMoeCtx *c) {
     cudaSetDevice(c->dev);
     if (c->stream) { cudaStreamSynchronize(c->stream); cudaStreamDestroy(c->stream); }
     if (c->aux) { cudaStreamSynchronize(c->aux); cudaStreamDestroy(c->aux); }
+    if (c->cpy) { cudaStreamSynchronize(c->cpy); cudaStreamDestroy(c->cpy); }
+    if (c->ev_res) cudaEventDestroy(c->ev_res);
     if (c->ev_fork) cudaEventDestroy(c->ev_fork);
     if (c->ev_join) cudaEventDestroy(c->ev_join);
     if (c->ev_pack) cudaEventDestroy(c->ev_pack);
@@ -494,6 +500,7 @@ static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
     } else {
         sw_prof_mark(c, SW_ST_SH_GATEUP, st); sw_prof_mark(c, SW_ST_SH_DOWN, st);
     }
+    if (c->wait_res) SW_CUDA(cudaStreamWaitEvent(st, c->ev_res, 0));         // forward_host: the residual rows are on their way
     if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, so, so_slices, out, T, K, L->D,
                           d->route_scale, 1 | (has_shared ? 2 : 0) | (accumulate ? 4 : 0), lo, cnt)) return sw_fail("combine launch failed");
     sw_prof_mark(c, SW_ST_COMBINE, st);
@@ -513,11 +520,25 @@ extern "C" int sw_moe_forward_host(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeL
     if (T == 0) return 0;
     if (!x_host || !out_host) return sw_fail("forward_host: null buffer");
     const size_t n = (size_t)T * L->D * sizeof(float);
-    // x goes up (straight from the caller's buffer when that is page-locked), MoE(x) comes back and is added to the
-    // caller's residual rows on the host: the residual itself never crosses the bus.
+    const bool xpin = sw_host_pinned(x_host), opin = sw_host_pinned(out_host);
+    // x goes up straight from the caller's buffer when that is page-locked.
     const float *src = x_host;
-    if (!sw_host_pinned(x_host)) { memcpy(c->hx, x_host, n); src = c->hx; }
+    if (!xpin) { memcpy(c->hx, x_host, n); src = c->hx; }
     SW_CUDA(cudaMemcpyAsync(c->dx, src, n, cudaMemcpyHostToDevice, c->stream));
+    if (opin && n >= 128 * 1024) {                  // (a few rows are cheaper to add on the host than to order a third stream)
+        // Page-locked residual rows: they go up on a copy stream while the kernels run, the block adds into them
+        // on the device, and the result comes down into the caller's buffer: no host pass over the rows at all.
+        SW_CUDA(cudaMemcpyAsync(c->dout, out_host, n, cudaMemcpyHostToDevice, c->cpy));
+        SW_CUDA(cudaEventRecord(c->ev_res, c->cpy));
+        c->wait_res = true;
+        const int rc = sw_forward_impl(c, d, L, c->dx, c->dout, T, c->stream, true);
+        c->wait_res = false;
+        if (rc) { cudaStreamSynchronize(c->cpy); return -1; }
+        SW_CUDA(cudaMemcpyAsync(out_host, c->dout, n, cudaMemcpyDeviceToHost, c->stream));
+        SW_CUDA(cudaStreamSynchronize(c->stream));
+        return 0;
+    }
+    // Pageable residual rows: MoE(x) comes back and is added on the host; the residual never crosses the bus.
     if (sw_forward_impl(c, d, L, c->dx, c->dout, T, c->stream, false)) return -1;
     SW_CUDA(cudaMemcpyAsync(c->hout, c->dout, n, cudaMemcpyDeviceToHost, c->stream));
     SW_CUDA(cudaStreamSynchronize(c->stream));

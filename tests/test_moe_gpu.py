@@ -354,3 +354,17 @@ def test_shared_stage_ahead_of_finish(orc):
     torch.cuda.synchronize()
     assert torch.equal(out2, out)
     blk.close()
+
+
+def test_forward_host_pinned_and_pageable_agree(orc):
+    """forward_host takes page-locked buffers directly (residual uploaded beside the kernels) and stages pageable ones."""
+    case = synth_case("c2", D=512, E=32, K=4, I=128, SI=128, T=20)
+    blk, layer, desc = make_block(case)
+    want = orc.moe_group(case.host, case.x, case.hin, exact=1)["out"]
+    out_pageable = case.hin.copy()
+    blk.forward_host(desc, layer, case.x, out_pageable)
+    xp = torch.from_numpy(case.x).pin_memory(); op = torch.from_numpy(case.hin.copy()).pin_memory()
+    blk.forward_host(desc, layer, xp.numpy(), op.numpy())
+    assert rel_l2(out_pageable, want) < 1e-3 and rel_l2(op.numpy(), want) < 1e-3
+    assert np.array_equal(op.numpy(), out_pageable)
+    blk.close()
