@@ -358,7 +358,7 @@ def test_shared_stage_ahead_of_finish(orc):
 
 def test_forward_host_pinned_and_pageable_agree(orc):
     """forward_host takes page-locked buffers directly (residual uploaded beside the kernels) and stages pageable ones."""
-    case = synth_case("c2", D=512, E=32, K=4, I=128, SI=128, T=20)
+    case = synth_case("c2", D=1024, E=32, K=4, I=128, SI=128, T=64)      # 256 KB of rows: above the copy-stream threshold
     blk, layer, desc = make_block(case)
     want = orc.moe_group(case.host, case.x, case.hin, exact=1)["out"]
     out_pageable = case.hin.copy()
