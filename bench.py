@@ -324,6 +324,25 @@ def run_ours(args):
         line["block_hbm_frac"] = block_bytes / (line["ms_per_step"] * 1e-3) / 1e9 / peak
         line["stage_ms"] = {k: round(v, 5) for k, v in per.items()}
 
+    # ---- expert parallel: rows and int4 bytes per GPU of one step (imbalance = max / mean rows per GPU) ----
+    if world > 1:
+        try:
+            ep.forward(layers[0], xs[0], outs[0])
+            torch.cuda.synchronize()
+            r = block.routing()
+            mine = (r["gexp"] >= lo) & (r["gexp"] < lo + cnt)
+            rows_here, experts_here = int(r["gcnt"][mine].sum()), int(mine.sum())
+            tt = torch.tensor([rows_here, experts_here], device=dev, dtype=torch.float64)
+            allr = [torch.zeros_like(tt) for _ in range(world)]
+            dist.all_gather(allr, tt)
+            rows = [float(a[0].item()) for a in allr]; exps = [float(a[1].item()) for a in allr]
+            per_expert = 1.5 * cfg.I * cfg.D + 8 * cfg.I + 4 * cfg.D
+            line["expert_parallel"] = {"rows_per_gpu": rows, "distinct_experts_per_gpu": exps,
+                                       "imbalance": max(rows) / (sum(rows) / world) if sum(rows) else None,
+                                       "int4_gbs_per_gpu": [e * per_expert / (line["ms_per_step"] * 1e-3) / 1e9 for e in exps]}
+        except Exception as e:                      # a reporting extra: never lose the bench line over it
+            line["expert_parallel"] = {"error": str(e)[:120]}
+
     # ---- end to end through host buffers: pinned x -> H2D, block, D2H of the result, every step ----
     if world == 1:
         hx = [x.numpy() for x in xs_host]
