@@ -222,6 +222,14 @@ def run_ours(args):
                 if (li - bi) % np.gcd(len(layers), NB) == 0:     # only the pairs (i % L, i % NB) that occur
                     graphs[(li, bi)] = block.graph(desc, layers[li], xs[bi], outs[bi])
         torch.cuda.synchronize()
+    # expert parallel: this rank's kernels of a step as three graphs per pair (the collectives stay NCCL calls)
+    if ep is not None and not args.no_graph:
+        for li in range(len(layers)):
+            for bi in range(NB):
+                if (li - bi) % np.gcd(len(layers), NB) == 0:
+                    ep.prepare(layers[li], xs[bi], outs[bi])
+        torch.cuda.synchronize()
+
     def step(i, use_graph=True):
         li, bi = i % len(layers), i % NB
         layer, x, out = layers[li], xs[bi], outs[bi]
@@ -267,7 +275,7 @@ def run_ours(args):
                        "l2": "inputs larger than L2: steps cycle over %d layers (%.2f GB of expert blobs each per GPU) and %d token batches"
                              % (len(layers), layers[0].expert_bytes() / 1e9, NB),
                        "parallelism": "ep%d" % world if world > 1 else "single",
-                       "launch": "cuda graph replay per step" if graphs else "one launch per kernel"},
+                       "launch": "cuda graph replay per step" if graphs else ("three graph replays and two NCCL calls per step" if (ep is not None and not args.no_graph) else "one launch per kernel")},
             "clocks": clocks, "gpu_launches": int(launches)}
 
     # ---- roofline of the dominant kernel: per-stage CUDA events over the same steps (1 GPU) ----

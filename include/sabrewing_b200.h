@@ -169,6 +169,13 @@ int  sw_moe_finish(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer
  * with the same T, which then skips its own shared-expert pass; ordering the two streams is the caller's job. */
 int  sw_moe_shared(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer,
                    const float *x, int T, void *stream);
+/* Capture of a sequence of stage calls into a graph: begin, then the calls with sw_moe_capture_stream(ctx) as
+ * their stream (recorded, not run; each must have run once before), then end.  The graph is launched and
+ * destroyed like one from sw_moe_graph_create.  For drivers that interleave the stages with their own work
+ * (collectives) and want one launch per segment. */
+void *sw_moe_capture_stream(SwMoeCtx *ctx);
+int  sw_moe_capture_begin(SwMoeCtx *ctx);
+int  sw_moe_capture_end(SwMoeCtx *ctx, SwMoeGraph **graph);
 
 /* Routing without any allocation (no counterpart in the reference, which sizes its
  * scratch with cudaMalloc on demand, c/backend_cuda_laguna.cu:471-493): router

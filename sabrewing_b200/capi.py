@@ -57,6 +57,9 @@ SIGNATURES = {
     "sw_moe_experts": (_i, [_vp, _pd, _pl, _vp, _vp, _i, _vp]),
     "sw_moe_finish": (_i, [_vp, _pd, _pl, _vp, _vp, _vp, _i, _vp]),
     "sw_moe_shared": (_i, [_vp, _pd, _pl, _vp, _i, _vp]),
+    "sw_moe_capture_stream": (_vp, [_vp]),
+    "sw_moe_capture_begin": (_i, [_vp]),
+    "sw_moe_capture_end": (_i, [_vp, C.POINTER(_vp)]),
     "sw_moe_route_static": (_i, [_pd, _pl, _vp, _i, _vp, _vp, _vp]),
     "sw_moe_get_routing": (_i, [_vp, _vp, _vp, _vp, C.POINTER(_i), _vp, _vp, _vp, _vp, _vp]),
     "sw_moe_status": (_i, [_vp]),

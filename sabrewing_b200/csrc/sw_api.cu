@@ -69,6 +69,7 @@ struct SwMoeCtx {
     void *spk = nullptr;         // packed bf16 hi/lo copy of x for the shared expert
     float *sums = nullptr;       // row sums of x and partial row sums of the SiLU*up rows
     int lastT = 0, lastK = 0, lastE = 0;
+    int cap_on = 0, cap_prof = 0; long long cap_l0 = 0;   // open stage capture (sw_moe_capture_begin)
     // a shared-expert result left by sw_moe_shared for the next sw_moe_finish of the same row count
     int shared_T = -1, shared_slices = 1; float *shared_so = nullptr;
     void *block = nullptr;      // one device allocation holding all device scratch
@@ -577,6 +578,36 @@ extern "C" int sw_moe_graph_create(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeL
     if (cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) { cudaGetLastError(); cudaGraphDestroy(graph); return sw_fail("cudaGraphInstantiate failed"); }
     SwMoeGraph *g = new SwMoeGraph{graph, exec, c, T, d->topk, d->n_experts, kernels};
     *gout = g;
+    return 0;
+}
+
+// Capture of any sequence of stage calls (route / experts / shared / finish): between capture_begin and
+// capture_end the caller passes sw_moe_capture_stream(ctx) as the stream of those calls; they are recorded, not
+// run.  Every call in the sequence must have run once before (set-up work cannot be captured).
+extern "C" void *sw_moe_capture_stream(SwMoeCtx *c) { return c ? (void *)c->stream : nullptr; }
+
+extern "C" int sw_moe_capture_begin(SwMoeCtx *c) {
+    if (!c) return sw_fail("null ctx");
+    if (c->cap_on) return sw_fail("capture_begin: a capture is already open");
+    SW_CUDA(cudaStreamSynchronize(c->stream));
+    if (cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) return sw_cuda_fail(cudaGetLastError(), "cudaStreamBeginCapture");
+    c->cap_on = 1; c->cap_prof = c->prof_on; c->prof_on = 0; c->cap_l0 = g_launches;
+    return 0;
+}
+
+extern "C" int sw_moe_capture_end(SwMoeCtx *c, SwMoeGraph **gout) {
+    if (!c || !gout) return sw_fail("capture_end: null argument");
+    *gout = nullptr;
+    if (!c->cap_on) return sw_fail("capture_end: no capture open");
+    const int kernels = (int)(g_launches - c->cap_l0);
+    g_launches = c->cap_l0;                            // captured, not launched
+    c->cap_on = 0; c->prof_on = c->cap_prof;
+    cudaGraph_t graph = nullptr;
+    const cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+    if (e != cudaSuccess || !graph) { cudaGetLastError(); if (graph) cudaGraphDestroy(graph); return sw_fail("graph capture failed: %s", cudaGetErrorString(e)); }
+    cudaGraphExec_t exec = nullptr;
+    if (cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) { cudaGetLastError(); cudaGraphDestroy(graph); return sw_fail("cudaGraphInstantiate failed"); }
+    *gout = new SwMoeGraph{graph, exec, c, c->lastT, c->lastK, c->lastE, kernels};
     return 0;
 }
 

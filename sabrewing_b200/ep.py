@@ -32,6 +32,7 @@ class ExpertParallelMoe:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self._bufs = {}
         self._side = None
+        self._graphs = {}
 
     def _buf(self, name, shape, like):
         b = self._bufs.get(name)
@@ -40,9 +41,31 @@ class ExpertParallelMoe:
             self._bufs[name] = b
         return b
 
+    def prepare(self, layer, x, out):
+        """Record this rank's kernels of one step for (layer, x, out) as three graphs -- shared expert; route +
+        resident experts; finish -- which forward() then launches between the collectives instead of a dozen
+        kernels one by one.  The collectives themselves stay ordinary NCCL calls.  CUDA block only."""
+        if self.world == 1 or not x.is_cuda or not hasattr(self.block, "capture"):
+            return
+        self.forward(layer, x, out)                      # set-up work and buffers, eagerly
+        torch.cuda.synchronize(x.device)
+        T, D = x.shape
+        b, d = self.block, self.desc
+        X, partial, routed = self._bufs["X"], self._bufs["partial"], self._bufs["routed"]
+        g_shared = b.capture(lambda s: b.shared(d, layer, x, stream=s))
+        g_experts = b.capture(lambda s: (b.route(d, layer, X, stream=s), b.experts(d, layer, X, partial, stream=s)))
+        # finish is recorded after a shared() of the same row count so that it takes the shared rows from there
+        b.shared(d, layer, x)
+        g_finish = b.capture(lambda s: b.finish(d, layer, x, routed, out, stream=s))
+        torch.cuda.synchronize(x.device)
+        self._graphs[(id(layer), x.data_ptr(), out.data_ptr())] = (g_shared, g_experts, g_finish, layer)
+
     def forward(self, layer, x, out):
         """out[T,D] += MoE(x[T,D]) for this rank's rows; `layer` is this rank's shard."""
         T, D = x.shape
+        gs = self._graphs.get((id(layer), x.data_ptr(), out.data_ptr()))
+        if gs is not None:
+            return self._forward_graphs(gs, x, out)
         # The shared expert needs only this rank's rows: on a second stream it runs beside the exchange and the
         # routed experts (CUDA block only; the CPU stand-in has no streams).
         side = None
@@ -69,4 +92,18 @@ class ExpertParallelMoe:
         if side is not None:
             torch.cuda.current_stream(x.device).wait_stream(side)
         self.block.finish(self.desc, layer, x, routed, out)
+        return out
+
+    def _forward_graphs(self, gs, x, out):
+        g_shared, g_experts, g_finish, _ = gs
+        T, D = x.shape
+        X, partial, routed = self._bufs["X"], self._bufs["partial"], self._bufs["routed"]
+        side, cur = self._side, torch.cuda.current_stream(x.device)
+        side.wait_stream(cur)
+        g_shared.replay(side)
+        dist.all_gather_into_tensor(X, x, group=self.group)
+        g_experts.replay()
+        dist.reduce_scatter_tensor(routed, partial, op=dist.ReduceOp.SUM, group=self.group)
+        cur.wait_stream(side)
+        g_finish.replay()
         return out

@@ -86,6 +86,13 @@ class MoeLayer:
         return sum(t.numel() * t.element_size() for t in (self.gu_q, self.gu_s, self.dn_q, self.dn_s))
 
 
+class _RawStream:
+    """A CUDA stream handle with the attribute the block's stream arguments read."""
+
+    def __init__(self, handle):
+        self.cuda_stream = handle
+
+
 class MoeGraph:
     """A captured block call; replay() launches it on a stream."""
 
@@ -191,6 +198,19 @@ class MoeBlock:
         self._chk(self.lib.sw_moe_finish(self.ctx, C.byref(d), C.byref(l), x.data_ptr(), routed.data_ptr(),
                                          out.data_ptr(), x.shape[0], self._stream(stream)), "sw_moe_finish")
         return out
+
+    def capture(self, fn, keep=()):
+        """Record the stage calls `fn(stream)` makes (route / experts / shared / finish with that stream) into a
+        MoeGraph.  fn must already have run once eagerly with the same arguments."""
+        self._chk(self.lib.sw_moe_capture_begin(self.ctx), "sw_moe_capture_begin")
+        cs = _RawStream(self.lib.sw_moe_capture_stream(self.ctx))
+        h = C.c_void_p()
+        try:
+            fn(cs)
+        finally:
+            rc = self.lib.sw_moe_capture_end(self.ctx, C.byref(h))
+        self._chk(rc, "sw_moe_capture_end")
+        return MoeGraph(self, h, self._last, keep)
 
     def routing(self, want_scores=False):
         """Host copies of the last routing: sel, w, G, gexp, gbeg, gcnt, grow, rowof (c/laguna.c:709-723)."""

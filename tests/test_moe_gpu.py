@@ -368,3 +368,29 @@ def test_forward_host_pinned_and_pageable_agree(orc):
     assert rel_l2(out_pageable, want) < 1e-3 and rel_l2(op.numpy(), want) < 1e-3
     assert np.array_equal(op.numpy(), out_pageable)
     blk.close()
+
+
+def test_stage_capture_replays_like_eager(orc):
+    """route + experts and shared + finish recorded with the stage-capture API give the one-call block's result."""
+    case = synth_case("c2", D=512, E=32, K=4, I=128, SI=128, T=24)
+    blk, layer, desc = make_block(case)
+    x = torch.from_numpy(case.x).cuda()
+    want = torch.from_numpy(case.hin).cuda(); blk.forward(desc, layer, x, want)
+    out = torch.from_numpy(case.hin).cuda()
+    routed = torch.empty_like(x)
+
+    def stages(s=None):
+        blk.route(desc, layer, x, stream=s); blk.experts(desc, layer, x, routed, stream=s)
+        blk.shared(desc, layer, x, stream=s); blk.finish(desc, layer, x, routed, out, stream=s)
+
+    stages()                                       # eager once: set-up work cannot be captured
+    torch.cuda.synchronize()
+    g = blk.capture(stages)
+    out.copy_(torch.from_numpy(case.hin).cuda())
+    l0 = blk.lib.sw_launch_count()
+    g.replay()
+    torch.cuda.synchronize()
+    assert blk.lib.sw_launch_count() - l0 >= 8
+    assert rel_l2(out.cpu().numpy(), want.cpu().numpy()) < 1e-6
+    check_routing(blk.routing(), orc.moe_group(case.host, case.x, None, exact=1))
+    g.close(); blk.close()
