@@ -224,10 +224,14 @@ def run_ours(args):
         torch.cuda.synchronize()
     # expert parallel: this rank's kernels of a step as three graphs per pair (the collectives stay NCCL calls)
     if ep is not None and not args.no_graph:
-        for li in range(len(layers)):
-            for bi in range(NB):
-                if (li - bi) % np.gcd(len(layers), NB) == 0:
-                    ep.prepare(layers[li], xs[bi], outs[bi])
+        try:
+            for li in range(len(layers)):
+                for bi in range(NB):
+                    if (li - bi) % np.gcd(len(layers), NB) == 0:
+                        ep.prepare(layers[li], xs[bi], outs[bi])
+        except Exception as e:                                  # every rank runs the same code: all fall back together
+            print("stage capture failed (%s); launching the kernels one by one" % e, file=sys.stderr, flush=True)
+            ep._graphs.clear()
         torch.cuda.synchronize()
 
     def step(i, use_graph=True):
