@@ -69,8 +69,11 @@ def test_golden_fixtures(orc, name):
     ("c3", dict(D=512, I=128, SI=128), 300),             # Zipf-skewed, ragged group sizes
     ("c4", dict(D=640, I=192), 64),                      # 384 experts, softmax
     ("c5", dict(D=512, I=128, SI=128), 50),              # 512 experts + shared
-    ("c2", dict(D=512, E=16, K=4, I=128, SI=128), 40),   # ~10 rows per expert: passes of up to 16 rows
+    ("c2", dict(D=512, E=16, K=4, I=128, SI=128), 40),   # ~10 rows per expert: several passes over a group
     ("c3", dict(D=512, E=16, K=4, I=256, SI=128), 45),   # the same under the Zipf bias: groups from 1 to over 16 rows
+    ("c2", dict(D=256, E=8, K=1, I=128, SI=128), 13),    # top-1
+    ("c1", dict(D=256, E=8, K=8, I=128), 5),             # every expert selected, softmax
+    ("c2", dict(D=384, E=12, K=3, I=128, SI=64), 7),     # D, experts not multiples of 128 / 8
 ])
 def test_scaled_configs(orc, base, kw, T):
     case = synth_case(base, corr_bias_std=0.01, T=T, **kw)
