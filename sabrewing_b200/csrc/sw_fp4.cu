@@ -4,13 +4,15 @@
 //
 // These calls serve single-token decode from host buffers, so the weight stream is short (K experts) and the
 // kernels run on CUDA cores: a warp owns RW output rows, a lane one 16-byte piece (32 columns = exactly one
-// scale block) of each row per step; the token row sits in shared memory and is read once for all RW rows.
+// scale block) of each row per step; the token row is read through L1 once for all RW rows.
 // A code is turned into its value without a table: the four bits s e1 e0 m, placed at fp16 bits 15, 11..10
 // and 9, are the fp16 number value * 2^-14 (e = 0 gives the subnormal m * 2^-15), so value = fp16 * 16384.
 #include "sw_common.cuh"
 #include <cuda_fp16.h>
 
-#define SW_FP4_RW 4            // rows (or gate/up row pairs) per warp
+// rows per warp (gate/up: row pairs, i.e. twice as many weight rows; fewer of them keep the register count,
+// and with it the number of resident warps, where the plain rows are)
+#define SW_FP4_RW(GLU) ((GLU) ? 2 : 4)
 #define SW_FP4_WARPS 8
 
 // 2^(e-127); 0xFF (the format's NaN) -> 0, 0 -> the denormal 2^-127 (c/moe_quant.h:250-256)
@@ -26,20 +28,24 @@ __device__ __forceinline__ float2 sw_fp4_pair(unsigned b) {
     return __half22float2(*reinterpret_cast<const __half2 *>(&h));
 }
 
-// sum over one 16-byte piece: 32 columns of x (shared memory) times the 32 codes, times 2^-14
-// (xs: the piece's eight float4, stored at position j ^ bx so that the lanes of a warp hit different banks)
-__device__ __forceinline__ float sw_fp4_piece(const uint4 w, const float4 *xs, int bx) {
-    float p = 0.f;
+// sum over one 16-byte piece: 32 columns of x times the 32 codes, times 2^-14
+__device__ __forceinline__ float sw_fp4_piece(const uint4 w, const float4 *xs, int) {
+    // four partial sums (one per 8 columns): one chain of 32 dependent multiply-adds per piece would leave the warp
+    // waiting on arithmetic latency
+    float p[4];
     const unsigned ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
     for (int q = 0; q < 4; q++) {
-        const float4 xa = xs[(2 * q) ^ bx], xb = xs[(2 * q + 1) ^ bx];        // columns 8q .. 8q+7
+        const float4 xa = __ldg(xs + 2 * q), xb = __ldg(xs + 2 * q + 1);      // columns 8q .. 8q+7
         const float2 v0 = sw_fp4_pair(ww[q] & 0xFFu), v1 = sw_fp4_pair((ww[q] >> 8) & 0xFFu);
         const float2 v2 = sw_fp4_pair((ww[q] >> 16) & 0xFFu), v3 = sw_fp4_pair(ww[q] >> 24);
-        p = fmaf(xa.x, v0.x, p); p = fmaf(xa.y, v0.y, p); p = fmaf(xa.z, v1.x, p); p = fmaf(xa.w, v1.y, p);
-        p = fmaf(xb.x, v2.x, p); p = fmaf(xb.y, v2.y, p); p = fmaf(xb.z, v3.x, p); p = fmaf(xb.w, v3.y, p);
+        float a = xa.x * v0.x, b = xa.y * v0.y;
+        a = fmaf(xa.z, v1.x, a); b = fmaf(xa.w, v1.y, b);
+        a = fmaf(xb.x, v2.x, a); b = fmaf(xb.y, v2.y, b);
+        a = fmaf(xb.z, v3.x, a); b = fmaf(xb.w, v3.y, b);
+        p[q] = a + b;
     }
-    return p;
+    return (p[0] + p[1]) + (p[2] + p[3]);
 }
 
 // GLU = false: Y[z, o] = X[z, :] . W[o, :]                       (z = blockIdx.y: a token row, or an expert slot)
@@ -50,20 +56,19 @@ __global__ void __launch_bounds__(SW_FP4_WARPS * 32)
 k_fp4_rows(const uint8_t *__restrict__ P, const uint8_t *__restrict__ ES, const int *__restrict__ sel, long long rows_per_expert,
            const float *__restrict__ X, long long x_stride, float *__restrict__ Y, long long y_stride,
            int I, int O, float limit) {
-    extern __shared__ float4 sw_fp4_x[];
+    // The token row (16 KB at most per warp step) is read straight through L1: every warp of the CTA reads the same
+    // pieces, so after the first touch they are hits, and no CTA waits for a staging copy before it streams weights.
     const int z = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const float *x = X + (size_t)z * x_stride;
-    for (int i = threadIdx.x; i < I / 4; i += blockDim.x)             // float4 j of piece b goes to 8b + (j ^ (b & 7))
-        sw_fp4_x[(i & ~7) | ((i & 7) ^ ((i >> 3) & 7))] = reinterpret_cast<const float4 *>(x)[i];
-    __syncthreads();
+    const float4 *sw_fp4_x = reinterpret_cast<const float4 *>(X + (size_t)z * x_stride);
     const long long erow = sel ? (long long)sel[z] * rows_per_expert : 0;
-    const int o0 = (blockIdx.x * SW_FP4_WARPS + warp) * SW_FP4_RW;
+    constexpr int RW = SW_FP4_RW(GLU);
+    const int o0 = (blockIdx.x * SW_FP4_WARPS + warp) * RW;
     if (o0 >= O) return;
-    constexpr int NR = GLU ? 2 * SW_FP4_RW : SW_FP4_RW;            // weight rows per warp
+    constexpr int NR = GLU ? 2 * RW : RW;                          // weight rows per warp
     const uint8_t *pw[NR], *pe[NR];
 #pragma unroll
     for (int r = 0; r < NR; r++) {
-        const int o = min(o0 + (r % SW_FP4_RW), O - 1) + (GLU && r >= SW_FP4_RW ? O : 0);
+        const int o = min(o0 + (r % RW), O - 1) + (GLU && r >= RW ? O : 0);
         pw[r] = P + (size_t)(erow + o) * (I / 2);
         pe[r] = ES + (size_t)(erow + o) * (I / 32);
     }
@@ -71,13 +76,26 @@ k_fp4_rows(const uint8_t *__restrict__ P, const uint8_t *__restrict__ ES, const 
 #pragma unroll
     for (int r = 0; r < NR; r++) acc[r] = 0.f;
     const int nblk = I / 32;
-    for (int b = lane; b < nblk; b += 32) {
-        uint4 w[NR]; unsigned e[NR];
+    // software pipeline: the pieces of the next step are requested before the current ones are multiplied
+    uint4 w[NR]; unsigned e[NR];
+    if (lane < nblk) {
 #pragma unroll
-        for (int r = 0; r < NR; r++) { w[r] = reinterpret_cast<const uint4 *>(pw[r])[b]; e[r] = pe[r][b]; }
+        for (int r = 0; r < NR; r++) { w[r] = reinterpret_cast<const uint4 *>(pw[r])[lane]; e[r] = pe[r][lane]; }
+    }
+    for (int b = lane; b < nblk; b += 32) {
+        uint4 wn[NR]; unsigned en[NR];
+        const bool more = b + 32 < nblk;
+        if (more) {
+#pragma unroll
+            for (int r = 0; r < NR; r++) { wn[r] = reinterpret_cast<const uint4 *>(pw[r])[b + 32]; en[r] = pe[r][b + 32]; }
+        }
         const float4 *xs = sw_fp4_x + b * 8;
 #pragma unroll
         for (int r = 0; r < NR; r++) acc[r] = fmaf(sw_fp4_piece(w[r], xs, b & 7) * 16384.f, sw_ue8m0(e[r]), acc[r]);
+        if (more) {
+#pragma unroll
+            for (int r = 0; r < NR; r++) { w[r] = wn[r]; e[r] = en[r]; }
+        }
     }
 #pragma unroll
     for (int r = 0; r < NR; r++)
@@ -86,10 +104,10 @@ k_fp4_rows(const uint8_t *__restrict__ P, const uint8_t *__restrict__ ES, const 
     if (lane == 0) {
         float *y = Y + (size_t)z * y_stride;
 #pragma unroll
-        for (int r = 0; r < SW_FP4_RW; r++) {
+        for (int r = 0; r < RW; r++) {
             if (o0 + r >= O) break;
             if (GLU) {
-                float g = acc[r], u = acc[SW_FP4_RW + r];
+                float g = acc[r], u = acc[RW + r];
                 g = g > limit ? limit : g;
                 u = u > limit ? limit : (u < -limit ? -limit : u);
                 y[o0 + r] = (g / (1.f + expf(-g))) * u;
@@ -114,15 +132,14 @@ static int sw_fp4_launch(const SwLaunchCfg &c, bool glu, const void *P, const vo
                          const float *X, long long x_stride, float *Y, long long y_stride, int Z, int I, int O, float limit) {
     if (Z <= 0 || O <= 0) return 0;
     if (I <= 0 || (I % 32) || (((uintptr_t)P) & 15) || ((I / 2) % 16)) return -1;
-    const size_t smem = (size_t)I * 4;
-    if (smem > 200 * 1024) return -1;
+    const size_t smem = 0;
     static bool attr_done = false;
     if (!attr_done) {
         if (cudaFuncSetAttribute(k_fp4_rows<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
             cudaFuncSetAttribute(k_fp4_rows<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return -1;
         attr_done = true;
     }
-    const int per_cta = SW_FP4_WARPS * SW_FP4_RW;
+    const int per_cta = SW_FP4_WARPS * (glu ? SW_FP4_RW(true) : SW_FP4_RW(false));
     dim3 grid((unsigned)((O + per_cta - 1) / per_cta), (unsigned)Z);
     if (glu) k_fp4_rows<true><<<grid, SW_FP4_WARPS * 32, smem, c.stream>>>((const uint8_t *)P, (const uint8_t *)ES, sel, rows_per_expert, X, x_stride, Y, y_stride, I, O, limit);
     else k_fp4_rows<false><<<grid, SW_FP4_WARPS * 32, smem, c.stream>>>((const uint8_t *)P, (const uint8_t *)ES, sel, rows_per_expert, X, x_stride, Y, y_stride, I, O, limit);
