@@ -185,11 +185,15 @@ int  sw_moe_capture_end(SwMoeCtx *ctx, SwMoeGraph **graph);
  * the library image that every GPU loading the library keeps until exit.  Meant
  * for hosts that cannot allocate when they need a routing decision (all free
  * device memory already given away, or no tolerance for the device-wide
- * synchronisation of an allocation).  Same ids and weights as sw_moe_route.  Sizes
- * beyond the limits return -1 with an error text.  The array is shared by all
- * calls on a GPU: calls that overlap on the device race, so order them.  The
- * first call on each device looks up the array's device address; issue it outside
- * any stream capture. */
+ * synchronisation of an allocation).  Same ids as sw_moe_route; weights equal to
+ * within one unit in the last place.  Sizes beyond the limits, NULL or misaligned
+ * buffers (x, router_w: 16 bytes) return -1 with an error text.  The array is
+ * shared by all calls on a GPU: calls that overlap on the device race, so order
+ * them.  The first call on each device looks up the array's device address; issue
+ * it outside any stream capture and at start-up: CUDA loads the module that holds
+ * the array lazily, so the memory is reserved by that first call, not when the
+ * library loads, and a host that has already given all device memory away by then
+ * gets -1. */
 int  sw_moe_route_static(const SwMoeDesc *desc, const SwMoeLayer *layer, const float *x, int T,
                          int *sel, float *w, void *stream);
 
@@ -200,8 +204,36 @@ int  sw_moe_get_routing(SwMoeCtx *ctx, int *sel, float *w, float *scores, int *G
                         int *gexp, int *gbeg, int *gcnt, int *grow, int *rowof);
 
 /* Device-side status word of the last launches (0 = clean); bit 0: an expert id
- * outside [0,E) reached the dispatch, bit 1: a row index outside [0,T). */
+ * outside [0,E) reached the dispatch, bit 1: a row index outside [0,T), bit 2: a
+ * bounded device-side wait ran out (the kernel gave up and returned), bit 3: an
+ * activation outside the fp16 range of the tensor-core expert kernels was clamped
+ * to +-65504 (the result is then not the reference's; the reference is f32
+ * throughout, c/moe_quant.h:45-217). */
 int  sw_moe_status(SwMoeCtx *ctx);
+/* Which expert kernels the last sw_moe_experts / sw_moe_forward of this context
+ * used: 0 CUDA cores, 1 mma.sync + cp.async, 2 mma.sync + TMA, 3 tcgen05 + TMEM;
+ * -1 before the first call.  For tests and benchmarks that must know the path. */
+int  sw_moe_last_path(SwMoeCtx *ctx);
+/* Argument checks of the block calls without a context or a device: descriptor
+ * ranges, layer pointers present and 16-byte aligned, x / out present and 16-byte
+ * aligned.  0 = acceptable, -1 = refused with an error text. */
+int  sw_moe_validate(const SwMoeDesc *desc, const SwMoeLayer *layer, const void *x, const void *out);
+/* Failure handling hooks; failures are injected on the host, never on the device.
+ * sw_test_fail_after(n): the reference's COLI_GPU_FAIL_AFTER (c/backend_cuda.cu:684-692,
+ * tested in c/tests/test_backend_cuda.cu:93-98): every compute entry point (the block,
+ * its stages, graph launches, the lag_cuda_* products) reports failure once n calls have
+ * succeeded; n = 0: every call fails; n < 0: off.  SW_FAIL_AFTER=n in the environment
+ * does the same from the start.  Uploads, queries and context creation are not gated.
+ * sw_test_fail_alloc(n): the n-th and every later device / page-locked allocation of this
+ * library fails without calling CUDA (n <= 0: off).
+ * sw_moe_test_wait_timeout: launches one CTA whose bounded barrier wait cannot succeed
+ * and returns the status bits it left (bit 2 expected); the context stays usable.
+ * sw_selftest_host: host-only checks of the per-device set-up slots and the tensor-map
+ * cache keying, 0 = pass. */
+void sw_test_fail_after(int n);
+void sw_test_fail_alloc(int n);
+int  sw_moe_test_wait_timeout(SwMoeCtx *ctx, int iters);
+int  sw_selftest_host(void);
 /* Per-stage device timing with CUDA events recorded on the call's stream between
  * the kernels of sw_moe_forward (what the reference's COLI_CUDA_PROFILE split does,
  * c/backend_cuda.cu:822-929).  enable=1 starts a fresh accumulation (up to 512

@@ -47,11 +47,38 @@ def isa_level():
     return "v4" if need <= _cpu_flags() else "v3"
 
 
-def build(ref_dir="/root/reference/c"):
-    """Compile the restatement, and the in-place reference build when its sources exist."""
+def reference_dir():
+    """The c/ directory of the reference checkout: $SABREWING_REF, else ../reference/c beside this repository.
+
+    None when neither holds laguna.c (the compiled reference under _ref/ is then used as shipped)."""
+    cands = [os.environ.get("SABREWING_REF"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference", "c")]
+    for c in cands:
+        if c and os.path.isfile(os.path.join(c, "laguna.c")):
+            return c
+    return None
+
+
+def build(ref_dir=None):
+    """Compile the restatement; with a reference checkout at hand also the in-place reference builds:
+    the CPU path (ref), the reference engine linked against this repository's library (dropin) and the
+    reference's CUDA tier for sm_100a (refcuda).  An explicit ref_dir that does not exist is an error."""
     subprocess.run(["make", "-C", _HERE, "all"], check=True, capture_output=True)
-    if os.path.isdir(ref_dir):
-        subprocess.run(["make", "-C", _HERE, "ref", "REF=" + ref_dir], check=True, capture_output=True)
+    if ref_dir is None:
+        ref_dir = reference_dir()
+        if ref_dir is None:
+            return
+    elif not os.path.isfile(os.path.join(ref_dir, "laguna.c")):
+        raise FileNotFoundError("no reference checkout at %r (set SABREWING_REF=<checkout>/c)" % ref_dir)
+    subprocess.run(["make", "-C", _HERE, "ref", "REF=" + ref_dir], check=True, capture_output=True)
+    swlib = os.path.join(os.path.dirname(_HERE), "sabrewing_b200", "libsabrewing_b200.so")
+    if os.path.exists(swlib):
+        subprocess.run(["make", "-C", _HERE, "dropin", "REF=" + ref_dir], check=True, capture_output=True)
+    if os.path.exists("/usr/local/cuda/bin/nvcc") or os.environ.get("NVCC"):
+        subprocess.run(["make", "-C", _HERE, "refcuda", "REF=" + ref_dir], check=True, capture_output=True)
+
+
+DROPIN_PATH = os.path.join(_HERE, "_ref", "laguna_dropin")
+REF_CUDA_PATH = os.path.join(_HERE, "_ref", "libref_cuda_laguna.so")
 
 
 def _ptr(a):

@@ -63,6 +63,12 @@ SIGNATURES = {
     "sw_moe_route_static": (_i, [_pd, _pl, _vp, _i, _vp, _vp, _vp]),
     "sw_moe_get_routing": (_i, [_vp, _vp, _vp, _vp, C.POINTER(_i), _vp, _vp, _vp, _vp, _vp]),
     "sw_moe_status": (_i, [_vp]),
+    "sw_moe_last_path": (_i, [_vp]),
+    "sw_moe_validate": (_i, [_pd, _pl, _vp, _vp]),
+    "sw_test_fail_after": (None, [_i]),
+    "sw_test_fail_alloc": (None, [_i]),
+    "sw_moe_test_wait_timeout": (_i, [_vp, _i]),
+    "sw_selftest_host": (_i, []),
     "sw_moe_profile": (_i, [_vp, _i]),
     "sw_moe_profile_read": (_i, [_vp, C.POINTER(C.c_float), C.POINTER(_i)]),
     "sw_moe_stage_count": (_i, []),

@@ -11,9 +11,58 @@
 #include <string.h>
 #include <stdlib.h>
 
-static long long g_launches = 0;
-void sw_count_launch(int n) { g_launches += n; }
-extern "C" long long sw_launch_count(void) { return g_launches; }
+static std::atomic<long long> g_launches{0};
+void sw_count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+extern "C" long long sw_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+std::mutex &sw_setup_mutex() { static std::mutex m; return m; }
+
+static int sw_env_int(const char *name, int dflt) { const char *e = getenv(name); return e && *e ? atoi(e) : dflt; }
+const SwTuning &sw_tuning() {
+    static const SwTuning t = [] {
+        SwTuning v{};
+        v.expert_pref = 2;
+        const char *e = getenv("SW_EXPERT_PATH");
+        if (e && !strcmp(e, "umma")) v.expert_pref = 3;
+        if (e && !strcmp(e, "tma")) v.expert_pref = 4;            // TMA decode kernels whatever the group size
+        if (e && !strcmp(e, "mma")) v.expert_pref = 1;
+        if (e && !strcmp(e, "simt")) v.expert_pref = 0;
+        const char *f = getenv("SW_FORCE_SIMT");
+        v.force_simt = (f && *f && *f != '0') ? 1 : 0;
+        if (v.force_simt) v.expert_pref = 0;
+        v.umma_min_rows = sw_env_int("SW_UMMA_MIN_ROWS", 16);    // mean rows per group from which the tcgen05 kernels win (measured)
+        v.tma_mt = sw_env_int("SW_TMA_MT", 0);
+        if (v.tma_mt != 1 && v.tma_mt != 2) v.tma_mt = 0;
+        v.tma_p = sw_env_int("SW_TMA_P", 0);
+        v.mma_mt = sw_env_int("SW_MMA_MT", 0);
+        v.fail_after = sw_env_int("SW_FAIL_AFTER", -1);
+        return v;
+    }();
+    return t;
+}
+
+// Host-side failure injection, two hooks.
+// (1) Compute calls, the reference's COLI_GPU_FAIL_AFTER (c/backend_cuda.cu:684-692): with SW_FAIL_AFTER=n in the
+//     environment, or after sw_test_fail_after(n), every compute entry point reports failure once n calls have
+//     succeeded (n = 0: every call fails); uploads, queries and context creation are not gated.  n < 0: off.
+// (2) Allocations: after sw_test_fail_alloc(n) the n-th and every later device or page-locked allocation of this
+//     library reports failure without calling CUDA (n <= 0: off).
+static std::atomic<long> g_fail_after{-2}, g_calls{0};         // -2: not read from the environment yet
+extern "C" void sw_test_fail_after(int n) { g_fail_after.store(n >= 0 ? n : -1); g_calls.store(0); }
+static bool sw_fault_injected() {
+    long n = g_fail_after.load(std::memory_order_relaxed);
+    if (n == -2) { n = sw_tuning().fail_after; g_fail_after.store(n); }
+    return n >= 0 && g_calls.fetch_add(1) >= n;
+}
+#define SW_GATE() do { if (sw_fault_injected()) return sw_fail("injected failure (SW_FAIL_AFTER)"); } while (0)
+static std::atomic<int> g_fail_alloc{0}, g_alloc_count{0};
+extern "C" void sw_test_fail_alloc(int n) { g_fail_alloc.store(n > 0 ? n : 0); g_alloc_count.store(0); }
+static bool sw_inject_alloc_failure() {
+    const int n = g_fail_alloc.load(std::memory_order_relaxed);
+    return n > 0 && g_alloc_count.fetch_add(1) + 1 >= n;
+}
+static cudaError_t sw_malloc(void **p, size_t n) { if (sw_inject_alloc_failure()) { *p = nullptr; return cudaErrorMemoryAllocation; } return cudaMalloc(p, n); }
+static cudaError_t sw_malloc_host(void **p, size_t n) { if (sw_inject_alloc_failure()) { *p = nullptr; return cudaErrorMemoryAllocation; } return cudaMallocHost(p, n); }
 
 static thread_local char g_err[256] = "";
 static int sw_fail(const char *fmt, ...) {
@@ -39,7 +88,7 @@ struct SwBuf {
         if (need <= cap) return 0;
         release();
         size_t want = need * 2;
-        cudaError_t e = pinned ? cudaMallocHost(&p, want) : cudaMalloc(&p, want);
+        cudaError_t e = pinned ? sw_malloc_host(&p, want) : sw_malloc(&p, want);
         if (e != cudaSuccess) { p = nullptr; cap = 0; cudaGetLastError(); return -1; }
         cap = want; return 0;
     }
@@ -69,6 +118,8 @@ struct SwMoeCtx {
     void *spk = nullptr;         // packed bf16 hi/lo copy of x for the shared expert
     float *sums = nullptr;       // row sums of x and partial row sums of the SiLU*up rows
     int lastT = 0, lastK = 0, lastE = 0;
+    int last_path = -1;          // expert kernels of the last experts/forward call (sw_moe_last_path)
+    int umma_terms = 2;          // fp16 terms per activation on the tcgen05 path: 1 = hi only, 2 = hi + lo
     int cap_on = 0, cap_prof = 0; long long cap_l0 = 0;   // open stage capture (sw_moe_capture_begin)
     // a shared-expert result left by sw_moe_shared for the next sw_moe_finish of the same row count
     int shared_T = -1, shared_slices = 1; float *shared_so = nullptr;
@@ -98,12 +149,14 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
     if (max_tokens <= 0 || max_experts <= 0 || max_experts > SW_MAX_EXPERTS || max_topk <= 0 ||
         max_topk > SW_MAX_TOPK || max_D <= 0 || max_I <= 0 || max_SI < 0)
         return sw_fail("ctx_create: bad limits (experts <= %d, topk <= %d)", SW_MAX_EXPERTS, SW_MAX_TOPK);
+    if (dev < 0 || dev >= SW_MAX_DEVICES) return sw_fail("ctx_create: device %d outside [0,%d)", dev, SW_MAX_DEVICES);
+    sw_tuning();                                   // the SW_* variables are read here, once, not on the call path
     SW_CUDA(cudaSetDevice(dev));
     SwMoeCtx *c = new SwMoeCtx();
     c->dev = dev; c->maxT = max_tokens; c->maxE = max_experts; c->maxK = max_topk;
     c->maxD = max_D; c->maxI = max_I; c->maxSI = max_SI;
     cudaDeviceProp prop;
-    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) { delete c; return sw_cuda_fail(cudaGetLastError(), "cudaGetDeviceProperties"); }
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) { const cudaError_t e = cudaGetLastError(); sw_moe_ctx_destroy(c); return sw_cuda_fail(e, "cudaGetDeviceProperties"); }
     c->num_sms = prop.multiProcessorCount;
     if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaStreamCreateWithFlags(&c->aux, cudaStreamNonBlocking) != cudaSuccess ||
@@ -111,7 +164,11 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
         cudaEventCreateWithFlags(&c->ev_res, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&c->ev_pack, cudaEventDisableTiming) != cudaSuccess) { delete c; return sw_cuda_fail(cudaGetLastError(), "cudaStreamCreate"); }
+        cudaEventCreateWithFlags(&c->ev_pack, cudaEventDisableTiming) != cudaSuccess) {
+        const cudaError_t e = cudaGetLastError();
+        sw_moe_ctx_destroy(c);                     // releases whatever was created before the failure
+        return sw_cuda_fail(e, "cudaStreamCreate");
+    }
 
     const size_t T = max_tokens, E = max_experts, K = max_topk, D = max_D, I = max_I, SI = max_SI, P = T * K;
     size_t sizes[] = {
@@ -135,8 +192,8 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
         ((size_t)((D + 127) / 128) * (T < 128 ? T : 128) + ((size_t)c->num_sms * 32 * 256 + E - 1) / E + T + 64) * E * 8   // rpart
     };
     size_t total = 0; for (size_t s : sizes) total += sw_align(s);
-    if (cudaMalloc(&c->block, total) != cudaSuccess) {
-        cudaGetLastError(); cudaStreamDestroy(c->stream); delete c;
+    if (sw_malloc(&c->block, total) != cudaSuccess) {
+        cudaGetLastError(); c->block = nullptr; sw_moe_ctx_destroy(c);
         return sw_fail("ctx_create: cudaMalloc of %zu bytes failed", total);
     }
     char *p = (char *)c->block; int i = 0;
@@ -147,11 +204,11 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
     c->glu = (float *)take(); c->slots = (float *)take(); c->sglu = (float *)take(); c->so = (float *)take();
     c->routed = (float *)take(); c->dx = (float *)take(); c->dout = (float *)take(); c->xp = take(); c->sums = (float *)take(); c->spk = take(); c->um.xg = take(); { char *q = (char *)take(); c->um.nchunks = (int *)q; c->um.chunks = q + 256; } c->rpart = (double *)take();
     cudaMemsetAsync(c->r.G, 0, 256, c->stream); cudaMemsetAsync(c->r.status, 0, 256, c->stream);
-    if (cudaMallocHost((void **)&c->hx, T * D * 4) != cudaSuccess || cudaMallocHost((void **)&c->hout, T * D * 4) != cudaSuccess) {
+    if (sw_malloc_host((void **)&c->hx, T * D * 4) != cudaSuccess || sw_malloc_host((void **)&c->hout, T * D * 4) != cudaSuccess) {
         cudaGetLastError(); sw_moe_ctx_destroy(c);
         return sw_fail("ctx_create: pinned staging allocation failed");
     }
-    SW_CUDA(cudaStreamSynchronize(c->stream));
+    if (cudaStreamSynchronize(c->stream) != cudaSuccess) { const cudaError_t e = cudaGetLastError(); sw_moe_ctx_destroy(c); return sw_cuda_fail(e, "cudaStreamSynchronize"); }
     *out = c;
     return 0;
 }
@@ -176,23 +233,56 @@ extern "C" void sw_moe_ctx_destroy(SwMoeCtx *c) {
     delete c;
 }
 
-static int sw_check(const SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, int T) {
-    if (!c || !d || !L) return sw_fail("null argument");
-    if (T < 0 || T > c->maxT) return sw_fail("T=%d outside [0,%d]", T, c->maxT);
-    if (d->n_experts <= 0 || d->n_experts > c->maxE) return sw_fail("n_experts=%d outside (0,%d]", d->n_experts, c->maxE);
-    if (d->topk <= 0 || d->topk > c->maxK || d->topk > d->n_experts) return sw_fail("topk=%d invalid", d->topk);
+// Argument checks that need no context and no device: descriptor ranges, layer pointers present and 16-byte
+// aligned (the kernels read them with 128-bit loads and lay TMA tensor maps over the blobs).
+static int sw_validate(const SwMoeDesc *d, const SwMoeLayer *L) {
+    if (!d || !L) return sw_fail("null argument");
+    if (d->n_experts <= 0 || d->n_experts > SW_MAX_EXPERTS) return sw_fail("n_experts=%d outside (0,%d]", d->n_experts, SW_MAX_EXPERTS);
+    if (d->topk <= 0 || d->topk > SW_MAX_TOPK || d->topk > d->n_experts) return sw_fail("topk=%d invalid", d->topk);
     if (d->route_act < 0 || d->route_act > 2) return sw_fail("route_act=%d unknown", d->route_act);
     if (d->shared_mode != SW_SHARED_NONE && d->shared_mode != SW_SHARED_UNSCALED)
         return sw_fail("shared_mode=%d is not wired (the reference wires NONE and UNSCALED only)", d->shared_mode);
-    if (L->D <= 0 || L->D > c->maxD || L->D % 32) return sw_fail("D=%d must be a multiple of 32 and <= %d", L->D, c->maxD);
-    if (L->I <= 0 || L->I > c->maxI || L->I % 32) return sw_fail("I=%d must be a multiple of 32 and <= %d", L->I, c->maxI);
+    if (L->D <= 0 || L->D % 32) return sw_fail("D=%d must be a positive multiple of 32", L->D);
+    if (L->I <= 0 || L->I % 32) return sw_fail("I=%d must be a positive multiple of 32", L->I);
     if (d->shared_mode != SW_SHARED_NONE) {
-        if (L->SI <= 0 || L->SI > c->maxSI || L->SI % 8) return sw_fail("SI=%d must be a multiple of 8 and <= %d", L->SI, c->maxSI);
+        if (L->SI <= 0 || L->SI % 8) return sw_fail("SI=%d must be a positive multiple of 8", L->SI);
         if (!L->sh_gate || !L->sh_up || !L->sh_down) return sw_fail("shared expert weights missing");
     }
     if (L->gs < 0 || (L->gs > 0 && L->gs % 32)) return sw_fail("gs=%d must be 0 or a multiple of 32", L->gs);
     if (!L->router_w || !L->gu_q || !L->gu_s || !L->dn_q || !L->dn_s) return sw_fail("layer weights missing");
     if (L->router_dtype != SW_DTYPE_F32 && L->router_dtype != SW_DTYPE_BF16) return sw_fail("router_dtype=%d unknown", L->router_dtype);
+    const uintptr_t al = (uintptr_t)L->router_w | (uintptr_t)L->gu_s | (uintptr_t)L->dn_s | (uintptr_t)L->sh_gate | (uintptr_t)L->sh_up |
+                         (uintptr_t)L->sh_down;
+    if (al & 15) return sw_fail("layer pointers must be 16-byte aligned (router_w, gu_s, dn_s, sh_*)");
+    if (((uintptr_t)L->corr_bias | (uintptr_t)L->logit_bias) & 3) return sw_fail("corr_bias / logit_bias must be 4-byte aligned");
+    return 0;
+}
+// row buffers: present and 16-byte aligned (float4 / uint4 accesses)
+static int sw_validate_rows(const void *a, const void *b, const void *c3, const char *what) {
+    if (!a || !b || !c3) return sw_fail("%s: null buffer", what);
+    if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c3) & 15) return sw_fail("%s: row buffers must be 16-byte aligned", what);
+    return 0;
+}
+extern "C" int sw_moe_validate(const SwMoeDesc *d, const SwMoeLayer *L, const void *x, const void *out) {
+    if (sw_validate(d, L)) return -1;
+    return sw_validate_rows(x, out, x, "validate");
+}
+
+static int sw_check(const SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, int T) {
+    if (!c) return sw_fail("null argument");
+    if (sw_validate(d, L)) return -1;
+    if (T < 0 || T > c->maxT) return sw_fail("T=%d outside [0,%d]", T, c->maxT);
+    if (d->n_experts > c->maxE) return sw_fail("n_experts=%d outside (0,%d]", d->n_experts, c->maxE);
+    if (d->topk > c->maxK) return sw_fail("topk=%d invalid", d->topk);
+    if (L->D > c->maxD) return sw_fail("D=%d must be a multiple of 32 and <= %d", L->D, c->maxD);
+    if (L->I > c->maxI) return sw_fail("I=%d must be a multiple of 32 and <= %d", L->I, c->maxI);
+    if (d->shared_mode != SW_SHARED_NONE && L->SI > c->maxSI) return sw_fail("SI=%d must be a multiple of 8 and <= %d", L->SI, c->maxSI);
+    // the context's device becomes current (a host may drive several GPUs from one thread)
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != c->dev) {
+        cudaGetLastError();
+        if (cudaSetDevice(c->dev) != cudaSuccess) return sw_cuda_fail(cudaGetLastError(), "cudaSetDevice");
+    }
     return 0;
 }
 
@@ -206,26 +296,15 @@ static void sw_resident(const SwMoeDesc *d, const SwMoeLayer *L, int *lo, int *c
 // [max_rows, I] (f32 or packed, same size); slots: [max_rows, D] f32.
 // Expert path: 2 = TMA-staged tensor-core kernels (default when the driver exports the
 // tensor-map encoder), 1 = cp.async tensor-core kernels, 0 = CUDA-core f32 kernels.
-// SW_EXPERT_PATH=tma|mma|simt overrides.
-// 3 = tcgen05/TMEM grouped GEMM, chosen when groups average SW_UMMA_MIN_ROWS (12) rows or more.
+// SW_EXPERT_PATH=tma|mma|simt|umma overrides.
+// 3 = tcgen05/TMEM grouped GEMM, chosen when groups average SW_UMMA_MIN_ROWS (16) rows or more.
 static int sw_expert_path(int D, int I, int rows, int groups) {
-    static int pref = -1, umma_min = 16;            // mean rows per group from which the tcgen05 kernels win (measured)
-    if (pref < 0) {
-        const char *e = getenv("SW_EXPERT_PATH");
-        pref = 2;
-        if (e && !strcmp(e, "umma")) pref = 3;
-        if (e && !strcmp(e, "tma")) pref = 4;            // TMA decode kernels whatever the group size
-        if (e && !strcmp(e, "mma")) pref = 1;
-        if (e && !strcmp(e, "simt")) pref = 0;
-        const char *f = getenv("SW_FORCE_SIMT");
-        if (f && *f && *f != '0') pref = 0;
-        const char *m = getenv("SW_UMMA_MIN_ROWS");
-        if (m) umma_min = atoi(m);
-    }
+    const SwTuning &t = sw_tuning();
+    const int pref = t.expert_pref;
     if (pref == 0 || D % 128 || I % 128) return 0;
     if (pref == 1 || !sw_tma_available()) return 1;
     if (pref == 4) return 2;
-    if (pref == 3 || (groups > 0 && rows >= (long long)umma_min * groups)) return 3;
+    if (pref == 3 || (groups > 0 && rows >= (long long)t.umma_min_rows * groups)) return 3;
     return 2;
 }
 
@@ -242,8 +321,10 @@ static int sw_resolve_path(const SwQ4Args &a, const void *gu_q, const void *dn_q
 static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, const float *gu_s,
                           const void *dn_q, const float *dn_s, const float *x, int rows_x, void *xp,
                           float *glu, float *slots, float *sums, int *status, int D, int I,
-                          void (*mark)(void *, int), void *mark_ctx, const SwUmmaScratch *um = nullptr, bool x_packed = false) {
+                          void (*mark)(void *, int), void *mark_ctx, const SwUmmaScratch *um = nullptr, bool x_packed = false,
+                          int *path_out = nullptr) {
     const int path = sw_resolve_path(a, gu_q, dn_q, D, I, um);
+    if (path_out) *path_out = path;
     if (path == 3) {
         // tcgen05 path: gather + split the token rows in packed-slot order, build the chunk list, two grouped GEMMs
         const long long nexp = a.expert_cnt > 4096 ? 4096 : a.expert_cnt;
@@ -269,7 +350,7 @@ static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, 
         int parts;
         if (path == 2) {
             int mt = (long long)a.max_groups * ((I + 63) / 64) >= (long long)cfg.num_sms * 4 ? 2 : 1;
-            { const char *e = getenv("SW_TMA_MT"); if (e && (atoi(e) == 1 || atoi(e) == 2)) mt = atoi(e); }
+            if (sw_tuning().tma_mt) mt = sw_tuning().tma_mt;
             SwMmaIO io{xp, xsum, 1, glu, ypart};
             if (sw_launch_q4_tma(cfg, a, io, status, nexp * 2 * I, true, mt)) return -1;
             parts = sw_q4_tma_parts(I, mt);
@@ -284,7 +365,7 @@ static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, 
         SwMmaIO io2{glu, ypart, parts, slots, nullptr};
         if (path == 2) {
             int mt = (long long)a.max_groups * ((D + 127) / 128) >= (long long)cfg.num_sms * 4 ? 2 : 1;
-            { const char *e = getenv("SW_TMA_MT"); if (e && (atoi(e) == 1 || atoi(e) == 2)) mt = atoi(e); }
+            if (sw_tuning().tma_mt) mt = sw_tuning().tma_mt;
             if (sw_launch_q4_tma(cfg, a, io2, status, nexp * D, false, mt)) return -1;
         } else {
             if (sw_launch_q4_mma(cfg, a, io2, false, sw_q4_mma_mt(cfg, a, false))) return -1;
@@ -310,8 +391,7 @@ static int sw_logits_topk(SwMoeCtx *c, const SwLaunchCfg &cfg, const SwMoeDesc *
     const bool fuse = (long long)T * K <= 4096;
     const SwRouting *dr = fuse ? &c->r : nullptr;
     unsigned *ticket = fuse ? (unsigned *)(c->r.status + 16) : nullptr;
-    static int force_simt = -1;
-    if (force_simt < 0) { const char *e = getenv("SW_FORCE_SIMT"); force_simt = (e && *e && *e != '0') ? 1 : 0; }
+    const int force_simt = sw_tuning().force_simt;
     if (!force_simt && L->D % 32 == 0) {
         const int KS = sw_router_slices(c->num_sms, T, L->D, E);
         if (sw_launch_router_dmma(cfg, x, L->router_w, L->router_dtype, c->rpart, T, L->D, E, KS)) return sw_fail("router launch failed");
@@ -330,7 +410,7 @@ static int sw_logits_topk(SwMoeCtx *c, const SwLaunchCfg &cfg, const SwMoeDesc *
 }
 
 static int sw_route_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, int T, cudaStream_t st) {
-    SwLaunchCfg cfg{c->num_sms, st};
+    SwLaunchCfg cfg{c->num_sms, st, c->dev};
     const int E = d->n_experts, K = d->topk;
     if (sw_logits_topk(c, cfg, d, L, x, T, false)) return -1;      // the top-k kernel's last CTA also runs the dispatch
     c->last_stream = st; c->lastT = T; c->lastK = K; c->lastE = E;
@@ -338,14 +418,14 @@ static int sw_route_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, c
 }
 
 static int sw_expert_stage(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, int T, cudaStream_t st) {
-    SwLaunchCfg cfg{c->num_sms, st};
+    SwLaunchCfg cfg{c->num_sms, st, c->dev};
     int lo, cnt; sw_resident(d, L, &lo, &cnt);
     const int K = d->topk, E = d->n_experts;
     SwQ4Args a{};
     a.gexp = c->r.gexp; a.gbeg = c->r.gbeg; a.gcnt = c->r.gcnt; a.G = c->r.G; a.grow = c->r.grow;
     a.expert_lo = lo; a.expert_cnt = cnt;
     a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K; a.gs = L->gs;
-    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, nullptr, nullptr, &c->um))
+    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, nullptr, nullptr, &c->um, false, &c->last_path))
         return sw_fail("expert launch failed");
     return 0;
 }
@@ -355,8 +435,7 @@ static int sw_expert_stage(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
 // the packed (or f32) intermediate.
 static int sw_shared_run(const SwLaunchCfg &cfg, const SwMoeLayer *L, const float *x, int T, void *pk, float *sglu, float *spart,
                          float **so, int *so_slices, void (*mark)(void *, int), void *mark_ctx, int *status = nullptr) {
-    static int force_simt = -1;
-    if (force_simt < 0) { const char *e = getenv("SW_FORCE_SIMT"); force_simt = (e && *e && *e != '0') ? 1 : 0; }
+    const int force_simt = sw_tuning().force_simt;
     if (!force_simt && T >= 128 && L->D % 64 == 0 && L->SI % 64 == 0 && sw_umma_available() && status) {
         // many rows: dense tcgen05 GEMMs; pk holds the planar bf16 hi|lo copy of x, sglu the planar hi|lo SiLU*up rows
         __nv_bfloat16 *xh = (__nv_bfloat16 *)pk, *xl = xh + (size_t)T * L->D;
@@ -392,34 +471,40 @@ static int sw_shared_run(const SwLaunchCfg &cfg, const SwMoeLayer *L, const floa
 }
 
 static int sw_shared_stage(SwMoeCtx *c, const SwMoeLayer *L, const float *x, int T, cudaStream_t st, float **so, int *so_slices) {
-    SwLaunchCfg cfg{c->num_sms, st};
+    SwLaunchCfg cfg{c->num_sms, st, c->dev};
     if (sw_shared_run(cfg, L, x, T, c->spk, c->sglu, c->so, so, so_slices, nullptr, nullptr, c->r.status)) return sw_fail("shared expert launch failed");
     return 0;
 }
 
 extern "C" int sw_moe_route(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, int T, void *stream) {
+    SW_GATE();
     if (sw_check(c, d, L, T)) return -1;
     if (T == 0) return 0;
+    if (sw_validate_rows(x, x, x, "route")) return -1;
     cudaStream_t st = (cudaStream_t)stream;
     return sw_route_impl(c, d, L, x, T, st);
 }
 
 extern "C" int sw_moe_experts(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, float *routed, int T, void *stream) {
+    SW_GATE();
     if (sw_check(c, d, L, T)) return -1;
     if (T == 0) return 0;
+    if (sw_validate_rows(x, routed, x, "experts")) return -1;
     if (c->lastT != T || c->lastK != d->topk || c->lastE != d->n_experts) return sw_fail("experts: no matching sw_moe_route before this call");
     cudaStream_t st = (cudaStream_t)stream;
     if (sw_expert_stage(c, d, L, x, T, st)) return -1;
-    SwLaunchCfg cfg{c->num_sms, st};
+    SwLaunchCfg cfg{c->num_sms, st, c->dev};
     int lo, cnt; sw_resident(d, L, &lo, &cnt);
     if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, nullptr, 0, routed, T, d->topk, L->D, 1.f, 0, lo, cnt)) return sw_fail("combine launch failed");
     return 0;
 }
 
 extern "C" int sw_moe_shared(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, int T, void *stream) {
+    SW_GATE();
     if (sw_check(c, d, L, T)) return -1;
     c->shared_T = -1;
     if (T == 0 || d->shared_mode == SW_SHARED_NONE) return 0;
+    if (sw_validate_rows(x, x, x, "shared")) return -1;
     float *so = nullptr; int so_slices = 1;
     if (sw_shared_stage(c, L, x, T, (cudaStream_t)stream, &so, &so_slices)) return -1;
     c->shared_T = T; c->shared_so = so; c->shared_slices = so_slices;
@@ -427,10 +512,12 @@ extern "C" int sw_moe_shared(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *
 }
 
 extern "C" int sw_moe_finish(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, const float *routed, float *out, int T, void *stream) {
+    SW_GATE();
     if (sw_check(c, d, L, T)) return -1;
     if (T == 0) return 0;
+    if (sw_validate_rows(x, routed, out, "finish")) return -1;
     cudaStream_t st = (cudaStream_t)stream;
-    SwLaunchCfg cfg{c->num_sms, st};
+    SwLaunchCfg cfg{c->num_sms, st, c->dev};
     const int has_shared = d->shared_mode != SW_SHARED_NONE;
     float *so = nullptr; int so_slices = 1;
     if (has_shared && c->shared_T == T) { so = c->shared_so; so_slices = c->shared_slices; c->shared_T = -1; }   // left by sw_moe_shared
@@ -443,14 +530,16 @@ extern "C" int sw_moe_finish(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *
 static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, float *out, int T, void *stream, bool accumulate);
 
 extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, float *out, int T, void *stream) {
+    SW_GATE();
     return sw_forward_impl(c, d, L, x, out, T, stream, true);
 }
 
 static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, float *out, int T, void *stream, bool accumulate) {
     if (sw_check(c, d, L, T)) return -1;
     if (T == 0) return 0;
+    if (sw_validate_rows(x, out, x, "forward")) return -1;
     cudaStream_t st = (cudaStream_t)stream;
-    SwLaunchCfg cfg{c->num_sms, st};
+    SwLaunchCfg cfg{c->num_sms, st, c->dev};
     const int E = d->n_experts, K = d->topk;
     int lo, cnt; sw_resident(d, L, &lo, &cnt);
     const int has_shared = d->shared_mode != SW_SHARED_NONE;
@@ -470,7 +559,7 @@ static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
     const int path = sw_resolve_path(a, L->gu_q, L->dn_q, L->D, L->I, &c->um);
     const bool prepack = !c->prof_on && (path == 1 || path == 2);
     if (overlap || prepack) {
-        SwLaunchCfg acfg{c->num_sms, c->aux};
+        SwLaunchCfg acfg{c->num_sms, c->aux, c->dev};
         SW_CUDA(cudaEventRecord(c->ev_fork, st));
         SW_CUDA(cudaStreamWaitEvent(c->aux, c->ev_fork, 0));
         if (prepack) {
@@ -479,7 +568,7 @@ static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
         }
     }
     if (overlap) {
-        SwLaunchCfg acfg{c->num_sms, c->aux};
+        SwLaunchCfg acfg{c->num_sms, c->aux, c->dev};
         if (sw_shared_run(acfg, L, x, T, c->spk, c->sglu, c->so, &so, &so_slices, nullptr, nullptr, c->r.status)) return sw_fail("shared expert launch failed");
         SW_CUDA(cudaEventRecord(c->ev_join, c->aux));
     }
@@ -491,7 +580,7 @@ static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
 
     auto mark = [](void *p, int which) { MarkCtx *m = (MarkCtx *)p; sw_prof_mark(m->c, which == 0 ? SW_ST_GATEUP : SW_ST_DOWN, m->st); };
     if (prepack) SW_CUDA(cudaStreamWaitEvent(st, c->ev_pack, 0));
-    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, mark, &mc, &c->um, prepack))
+    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, mark, &mc, &c->um, prepack, &c->last_path))
         return sw_fail("expert launch failed");
     if (overlap) {
         SW_CUDA(cudaStreamWaitEvent(st, c->ev_join, 0));
@@ -517,6 +606,7 @@ static bool sw_host_pinned(const void *p) {
 }
 
 extern "C" int sw_moe_forward_host(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x_host, float *out_host, int T) {
+    SW_GATE();
     if (sw_check(c, d, L, T)) return -1;
     if (T == 0) return 0;
     if (!x_host || !out_host) return sw_fail("forward_host: null buffer");
@@ -567,10 +657,10 @@ extern "C" int sw_moe_graph_create(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeL
     SW_CUDA(cudaStreamSynchronize(c->stream));
     cudaGraph_t graph = nullptr;
     if (cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { c->prof_on = prof; return sw_cuda_fail(cudaGetLastError(), "cudaStreamBeginCapture"); }
-    const long long l0 = g_launches;
+    const long long l0 = g_launches.load();
     const int rc = sw_moe_forward(c, d, L, x, out, T, c->stream);
-    const int kernels = (int)(g_launches - l0);
-    g_launches = l0;                                   // captured, not launched
+    const int kernels = (int)(g_launches.load() - l0);
+    g_launches.store(l0);                                   // captured, not launched
     cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
     c->prof_on = prof;
     if (rc || e != cudaSuccess || !graph) { cudaGetLastError(); if (graph) cudaGraphDestroy(graph); return rc ? -1 : sw_fail("graph capture failed: %s", cudaGetErrorString(e)); }
@@ -591,7 +681,7 @@ extern "C" int sw_moe_capture_begin(SwMoeCtx *c) {
     if (c->cap_on) return sw_fail("capture_begin: a capture is already open");
     SW_CUDA(cudaStreamSynchronize(c->stream));
     if (cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) return sw_cuda_fail(cudaGetLastError(), "cudaStreamBeginCapture");
-    c->cap_on = 1; c->cap_prof = c->prof_on; c->prof_on = 0; c->cap_l0 = g_launches;
+    c->cap_on = 1; c->cap_prof = c->prof_on; c->prof_on = 0; c->cap_l0 = g_launches.load();
     return 0;
 }
 
@@ -599,8 +689,8 @@ extern "C" int sw_moe_capture_end(SwMoeCtx *c, SwMoeGraph **gout) {
     if (!c || !gout) return sw_fail("capture_end: null argument");
     *gout = nullptr;
     if (!c->cap_on) return sw_fail("capture_end: no capture open");
-    const int kernels = (int)(g_launches - c->cap_l0);
-    g_launches = c->cap_l0;                            // captured, not launched
+    const int kernels = (int)(g_launches.load() - c->cap_l0);
+    g_launches.store(c->cap_l0);                            // captured, not launched
     c->cap_on = 0; c->prof_on = c->cap_prof;
     cudaGraph_t graph = nullptr;
     const cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
@@ -613,6 +703,7 @@ extern "C" int sw_moe_capture_end(SwMoeCtx *c, SwMoeGraph **gout) {
 
 extern "C" int sw_moe_graph_launch(SwMoeGraph *g, void *stream) {
     if (!g) return sw_fail("graph_launch: null graph");
+    SW_GATE();
     SW_CUDA(cudaGraphLaunch(g->exec, (cudaStream_t)stream));
     g->ctx->last_stream = (cudaStream_t)stream; g->ctx->lastT = g->T; g->ctx->lastK = g->K; g->ctx->lastE = g->E;
     sw_count_launch(g->kernels);
@@ -649,6 +740,40 @@ extern "C" int sw_moe_status(SwMoeCtx *c) {
     if (c->last_stream) cudaStreamSynchronize(c->last_stream);
     if (cudaMemcpy(&s, c->r.status, 4, cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return -1; }
     return s;
+}
+
+// Expert kernels of the last sw_moe_experts / sw_moe_forward call of this context:
+// 0 CUDA cores (k_q4_group), 1 mma.sync + cp.async (k_q4_mma), 2 mma.sync + TMA (k_q4_tma), 3 tcgen05 + TMEM (k_q4_umma); -1 before the first call.
+extern "C" int sw_moe_last_path(SwMoeCtx *c) { return c ? c->last_path : -1; }
+
+// Runs a one-CTA kernel whose bounded wait cannot succeed (limit = `iters` polls of a barrier nobody arrives at),
+// clears the status word first, and returns the status bits afterwards: SW_ST_TIMEOUT (4) when the give-up path
+// worked.  The context stays usable.
+extern "C" int sw_moe_test_wait_timeout(SwMoeCtx *c, int iters) {
+    if (!c || iters <= 0 || iters > (1 << 20)) return sw_fail("test_wait_timeout: bad argument");
+    SwLaunchCfg cfg{c->num_sms, c->stream, c->dev};
+    SW_CUDA(cudaMemsetAsync(c->r.status, 0, 4, c->stream));
+    if (sw_launch_wait_runs_out(cfg, c->r.status, (unsigned)iters)) return sw_fail("test kernel launch failed");
+    int st = 0;
+    SW_CUDA(cudaMemcpyAsync(&st, c->r.status, 4, cudaMemcpyDeviceToHost, c->stream));
+    SW_CUDA(cudaStreamSynchronize(c->stream));
+    SW_CUDA(cudaMemsetAsync(c->r.status, 0, 4, c->stream));
+    SW_CUDA(cudaStreamSynchronize(c->stream));
+    return st;
+}
+
+// Host-only self-test of the per-device set-up slots and of the tensor-map cache keying (no device needed).
+int sw_selftest_map_cache();
+extern "C" int sw_selftest_host(void) {
+    SwPerDevice slots{};
+    int runs = 0;
+    auto init7 = [&] { runs++; return 7; };
+    if (slots.get(0, init7) != 7 || slots.get(0, init7) != 7 || runs != 1) return 101;       // device 0: set up once
+    if (slots.get(1, [&] { runs++; return 9; }) != 9 || runs != 2) return 102;              // device 1 does its own set-up
+    if (slots.get(0, init7) != 7 || runs != 2) return 103;
+    if (slots.get(2, [&] { runs++; return -1; }) > 0 || slots.get(2, [&] { runs++; return 3; }) != 3 || runs != 4) return 104;   // a failure is not cached
+    if (slots.get(SW_MAX_DEVICES, init7) > 0 || slots.get(-1, init7) > 0) return 105;
+    return sw_selftest_map_cache();
 }
 
 extern "C" int sw_moe_profile(SwMoeCtx *c, int enable) {
@@ -691,6 +816,8 @@ static struct {
 } g_lag;
 
 extern "C" int lag_cuda_init(int dev) {
+    if (dev < 0 || dev >= SW_MAX_DEVICES) return -1;
+    sw_tuning();
     cudaSetDeviceFlags(cudaDeviceScheduleSpin);   // many short blocking calls per token (c/backend_cuda_laguna.cu:17-21)
     cudaGetLastError();
     if (cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); return -1; }
@@ -715,7 +842,7 @@ extern "C" size_t lag_cuda_total_bytes(void) {
 }
 extern "C" void *lag_cuda_upload(const void *h, size_t n) {
     void *d = nullptr;
-    if (cudaMalloc(&d, n ? n : 1) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (sw_malloc(&d, n ? n : 1) != cudaSuccess) { cudaGetLastError(); return nullptr; }
     if (n && cudaMemcpy(d, h, n, cudaMemcpyHostToDevice) != cudaSuccess) { cudaGetLastError(); cudaFree(d); return nullptr; }
     return d;
 }
@@ -735,15 +862,17 @@ static int lag_roundtrip(float *y, const float *x, size_t xn, size_t yn, F body)
 }
 
 extern "C" int lag_cuda_matmul_bf16(float *y, const float *x, const void *W, int S, int I, int O) {
+    if (sw_fault_injected()) return -1;
     if (!g_lag.ok || S <= 0 || I <= 0 || O <= 0 || (I & 7)) return -1;
-    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st};
+    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st, g_lag.dev};
     return lag_roundtrip(y, x, (size_t)S * I * 4, (size_t)S * O * 4, [&] {
         return sw_launch_bf16_rows(cfg, (const float *)g_lag.dx.p, W, (float *)g_lag.dy.p, S, I, O);
     });
 }
 extern "C" int lag_cuda_matmul_q8(float *y, const float *x, const void *W, int S, int I, int O) {
+    if (sw_fault_injected()) return -1;
     if (!g_lag.ok || S <= 0 || I <= 0 || O <= 0) return -1;
-    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st};
+    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st, g_lag.dev};
     const int8_t *q8 = (const int8_t *)W;
     const float *scale = (const float *)(q8 + (size_t)I * O);
     return lag_roundtrip(y, x, (size_t)S * I * 4, (size_t)S * O * 4, [&] {
@@ -782,13 +911,14 @@ static int lag_group_core(float *acc, const float *x, const void *gu_q, const fl
                           const void *dn_q, const float *dn_s,
                           const int *gexp, const int *gbeg, const int *gcnt, int G,
                           const int *grow, const int *rowof, const float *w, int S, int K, int I, int D) {
+    if (sw_fault_injected()) return -1;
     if (!g_lag.ok || S <= 0 || K <= 0 || G <= 0 || (D % 32) || (I % 32)) return -1;
     const int P = S * K;
     if (g_lag.dglu.ensure((size_t)P * I * 4) || g_lag.dslot.ensure((size_t)P * D * 4) || g_lag.dxp.ensure((size_t)S * D * 4) ||
         g_lag.dsums.ensure(((size_t)S + 64 + (size_t)P * (I / 8 + 1)) * 4)) return -1;
     LagIdx ix;
     if (lag_stage_idx(&ix, gexp, gbeg, gcnt, G, grow, rowof, w, P)) return -1;
-    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st};
+    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st, g_lag.dev};
     return lag_roundtrip(acc, x, (size_t)S * D * 4, (size_t)S * D * 4, [&] {
         SwQ4Args a{};
         a.gexp = ix.gexp; a.gbeg = ix.gbeg; a.gcnt = ix.gcnt; a.G = ix.G; a.grow = ix.grow;
@@ -830,8 +960,9 @@ extern "C" int lag_cuda_expert_q4(float *out, const float *x, const void *p13, c
 
 // fp4 pair (c/backend_cuda_laguna.h:83-99): same conventions as the int4 calls.
 extern "C" int lag_cuda_matmul_fp4(float *y, const float *x, const void *packed, const void *es, int S, int I, int O) {
+    if (sw_fault_injected()) return -1;
     if (!g_lag.ok || S <= 0 || O <= 0 || I <= 0 || (I & 31)) return -1;          // scale blocks are 32 wide
-    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st};
+    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st, g_lag.dev};
     return lag_roundtrip(y, x, (size_t)S * I * 4, (size_t)S * O * 4, [&] {
         return sw_launch_fp4_rows(cfg, (const float *)g_lag.dx.p, packed, es, (float *)g_lag.dy.p, S, I, O);
     });
@@ -840,13 +971,14 @@ extern "C" int lag_cuda_matmul_fp4(float *y, const float *x, const void *packed,
 extern "C" int lag_cuda_moe_experts_fp4(float *out, const float *x, const void *gu_q, const void *gu_es,
                                         const void *dn_q, const void *dn_es, const int *sel, const float *w, int K,
                                         int I, int D, float limit) {
+    if (sw_fault_injected()) return -1;
     if (!g_lag.ok || K < 0 || K > 4096 || I <= 0 || D <= 0 || (D & 31) || (I & 31)) return -1;
     if (K > 0 && (!sel || !w)) return -1;
     const size_t ib = (size_t)(K > 0 ? K : 1) * 8;                                // sel [K] int32, then w [K] f32
     if (g_lag.didx.ensure(ib) || g_lag.hidx.ensure(ib) || g_lag.dglu.ensure((size_t)(K + 1) * I * 4) ||
         g_lag.dslot.ensure((size_t)(K + 1) * D * 4)) return -1;
     if (K > 0) { memcpy(g_lag.hidx.p, sel, (size_t)K * 4); memcpy((char *)g_lag.hidx.p + (size_t)K * 4, w, (size_t)K * 4); }
-    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st};
+    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st, g_lag.dev};
     return lag_roundtrip(out, x, (size_t)D * 4, (size_t)D * 4, [&] {
         if (K > 0 && cudaMemcpyAsync(g_lag.didx.p, g_lag.hidx.p, (size_t)K * 8, cudaMemcpyHostToDevice, g_lag.st) != cudaSuccess) { cudaGetLastError(); return -1; }
         const int *dsel = (const int *)g_lag.didx.p;
@@ -857,6 +989,7 @@ extern "C" int lag_cuda_moe_experts_fp4(float *out, const float *x, const void *
 }
 
 extern "C" int lag_cuda_matmul_q4(float *y, const float *x, const void *packed, const void *scale, int S, int I, int O) {
+    if (sw_fault_injected()) return -1;
     if (!g_lag.ok || S <= 0 || O <= 0 || I <= 0 || (I % 32)) return -1;
     // a single group of S packed rows through the row-output form of the grouped kernel
     if (g_lag.dmisc.ensure(256 * 4)) return -1;
@@ -865,7 +998,7 @@ extern "C" int lag_cuda_matmul_q4(float *y, const float *x, const void *packed, 
     if (cudaMemcpyAsync(g_lag.dmisc.p, h, sizeof h, cudaMemcpyHostToDevice, g_lag.st) != cudaSuccess) { cudaGetLastError(); return -1; }
     if (cudaStreamSynchronize(g_lag.st) != cudaSuccess) { cudaGetLastError(); return -1; }   // h is a stack buffer
     int *dm = (int *)g_lag.dmisc.p;
-    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st};
+    SwLaunchCfg cfg{g_lag.num_sms, g_lag.st, g_lag.dev};
     return lag_roundtrip(y, x, (size_t)S * I * 4, (size_t)S * O * 4, [&] {
         SwQ4Args a{};
         a.G = dm; a.gexp = dm + 64; a.gbeg = dm + 65; a.gcnt = dm + 66; a.grow = nullptr;

@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <atomic>
+#include <mutex>
 
 #define SW_FULL_MASK 0xffffffffu
 #define SW_MAX_EXPERTS 1024     // top-k keeps <= 32 scores per lane
@@ -12,6 +14,7 @@
 #define SW_ST_BAD_EXPERT 1
 #define SW_ST_BAD_ROW    2
 #define SW_ST_TIMEOUT    4     // a bounded device-side wait ran out
+#define SW_ST_RANGE      8     // an activation left the fp16 range of the tensor-core paths and was clamped to +-65504
 
 // Routing + dispatch arrays of one block call (device pointers).  Names follow
 // the reference's host arrays (c/laguna.c:709-723).
@@ -29,7 +32,42 @@ struct SwRouting {
 struct SwLaunchCfg {
     int num_sms;
     cudaStream_t stream;
+    int dev;           // CUDA device the stream belongs to (function attributes and occupancy are kept per device)
 };
+
+// Set-up results that CUDA keeps per device (opt-in to large shared memory, resident CTAs per SM): one slot per
+// device, filled once under a process-wide mutex, so a second context on another GPU does its own set-up.
+#define SW_MAX_DEVICES 64
+std::mutex &sw_setup_mutex();
+struct SwPerDevice {
+    std::atomic<int> v[SW_MAX_DEVICES];
+    // The cached value of `dev` (> 0).  `init` computes it the first time and returns > 0, or <= 0 on failure,
+    // which is returned uncached so that the next call tries again.
+    template <typename F> int get(int dev, F init) {
+        if (dev < 0 || dev >= SW_MAX_DEVICES) return -1;
+        int cur = v[dev].load(std::memory_order_acquire);
+        if (cur > 0) return cur;
+        std::lock_guard<std::mutex> g(sw_setup_mutex());
+        cur = v[dev].load(std::memory_order_relaxed);
+        if (cur > 0) return cur;
+        cur = init();
+        if (cur > 0) v[dev].store(cur, std::memory_order_release);
+        return cur;
+    }
+};
+
+// Tuning knobs (SW_* environment variables), read once per process -- when the first context is created or
+// lag_cuda_init runs -- never on the call path.
+struct SwTuning {
+    int expert_pref;     // SW_EXPERT_PATH: 2 default, 3 umma, 4 tma always, 1 mma, 0 simt
+    int umma_min_rows;   // SW_UMMA_MIN_ROWS: mean rows per group from which the tcgen05 kernels are used
+    int force_simt;      // SW_FORCE_SIMT
+    int tma_mt;          // SW_TMA_MT: 0 = choose, 1 or 2
+    int tma_p;           // SW_TMA_P: ring depth of the TMA decode kernels (0 = default)
+    int mma_mt;          // SW_MMA_MT
+    int fail_after;      // SW_FAIL_AFTER: > 0 makes the n-th and later device allocations of this library fail (host-side failure injection)
+};
+const SwTuning &sw_tuning();
 
 void sw_count_launch(int n = 1);
 
@@ -75,6 +113,7 @@ int sw_launch_q4_mma(const SwLaunchCfg &c, const SwQ4Args &a, const SwMmaIO &io,
 bool sw_tma_available();
 int sw_q4_tma_parts(int OUT, int mt);
 int sw_launch_q4_tma(const SwLaunchCfg &c, const SwQ4Args &a, const SwMmaIO &io, int *status, long long rows_total, bool gateup, int mt);
+int sw_launch_wait_runs_out(const SwLaunchCfg &c, int *status, unsigned limit);
 // sw_umma.cu: tcgen05/TMEM grouped GEMM for groups with many rows
 bool sw_umma_available();
 int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow, int P, int KD, void *hi, void *lo);

@@ -181,11 +181,11 @@ static int sw_launch_q4(const SwLaunchCfg &c, const SwQ4Args &a) {
     if (smem > 220 * 1024) return -1;
     if (a.gs < 0 || (a.gs > 0 && a.gs % 32)) return -1;
     auto kern = a.gs > 0 ? k_q4_group<GATEUP, NC, true> : k_q4_group<GATEUP, NC, false>;
-    static size_t attr_smem[2] = {0, 0};
-    if (smem > attr_smem[a.gs > 0]) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -1;
-        attr_smem[a.gs > 0] = smem;
-    }
+    // the opt-in covers the largest size this kernel can be given here (220 KB), set once per device
+    static SwPerDevice attr[2];
+    if (attr[a.gs > 0].get(c.dev, [&] {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess) { cudaGetLastError(); return -1; }
+            return 1; }) <= 0) return -1;
     // rows per work item: enough items to fill the machine a few times over, but
     // never below one pass of the 8 warps.
     const int pass = GATEUP ? 16 : 32;

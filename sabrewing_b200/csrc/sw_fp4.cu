@@ -133,12 +133,11 @@ static int sw_fp4_launch(const SwLaunchCfg &c, bool glu, const void *P, const vo
     if (Z <= 0 || O <= 0) return 0;
     if (I <= 0 || (I % 32) || (((uintptr_t)P) & 15) || ((I / 2) % 16)) return -1;
     const size_t smem = 0;
-    static bool attr_done = false;
-    if (!attr_done) {
-        if (cudaFuncSetAttribute(k_fp4_rows<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
-            cudaFuncSetAttribute(k_fp4_rows<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return -1;
-        attr_done = true;
-    }
+    static SwPerDevice attr_done;
+    if (attr_done.get(c.dev, [] {
+            if (cudaFuncSetAttribute(k_fp4_rows<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+                cudaFuncSetAttribute(k_fp4_rows<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) { cudaGetLastError(); return -1; }
+            return 1; }) <= 0) return -1;
     const int per_cta = SW_FP4_WARPS * (glu ? SW_FP4_RW(true) : SW_FP4_RW(false));
     dim3 grid((unsigned)((O + per_cta - 1) / per_cta), (unsigned)Z);
     if (glu) k_fp4_rows<true><<<grid, SW_FP4_WARPS * 32, smem, c.stream>>>((const uint8_t *)P, (const uint8_t *)ES, sel, rows_per_expert, X, x_stride, Y, y_stride, I, O, limit);

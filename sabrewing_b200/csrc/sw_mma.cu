@@ -362,15 +362,15 @@ k_q4_mma(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
 
 template <bool GATEUP, int MT, int P>
 static int sw_launch_q4_mma_t(const SwLaunchCfg &c, const SwQ4Args &a, const SwMmaIO &io) {
-    static int ctas_per_sm = 0;                       // resident CTAs of this instantiation
+    static SwPerDevice per_dev;                       // resident CTAs per SM of this instantiation, per device
     constexpr int SMEM = P * 2 * MT * 128 * 16;
     auto kern = k_q4_mma<GATEUP, MT, P>;
-    if (ctas_per_sm == 0) {
+    const int ctas_per_sm = per_dev.get(c.dev, [&] {
+        int n = 0;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, kern, 128, SMEM) != cudaSuccess || ctas_per_sm < 1) {
-            cudaGetLastError(); ctas_per_sm = 1;
-        }
-    }
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, 128, SMEM) != cudaSuccess || n < 1) { cudaGetLastError(); n = 1; }
+        return n; });
+    if (ctas_per_sm <= 0) return -1;
     long long grid = (long long)c.num_sms * ctas_per_sm;
     constexpr int OPI = MT * (GATEUP ? 8 : 16);
     long long items = (long long)a.max_groups * ((a.OUT + OPI - 1) / OPI);
@@ -386,8 +386,7 @@ static int sw_launch_q4_mma_t(const SwLaunchCfg &c, const SwQ4Args &a, const SwM
 // m-tiles per warp item for a launch: few groups (single-row decode) want small
 // items so that every SM gets work; SW_MMA_MT=1|2|4 overrides the choice (tuning knob).
 int sw_q4_mma_mt(const SwLaunchCfg &c, const SwQ4Args &a, bool gateup) {
-    static int mt_env = -1;
-    if (mt_env < 0) { const char *e = getenv("SW_MMA_MT"); mt_env = e ? atoi(e) : 0; }
+    const int mt_env = sw_tuning().mma_mt;
     if (mt_env == 1 || mt_env == 2 || mt_env == 4) return mt_env;
     const int opi4 = gateup ? 32 : 64;
     const long long items4 = (long long)a.max_groups * ((a.OUT + opi4 - 1) / opi4);
@@ -591,12 +590,11 @@ int sw_launch_bf16_mma(const SwLaunchCfg &c, const void *W0, const void *W1, con
     if (KD % 32 || KS < 1) return -1;
     constexpr int P = 8;
     constexpr int SMEM = P * 2 * 128 * 16;
-    static bool attr = false;
-    if (!attr) {
-        if (cudaFuncSetAttribute(k_bf16_mma<true, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(k_bf16_mma<false, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
-        attr = true;
-    }
+    static SwPerDevice attr;
+    if (attr.get(c.dev, [] {
+            if (cudaFuncSetAttribute(k_bf16_mma<true, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+                cudaFuncSetAttribute(k_bf16_mma<false, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
+            return 1; }) <= 0) return -1;
     const int mblocks = (O + (gateup ? 8 : 16) - 1) / (gateup ? 8 : 16);
     const int slice = ((KD + KS - 1) / KS + 31) & ~31;
     long long items = (long long)mblocks * KS, need = (items + 3) / 4;

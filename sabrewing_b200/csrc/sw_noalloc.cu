@@ -14,7 +14,9 @@
 // the contraction into the fixed array, takes a ticket from a counter in the same
 // array, and the CTA that draws the last ticket sums the partials in slice order,
 // applies the gate and selects the top-k.  The arithmetic and the order of the
-// partial sums are those of sw_moe_route, so both give the same ids and weights.
+// partial sums are those of sw_moe_route, so both give the same ids; the combine
+// weights agree to the last place or one unit of it (the softmax denominator is
+// reduced over 128 threads here and over 256 there).
 //
 // Limits (rejected with an error text, nothing is launched): T <= 8 rows,
 // n_experts <= 512, D <= 8192 and D % 32 == 0.
@@ -27,7 +29,10 @@
 //
 // The first call on a device looks up the device address of the array
 // (cudaGetSymbolAddress) and queries the SM count; make that first call outside
-// any stream capture.
+// any stream capture.  Make it at start-up too: CUDA loads a module lazily, so the
+// 2.1 MB are reserved when this first call touches the module, not when the
+// library is loaded -- a host that gives all device memory away before its first
+// call finds no room left for the array and gets -1.
 #include "sw_common.cuh"
 #pragma GCC visibility push(default)
 #include "../../include/sabrewing_b200.h"
@@ -191,14 +196,23 @@ extern "C" int sw_moe_route_static(const SwMoeDesc *d, const SwMoeLayer *L, cons
     if (L->D <= 0 || L->D > SW_STATIC_MAX_D || L->D % 32) return sw_noalloc_fail("route_static: D must be a multiple of 32 and <= 8192");
     if (d->topk <= 0 || d->topk > SW_MAX_TOPK || d->topk > d->n_experts) return sw_noalloc_fail("route_static: bad topk");
     if (d->route_act < 0 || d->route_act > 2 || !L->router_w) return sw_noalloc_fail("route_static: bad route_act or missing router weights");
+    if (L->router_dtype != SW_DTYPE_F32 && L->router_dtype != SW_DTYPE_BF16) return sw_noalloc_fail("route_static: unknown router_dtype");
+    // x and the router rows are read with 128-bit loads
+    if (((uintptr_t)x | (uintptr_t)L->router_w) & 15) return sw_noalloc_fail("route_static: x and router_w must be 16-byte aligned");
+    if (((uintptr_t)sel | (uintptr_t)w | (uintptr_t)L->corr_bias | (uintptr_t)L->logit_bias) & 3) return sw_noalloc_fail("route_static: sel, w and the bias arrays must be 4-byte aligned");
     if (T == 0) return 0;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return sw_noalloc_fail("route_static: no current device"); }
-    if (!g_static_dev[dev].ptr) {
-        void *p = nullptr; int sms = 0;
-        if (cudaGetSymbolAddress(&p, sw_static_scratch) != cudaSuccess || !p) { cudaGetLastError(); return sw_noalloc_fail("route_static: cudaGetSymbolAddress failed"); }
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) { cudaGetLastError(); return sw_noalloc_fail("route_static: cannot query the device"); }
-        g_static_dev[dev].ptr = p; g_static_dev[dev].sms = sms;
+    {
+        // first call on this device: look the array's device address up (under the set-up mutex, so that two
+        // threads making their first call at once both see a complete entry)
+        std::lock_guard<std::mutex> g(sw_setup_mutex());
+        if (!g_static_dev[dev].ptr) {
+            void *p = nullptr; int sms = 0;
+            if (cudaGetSymbolAddress(&p, sw_static_scratch) != cudaSuccess || !p) { cudaGetLastError(); return sw_noalloc_fail("route_static: cudaGetSymbolAddress failed"); }
+            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) { cudaGetLastError(); return sw_noalloc_fail("route_static: cannot query the device"); }
+            g_static_dev[dev].sms = sms; g_static_dev[dev].ptr = p;
+        }
     }
     const int E = d->n_experts;
     const int KS = sw_router_slices(g_static_dev[dev].sms, T, L->D, E);      // same slicing as sw_moe_route

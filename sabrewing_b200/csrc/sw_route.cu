@@ -439,11 +439,10 @@ int sw_launch_route_topk(const SwLaunchCfg &c, float *scores, const double *part
                          const SwRouting *dr, unsigned *ticket) {
     if (T <= 0) return 0;
     if (E > SW_MAX_EXPERTS || K > SW_MAX_TOPK || K > E || K <= 0) return -1;
-    static bool attr_done = false;
-    if (!attr_done) {
-        if (cudaFuncSetAttribute(k_route_topk, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024) != cudaSuccess) return -1;
-        attr_done = true;
-    }
+    static SwPerDevice attr_done;
+    if (attr_done.get(c.dev, [] {
+            if (cudaFuncSetAttribute(k_route_topk, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024) != cudaSuccess) { cudaGetLastError(); return -1; }
+            return 1; }) <= 0) return -1;
     SwRouting none{};
     const bool fuse = dr && ticket;
     size_t smem = fuse ? (size_t)(256 / 32 + 2) * E * sizeof(int) : 0;
@@ -467,11 +466,10 @@ int sw_launch_dispatch(const SwLaunchCfg &c, const SwRouting &r, int T, int K, i
     if (T <= 0) return 0;
     if (E > SW_MAX_EXPERTS) return -1;
     size_t smem = (size_t)(SW_DISPATCH_THREADS / 32 + 2) * E * sizeof(int);
-    static bool attr_done = false;
-    if (!attr_done) {
-        if (cudaFuncSetAttribute(k_dispatch, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess) return -1;
-        attr_done = true;
-    }
+    static SwPerDevice attr_done;
+    if (attr_done.get(c.dev, [] {
+            if (cudaFuncSetAttribute(k_dispatch, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess) { cudaGetLastError(); return -1; }
+            return 1; }) <= 0) return -1;
     k_dispatch<<<1, SW_DISPATCH_THREADS, smem, c.stream>>>(r.sel, T * K, K, E, T, r.G, r.gexp, r.gbeg, r.gcnt,
                                                           r.grow, r.rowof, r.status);
     sw_count_launch();

@@ -38,8 +38,8 @@ __device__ __forceinline__ void sw_mbar_arrive(unsigned bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
 }
 // bounded wait: false when the limit ran out
-__device__ __forceinline__ bool sw_mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag) {
-    for (unsigned it = 0; it < SW_WAIT_LIMIT; it++) {
+__device__ __forceinline__ bool sw_mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag, unsigned limit = SW_WAIT_LIMIT) {
+    for (unsigned it = 0; it < limit; it++) {
         unsigned ok;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
@@ -383,6 +383,26 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
     }
 }
 
+// A wait that must run out: one CTA waits `limit` iterations on a barrier nobody arrives at, then reports through the
+// status word exactly as the expert kernels do (SW_ST_TIMEOUT, clean return).  Exercises the give-up path of
+// sw_mbar_wait without faulting or hanging anything.
+__global__ void k_wait_runs_out(int *status, unsigned limit) {
+    __shared__ unsigned long long bar;
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) {
+        sw_mbar_init(sw_smem_u32(&bar), 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !sw_mbar_wait(sw_smem_u32(&bar), 0, &s_abort, limit)) atomicOr(status, SW_ST_TIMEOUT);
+}
+int sw_launch_wait_runs_out(const SwLaunchCfg &c, int *status, unsigned limit) {
+    k_wait_runs_out<<<1, 32, 0, c.stream>>>(status, limit);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
 // ---------------------------------------------------------------------------
 // Host side: tensor maps (cached per weight blob) and launch.
 // ---------------------------------------------------------------------------
@@ -390,43 +410,76 @@ typedef CUresult (*sw_encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t,
                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 static sw_encode_fn sw_get_encode() {
-    static sw_encode_fn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
+    // looked up once (thread-safe static initialisation); NULL when the driver does not export the encoder
+    static const sw_encode_fn fn = [] {
         void *p = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = (sw_encode_fn)p;
-        else cudaGetLastError();
-    }
+            return (sw_encode_fn)p;
+        cudaGetLastError();
+        return (sw_encode_fn)nullptr;
+    }();
     return fn;
 }
 
-struct SwMapKey { const void *ptr; int rowbytes, boxrows; long long rows; };
+// Cache of encoded tensor maps, keyed by (device, blob pointer, row bytes, rows, box rows).  Guarded by a mutex
+// and handed out BY VALUE: an entry may be recycled by another thread while a launch still uses its copy.
+struct SwMapKey { int dev; const void *ptr; int rowbytes, boxrows; long long rows; };
 struct SwMapEntry { SwMapKey k; CUtensorMap m; };
 static SwMapEntry g_maps[64];
 static int g_nmaps = 0, g_map_next = 0;
+static std::mutex g_maps_mu;
 
-static const CUtensorMap *sw_get_map(const void *ptr, int rowbytes, long long rows, int boxrows) {
-    for (int i = 0; i < g_nmaps; i++) {
-        const SwMapKey &k = g_maps[i].k;
-        if (k.ptr == ptr && k.rowbytes == rowbytes && k.boxrows == boxrows && k.rows == rows) return &g_maps[i].m;
-    }
-    sw_encode_fn enc = sw_get_encode();
-    if (!enc) return nullptr;
-    int slot = g_nmaps < 64 ? g_nmaps++ : (g_map_next++ % 64);
+static bool sw_key_eq(const SwMapKey &a, const SwMapKey &b) {
+    return a.dev == b.dev && a.ptr == b.ptr && a.rowbytes == b.rowbytes && a.boxrows == b.boxrows && a.rows == b.rows;
+}
+
+// enc: the driver's cuTensorMapEncodeTiled (or a stand-in of the host self-test)
+static int sw_get_map_with(sw_encode_fn enc, int dev, const void *ptr, int rowbytes, long long rows, int boxrows, CUtensorMap *out) {
+    const SwMapKey key{dev, ptr, rowbytes, boxrows, rows};
+    std::lock_guard<std::mutex> g(g_maps_mu);
+    for (int i = 0; i < g_nmaps; i++)
+        if (sw_key_eq(g_maps[i].k, key)) { *out = g_maps[i].m; return 0; }
+    if (!enc) return -1;
+    CUtensorMap m;
     cuuint64_t dims[2] = {(cuuint64_t)rowbytes, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)rowbytes};
     cuuint32_t box[2] = {128, (cuuint32_t)boxrows};
     cuuint32_t estr[2] = {1, 1};
-    if (enc(&g_maps[slot].m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
-        if (slot == g_nmaps - 1) g_nmaps--;
-        return nullptr;
-    }
-    g_maps[slot].k = SwMapKey{ptr, rowbytes, boxrows, rows};
-    return &g_maps[slot].m;
+    if (enc(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return -1;
+    const int slot = g_nmaps < 64 ? g_nmaps++ : (g_map_next++ % 64);
+    g_maps[slot].k = key; g_maps[slot].m = m;
+    *out = m;
+    return 0;
+}
+
+// Host-only check of the cache keying (no device needed): a stand-in encoder counts its calls and stamps the map
+// with them.  Returns 0 when every lookup behaved, else the number of the failed check.
+static int g_fake_calls = 0;
+static CUresult sw_fake_encode(CUtensorMap *m, CUtensorMapDataType, cuuint32_t, void *ptr, const cuuint64_t *, const cuuint64_t *,
+                               const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill) {
+    memset(m, 0, sizeof *m); g_fake_calls++;
+    memcpy(m, &g_fake_calls, sizeof g_fake_calls); memcpy((char *)m + 8, &ptr, sizeof ptr);
+    return CUDA_SUCCESS;
+}
+int sw_selftest_map_cache() {
+    { std::lock_guard<std::mutex> g(g_maps_mu); g_nmaps = 0; g_map_next = 0; }
+    g_fake_calls = 0;
+    CUtensorMap a, b, c2;
+    char blob[4];
+    if (sw_get_map_with(sw_fake_encode, 0, blob, 2048, 100, 64, &a) || g_fake_calls != 1) return 1;
+    if (sw_get_map_with(sw_fake_encode, 0, blob, 2048, 100, 64, &b) || g_fake_calls != 1 || memcmp(&a, &b, sizeof a)) return 2;   // hit
+    if (sw_get_map_with(sw_fake_encode, 1, blob, 2048, 100, 64, &c2) || g_fake_calls != 2) return 3;                              // other device: miss
+    if (sw_get_map_with(sw_fake_encode, 0, blob, 2048, 100, 128, &c2) || g_fake_calls != 3) return 4;                             // other box: miss
+    if (sw_get_map_with(sw_fake_encode, 0, blob + 1, 2048, 100, 64, &c2) || g_fake_calls != 4) return 5;                         // other blob: miss
+    for (int i = 0; i < 80; i++) if (sw_get_map_with(sw_fake_encode, 2, blob, 2048, 1000 + i, 64, &c2)) return 6;                 // more entries than slots: recycled
+    if (sw_get_map_with(sw_fake_encode, 2, blob, 2048, 1079, 64, &b) || g_fake_calls != 84) return 7;                             // the newest is still there
+    if (sw_get_map_with(nullptr, 3, blob, 2048, 1, 64, &b) == 0) return 8;                                                        // no encoder: a miss fails
+    { std::lock_guard<std::mutex> g(g_maps_mu); g_nmaps = 0; g_map_next = 0; }
+    return 0;
 }
 
 template <bool GATEUP, int MT, int P>
@@ -436,14 +489,16 @@ static int sw_launch_q4_tma_t(const SwLaunchCfg &c, const SwQ4Args &a, const SwM
     constexpr int SMEM = P * STAGE_BYTES + 1024;
     constexpr int OPI = GATEUP ? 32 * MT : 64 * MT;
     constexpr int BOXROWS = GATEUP ? 32 * MT : (MT == 4 ? 128 : 64 * MT);
-    static int ctas_per_sm = 0;
+    static SwPerDevice per_dev;                       // resident CTAs per SM of this instantiation, per device
     auto kern = k_q4_tma<GATEUP, MT, P>;
-    if (ctas_per_sm == 0) {
+    const int ctas_per_sm = per_dev.get(c.dev, [&] {
+        int n = 0;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, kern, 160, SMEM) != cudaSuccess || ctas_per_sm < 1) { cudaGetLastError(); ctas_per_sm = 1; }
-    }
-    const CUtensorMap *tm = sw_get_map(a.q, a.KD / 2, rows_total, BOXROWS);
-    if (!tm) return -1;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, 160, SMEM) != cudaSuccess || n < 1) { cudaGetLastError(); n = 1; }
+        return n; });
+    if (ctas_per_sm <= 0) return -1;
+    CUtensorMap tm;
+    if (sw_get_map_with(sw_get_encode(), c.dev, a.q, a.KD / 2, rows_total, BOXROWS, &tm)) return -1;
     SwTmaArgs ka;
     ka.Ws = a.s; ka.XP = (const unsigned char *)io.XP; ka.xsum = io.xsum; ka.xsum_parts = io.xsum_parts;
     ka.Yout = io.Y; ka.ypart = io.ypart; ka.gexp = a.gexp; ka.gbeg = a.gbeg; ka.gcnt = a.gcnt; ka.Gp = a.G; ka.grow = a.grow;
@@ -452,7 +507,7 @@ static int sw_launch_q4_tma_t(const SwLaunchCfg &c, const SwQ4Args &a, const SwM
     long long grid = (long long)c.num_sms * ctas_per_sm;
     if (grid > items) grid = items;
     if (grid < 1) grid = 1;
-    kern<<<(unsigned)grid, 160, SMEM, c.stream>>>(*tm, ka);
+    kern<<<(unsigned)grid, 160, SMEM, c.stream>>>(tm, ka);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
@@ -466,8 +521,7 @@ bool sw_tma_available() { return sw_get_encode() != nullptr; }
 int sw_launch_q4_tma(const SwLaunchCfg &c, const SwQ4Args &a, const SwMmaIO &io, int *status, long long rows_total, bool gateup, int mt) {
     if (a.max_groups <= 0 || a.max_rows <= 0) return 0;
     if (a.KD % 128 || a.OUT <= 0 || ((uintptr_t)a.q & 15)) return -1;
-    static int p_env = -1;                  // SW_TMA_P=2|3|4|6: ring depth (tuning knob)
-    if (p_env < 0) { const char *e = getenv("SW_TMA_P"); p_env = e ? atoi(e) : 0; }
+    const int p_env = sw_tuning().tma_p;     // SW_TMA_P=2|3|4|6: ring depth (tuning knob)
     const int P = p_env ? p_env : 2;          // shallow rings, more resident CTAs: measured best on B200
 #define SW_TMA_CASE(G, M, PP) if (mt == M && P == PP) return sw_launch_q4_tma_t<G, M, PP>(c, a, io, status, rows_total)
     if (gateup) {

@@ -412,12 +412,15 @@ typedef CUresult (*um_encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t,
                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 static um_encode_fn um_get_encode() {
-    static um_encode_fn fn = nullptr; static bool tried = false;
-    if (!tried) {
-        tried = true; void *p = nullptr; cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = (um_encode_fn)p;
-        else cudaGetLastError();
-    }
+    // looked up once (thread-safe static initialisation); NULL when the driver does not export the encoder
+    static const um_encode_fn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            return (um_encode_fn)p;
+        cudaGetLastError();
+        return (um_encode_fn)nullptr;
+    }();
     return fn;
 }
 static int um_make_map(CUtensorMap *m, CUtensorMapDataType dt, int esize, const void *ptr, long long inner, long long rows,
@@ -466,12 +469,11 @@ int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_h
         if (um_make_map(&tl[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act_lo, a.KD, a.max_rows, 64, R[i], CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
     }
     constexpr int SMEM = UM_STAGES * UM_STAGE_BYTES + UM_ABUF * UM_A16 + 1024;
-    static bool attr = false;
-    if (!attr) {
-        if (cudaFuncSetAttribute(k_q4_umma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(k_q4_umma<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
-        attr = true;
-    }
+    static SwPerDevice attr;
+    if (attr.get(c.dev, [] {
+            if (cudaFuncSetAttribute(k_q4_umma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+                cudaFuncSetAttribute(k_q4_umma<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
+            return 1; }) <= 0) return -1;
     UmArgs ka;
     ka.Ws = a.s; ka.Y0 = Y0; ka.Y1 = Y1; ka.gexp = a.gexp; ka.gbeg = a.gbeg; ka.gcnt = a.gcnt; ka.nchunks = nchunks;
     ka.chunks = (const int2 *)chunks; ka.status = status; ka.KD = a.KD; ka.OUT = a.OUT; ka.expert_lo = a.expert_lo;
@@ -685,12 +687,11 @@ int sw_launch_bf16_umma(const SwLaunchCfg &c, const void *W0, const void *W1, co
     if (um_make_map(&th, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, act_hi, KD, T, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
     if (um_make_map(&tl, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, act_lo, KD, T, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
     constexpr int SMEM = UB_STAGES * UB_STAGE_BYTES + 1024;
-    static bool attr = false;
-    if (!attr) {
-        if (cudaFuncSetAttribute(k_bf16_umma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(k_bf16_umma<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
-        attr = true;
-    }
+    static SwPerDevice attr;
+    if (attr.get(c.dev, [] {
+            if (cudaFuncSetAttribute(k_bf16_umma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+                cudaFuncSetAttribute(k_bf16_umma<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
+            return 1; }) <= 0) return -1;
     UbArgs ka{Y0, Y1, T, KD, O, status};
     const int opt = gateup ? 64 : 128;
     long long items = (long long)((O + opt - 1) / opt) * ((T + 127) / 128);

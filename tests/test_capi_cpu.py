@@ -56,3 +56,44 @@ def test_missing_library_is_a_loud_error(monkeypatch, tmp_path):
     monkeypatch.setattr(capi, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         capi.lib()
+
+
+def test_host_selftest_of_per_device_setup_and_map_cache():
+    """Function attributes / occupancy are cached per device and the tensor-map cache is keyed by device too."""
+    from sabrewing_b200 import capi
+    assert capi.lib().sw_selftest_host() == 0
+
+
+def _layer(**kw):
+    from sabrewing_b200 import capi
+    base = dict(D=128, I=64, SI=0, router_dtype=capi.DTYPE_BF16, router_w=0x1000, corr_bias=None, logit_bias=None,
+                gu_q=0x2000, gu_s=0x3000, dn_q=0x4000, dn_s=0x5000, sh_gate=None, sh_up=None, sh_down=None,
+                expert_lo=0, expert_cnt=0, gs=0)
+    base.update(kw)
+    return capi.SwMoeLayer(*[base[f[0]] for f in capi.SwMoeLayer._fields_])
+
+
+def test_validate_refuses_null_and_misaligned_buffers_without_a_device():
+    """Return codes only: nothing is launched (the pointers are never dereferenced)."""
+    from sabrewing_b200 import capi
+    l = capi.lib()
+    d = capi.SwMoeDesc(8, 2, 0, 0, 0, 1.0, 0)
+    ok = _layer()
+    assert l.sw_moe_validate(C.byref(d), C.byref(ok), 0x10000, 0x20000) == 0
+    assert l.sw_moe_validate(C.byref(d), C.byref(ok), None, 0x20000) == -1 and "null" in capi.last_error()
+    assert l.sw_moe_validate(C.byref(d), C.byref(ok), 0x10004, 0x20000) == -1 and "16-byte" in capi.last_error()   # a column-offset view
+    assert l.sw_moe_validate(C.byref(d), C.byref(ok), 0x10000, 0x20008) == -1
+    bad = _layer(router_w=0x1008)
+    assert l.sw_moe_validate(C.byref(d), C.byref(bad), 0x10000, 0x20000) == -1 and "aligned" in capi.last_error()
+    bad = _layer(gu_s=0x3004)
+    assert l.sw_moe_validate(C.byref(d), C.byref(bad), 0x10000, 0x20000) == -1
+    bad = _layer(dn_q=None)
+    assert l.sw_moe_validate(C.byref(d), C.byref(bad), 0x10000, 0x20000) == -1 and "missing" in capi.last_error()
+    d2 = capi.SwMoeDesc(8, 2, 0, 0, 0, 1.0, 1)           # shared expert asked for, weights absent
+    assert l.sw_moe_validate(C.byref(d2), C.byref(_layer(SI=64)), 0x10000, 0x20000) == -1
+    # the allocation-free routing entry checks its buffers before it touches CUDA
+    sel = 0x30000
+    assert l.sw_moe_route_static(C.byref(d), C.byref(ok), 0x10004, 2, sel, sel, None) == -1 and "16-byte" in capi.last_error()
+    assert l.sw_moe_route_static(C.byref(d), C.byref(_layer(router_w=0x1002)), 0x10000, 2, sel, sel, None) == -1
+    assert l.sw_moe_route_static(C.byref(d), C.byref(ok), 0x10000, 2, 0x30002, sel, None) == -1
+    assert l.sw_moe_route_static(C.byref(d), C.byref(ok), None, 2, sel, sel, None) == -1 and "null" in capi.last_error()

@@ -35,12 +35,15 @@ def check_routing(got, want):
     assert werr.max() < W_TOL, werr.max()
 
 
-def run_case(case, orc, ref_out=None):
+def run_case(case, orc, ref_out=None, path=None):
     blk, layer, desc = make_block(case)
     x = torch.from_numpy(case.x).cuda(); out = torch.from_numpy(case.hin).cuda()
+    assert blk.lib.sw_moe_last_path(blk.ctx) == -1
     blk.forward(desc, layer, x, out)
     torch.cuda.synchronize()
     assert blk.status() == 0
+    if path is not None:                  # the expert kernels that ran: 0 CUDA cores, 1 mma.sync, 2 TMA, 3 tcgen05
+        assert blk.lib.sw_moe_last_path(blk.ctx) == path
     want = orc.moe_group(case.host, case.x, case.hin, exact=1)
     check_routing(blk.routing(), want)
     err = rel_l2(out.cpu().numpy() - case.hin, want["out"] - case.hin)
@@ -89,7 +92,7 @@ def test_large_groups_take_the_tensor_memory_path(orc, base, kw, T):
     """Groups averaging >= 16 rows (with I % 128 == 0 and D % 256 == 0) run the tcgen05/TMEM grouped GEMM; same parity bars."""
     case = synth_case(base, corr_bias_std=0.01, T=T, **kw)
     assert T * case.cfg.K >= 16 * case.cfg.E and case.cfg.I % 128 == 0 and case.cfg.D % 256 == 0
-    run_case(case, orc)
+    run_case(case, orc, path=3)
 
 
 @pytest.mark.parametrize("gs,kw", [(64, dict(D=256, I=128, SI=64, E=16, K=4)), (128, dict(D=512, I=256, SI=64, E=16, K=4)),
@@ -97,7 +100,7 @@ def test_large_groups_take_the_tensor_memory_path(orc, base, kw, T):
 def test_group_scaled_int4(orc, gs, kw):
     """One scale per gs columns (the reference's fmt=4 container, c/quant.h:167-202), checked against the CPU checker."""
     case = synth_case("c2", corr_bias_std=0.01, T=21, gs=gs, **kw)
-    run_case(case, orc)
+    run_case(case, orc, path=0)
 
 
 def test_graph_replay_matches_eager(orc):
@@ -399,3 +402,134 @@ def test_stage_capture_replays_like_eager(orc):
     assert rel_l2(out.cpu().numpy(), want.cpu().numpy()) < 1e-6
     check_routing(blk.routing(), orc.moe_group(case.host, case.x, None, exact=1))
     g.close(); blk.close()
+
+
+def test_small_groups_take_the_tma_path_and_odd_widths_the_cuda_cores(orc):
+    """Path proof for the decode kernels: widths that are multiples of 128 run k_q4_tma (2); others k_q4_group (0)."""
+    run_case(synth_case("c2", corr_bias_std=0.01, T=8, D=512, E=32, K=4, I=128, SI=128), orc, path=2)
+    run_case(synth_case("c2", corr_bias_std=0.01, T=8, D=384, E=12, K=3, I=96, SI=64), orc, path=0)
+
+
+def test_misaligned_blob_falls_back_to_the_cp_async_kernels(orc):
+    """An int4 blob that is not 16-byte aligned cannot sit under a TMA tensor map: the mma.sync + cp.async kernels
+    (path 1) take over, same results."""
+    from sabrewing_b200.moe_block import MoeBlock, MoeLayer, desc_from_config
+    case = synth_case("c2", corr_bias_std=0.01, T=8, D=512, E=32, K=4, I=128, SI=128)
+    cfg = case.cfg
+    blk = MoeBlock("cuda:0", 8, cfg.E, cfg.K, cfg.D, cfg.I, cfg.SI)
+    layer = MoeLayer(cfg.D, cfg.I, cfg.SI, case.a, "cuda:0")
+    pad = torch.empty(layer.gu_q.numel() + 16, dtype=torch.uint8, device="cuda")     # same bytes, 8 bytes off alignment
+    off = (8 - pad.data_ptr() % 16) % 16
+    shifted = pad[off:off + layer.gu_q.numel()].view(layer.gu_q.shape); shifted.copy_(layer.gu_q)
+    layer.gu_q = shifted
+    assert layer.gu_q.data_ptr() % 16 == 8
+    x = torch.from_numpy(case.x).cuda(); out = torch.from_numpy(case.hin).cuda()
+    blk.forward(desc_from_config(cfg), layer, x, out)
+    torch.cuda.synchronize()
+    assert blk.lib.sw_moe_last_path(blk.ctx) == 1 and blk.status() == 0
+    want = orc.moe_group(case.host, case.x, case.hin, exact=1)
+    check_routing(blk.routing(), want)
+    assert rel_l2(out.cpu().numpy() - case.hin, want["out"] - case.hin) < OUT_TOL
+    blk.close()
+
+
+def test_bad_row_pointers_are_refused_before_any_launch():
+    """NULL or a column-offset view (not 16-byte aligned) comes back as -1 with a text, not as a device fault."""
+    from sabrewing_b200 import capi
+    case = synth_case("c2", D=256, E=8, K=2, I=128, SI=128, T=4)
+    blk, layer, desc = make_block(case)
+    d, l = desc.c(), layer.c()
+    buf = torch.zeros(4 * 256 + 8, device="cuda")
+    good, off = buf.data_ptr(), buf.data_ptr() + 4
+    out = torch.zeros(4 * 256, device="cuda")
+    l0 = blk.lib.sw_launch_count()
+    assert blk.lib.sw_moe_forward(blk.ctx, C.byref(d), C.byref(l), off, out.data_ptr(), 4, None) == -1
+    assert "16-byte" in capi.last_error()
+    assert blk.lib.sw_moe_forward(blk.ctx, C.byref(d), C.byref(l), good, None, 4, None) == -1
+    assert "null" in capi.last_error()
+    assert blk.lib.sw_moe_route(blk.ctx, C.byref(d), C.byref(l), off, 4, None) == -1
+    assert blk.lib.sw_launch_count() == l0                                   # nothing was launched
+    assert blk.lib.sw_moe_forward(blk.ctx, C.byref(d), C.byref(l), good, out.data_ptr(), 4, None) == 0   # and the context still works
+    torch.cuda.synchronize()
+    blk.close()
+
+
+def test_injected_failures_are_clean_errors(orc):
+    """Host-side failure injection.  Compute calls: the reference's COLI_GPU_FAIL_AFTER hook and its test
+    (c/backend_cuda.cu:684-692, c/tests/test_backend_cuda.cu:93-98): on -> the call reports failure, off -> the same call
+    works.  Allocations: the n-th allocation fails, the call returns its error code, what was created so far is released."""
+    from sabrewing_b200 import capi
+    lib = capi.lib()
+    case = synth_case("c2", D=256, E=8, K=2, I=128, SI=128, T=4)
+    blk, layer, desc = make_block(case)
+    x = torch.from_numpy(case.x).cuda(); out = torch.from_numpy(case.hin).cuda()
+    try:
+        lib.sw_test_fail_after(0)                                   # every compute call fails
+        with pytest.raises(RuntimeError, match="injected"):
+            blk.forward(desc, layer, x, out)
+        y = np.zeros((1, 8), np.float32)
+        assert lib.lag_cuda_matmul_q4(y.ctypes.data, y.ctypes.data, None, None, 1, 64, 8) == -1
+        lib.sw_test_fail_after(2)                                   # two calls succeed, the third fails
+        blk.route(desc, layer, x); blk.route(desc, layer, x)
+        with pytest.raises(RuntimeError, match="injected"):
+            blk.route(desc, layer, x)
+    finally:
+        lib.sw_test_fail_after(-1)
+    blk.forward(desc, layer, x, out)                                # off: healthy call right after
+    torch.cuda.synchronize()
+    want = orc.moe_group(case.host, case.x, case.hin, exact=1)
+    assert rel_l2(out.cpu().numpy() - case.hin, want["out"] - case.hin) < OUT_TOL
+    blk.close()
+
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    try:
+        for n in (1, 2, 3):                 # device block, first and second page-locked staging buffer
+            lib.sw_test_fail_alloc(n)
+            ctx = C.c_void_p()
+            assert lib.sw_moe_ctx_create(C.byref(ctx), 0, 64, 32, 4, 1024, 256, 256) == -1
+            assert not ctx.value and "failed" in capi.last_error()
+        lib.sw_test_fail_alloc(1)
+        blob = np.zeros(64, np.uint8)
+        assert lib.lag_cuda_upload(blob.ctypes.data, blob.nbytes) is None       # NULL on failure, like the reference
+    finally:
+        lib.sw_test_fail_alloc(0)
+    ctx = C.c_void_p()
+    assert lib.sw_moe_ctx_create(C.byref(ctx), 0, 64, 32, 4, 1024, 256, 256) == 0
+    lib.sw_moe_ctx_destroy(ctx)
+    torch.cuda.synchronize()
+    assert abs(torch.cuda.mem_get_info()[0] - free0) < (64 << 20)            # the failed creations leaked no device memory
+
+
+def test_a_bounded_wait_that_runs_out_reports_and_returns(orc):
+    """The give-up path of the kernels' mbarrier waits: a barrier nobody arrives at, a limit of a few thousand polls,
+    SW_ST_TIMEOUT in the status word, a clean return, and the context computes correctly afterwards."""
+    case = synth_case("c2", D=256, E=8, K=2, I=128, SI=128, T=4)
+    blk, layer, desc = make_block(case)
+    assert blk.lib.sw_moe_test_wait_timeout(blk.ctx, 4096) == 4
+    assert blk.status() == 0                                                  # cleared again by the test entry
+    x = torch.from_numpy(case.x).cuda(); out = torch.from_numpy(case.hin).cuda()
+    blk.forward(desc, layer, x, out)
+    torch.cuda.synchronize()
+    want = orc.moe_group(case.host, case.x, case.hin, exact=1)
+    assert rel_l2(out.cpu().numpy() - case.hin, want["out"] - case.hin) < OUT_TOL
+    blk.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
+def test_two_devices_in_one_process(orc):
+    """Function attributes and occupancy are per device: a second context on another GPU sets its own."""
+    from sabrewing_b200.moe_block import MoeBlock, MoeLayer, desc_from_config
+    case = synth_case("c3", corr_bias_std=0.01, T=300, D=512, I=256, SI=128, E=16, K=4)      # tcgen05 path: ~200 KB of shared memory
+    cfg = case.cfg
+    want = orc.moe_group(case.host, case.x, case.hin, exact=1)
+    for dev in ("cuda:0", "cuda:1"):
+        blk = MoeBlock(dev, 300, cfg.E, cfg.K, cfg.D, cfg.I, cfg.SI)
+        layer = MoeLayer(cfg.D, cfg.I, cfg.SI, case.a, dev)
+        x = torch.from_numpy(case.x).to(dev); out = torch.from_numpy(case.hin).to(dev)
+        with torch.cuda.device(dev):
+            blk.forward(desc_from_config(cfg), layer, x, out)
+            torch.cuda.synchronize(dev)
+        assert blk.status() == 0 and blk.lib.sw_moe_last_path(blk.ctx) == 3
+        assert rel_l2(out.cpu().numpy() - case.hin, want["out"] - case.hin) < OUT_TOL
+        blk.close()
