@@ -210,6 +210,19 @@ int  sw_moe_get_routing(SwMoeCtx *ctx, int *sel, float *w, float *scores, int *G
  * to +-65504 (the result is then not the reference's; the reference is f32
  * throughout, c/moe_quant.h:45-217). */
 int  sw_moe_status(SwMoeCtx *ctx);
+/* Context options.  SW_OPT_UMMA_TERMS: how the tcgen05 grouped GEMM (groups averaging >= 16
+ * rows: prefill, large batches) feeds f32 activations to the fp16 tensor cores.  2 = two
+ * fp16 terms, x = hi + lo, two MMAs per step: f32-level accuracy (measured ~1e-5 relative
+ * L2 on the 4096-token prefill).  1 = fp16(x) alone, half the tensor work: each activation
+ * is rounded to 11 significant bits, measured relative L2 of the block output against the
+ * reference's exact f32 path stated with the results (bar: 1e-3).  The decode kernels
+ * (small groups) always use both terms.
+ * SW_OPT_EXPERT_PATH: -1 (default) lets the library choose the expert kernels by shape
+ * and mean group size; 0..3 asks for one family (numbering of sw_moe_last_path), lowered
+ * when the shapes do not fit it.  For tests and measurements.
+ * 0 = ok, -1 = unknown option or value. */
+enum { SW_OPT_UMMA_TERMS = 1, SW_OPT_EXPERT_PATH = 2 };
+int  sw_moe_set_option(SwMoeCtx *ctx, int option, int value);
 /* Which expert kernels the last sw_moe_experts / sw_moe_forward of this context
  * used: 0 CUDA cores, 1 mma.sync + cp.async, 2 mma.sync + TMA, 3 tcgen05 + TMEM;
  * -1 before the first call.  For tests and benchmarks that must know the path. */

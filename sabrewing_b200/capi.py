@@ -12,6 +12,7 @@ LIB_PATH = os.path.join(_HERE, "libsabrewing_b200.so")
 ROUTE_SIGMOID, ROUTE_SOFTMAX, ROUTE_SOFTPLUS = 0, 1, 2
 SHARED_NONE, SHARED_UNSCALED = 0, 1
 DTYPE_F32, DTYPE_BF16 = 0, 1
+OPT_UMMA_TERMS, OPT_EXPERT_PATH = 1, 2
 
 
 class SwMoeDesc(C.Structure):
@@ -64,6 +65,7 @@ SIGNATURES = {
     "sw_moe_get_routing": (_i, [_vp, _vp, _vp, _vp, C.POINTER(_i), _vp, _vp, _vp, _vp, _vp]),
     "sw_moe_status": (_i, [_vp]),
     "sw_moe_last_path": (_i, [_vp]),
+    "sw_moe_set_option": (_i, [_vp, _i, _i]),
     "sw_moe_validate": (_i, [_pd, _pl, _vp, _vp]),
     "sw_test_fail_after": (None, [_i]),
     "sw_test_fail_alloc": (None, [_i]),

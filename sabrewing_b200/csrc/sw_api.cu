@@ -119,7 +119,8 @@ struct SwMoeCtx {
     float *sums = nullptr;       // row sums of x and partial row sums of the SiLU*up rows
     int lastT = 0, lastK = 0, lastE = 0;
     int last_path = -1;          // expert kernels of the last experts/forward call (sw_moe_last_path)
-    int umma_terms = 2;          // fp16 terms per activation on the tcgen05 path: 1 = hi only, 2 = hi + lo
+    int umma_terms = 2;
+    int forced_path = -1;        // SW_OPT_EXPERT_PATH: -1 = choose by shape and group size          // fp16 terms per activation on the tcgen05 path: 1 = hi only, 2 = hi + lo
     int cap_on = 0, cap_prof = 0; long long cap_l0 = 0;   // open stage capture (sw_moe_capture_begin)
     // a shared-expert result left by sw_moe_shared for the next sw_moe_finish of the same row count
     int shared_T = -1, shared_slices = 1; float *shared_so = nullptr;
@@ -251,9 +252,9 @@ static int sw_validate(const SwMoeDesc *d, const SwMoeLayer *L) {
     if (L->gs < 0 || (L->gs > 0 && L->gs % 32)) return sw_fail("gs=%d must be 0 or a multiple of 32", L->gs);
     if (!L->router_w || !L->gu_q || !L->gu_s || !L->dn_q || !L->dn_s) return sw_fail("layer weights missing");
     if (L->router_dtype != SW_DTYPE_F32 && L->router_dtype != SW_DTYPE_BF16) return sw_fail("router_dtype=%d unknown", L->router_dtype);
-    const uintptr_t al = (uintptr_t)L->router_w | (uintptr_t)L->gu_s | (uintptr_t)L->dn_s | (uintptr_t)L->sh_gate | (uintptr_t)L->sh_up |
+    const uintptr_t al = (uintptr_t)L->router_w | (uintptr_t)L->gu_q | (uintptr_t)L->dn_q | (uintptr_t)L->gu_s | (uintptr_t)L->dn_s | (uintptr_t)L->sh_gate | (uintptr_t)L->sh_up |
                          (uintptr_t)L->sh_down;
-    if (al & 15) return sw_fail("layer pointers must be 16-byte aligned (router_w, gu_s, dn_s, sh_*)");
+    if (al & 15) return sw_fail("layer pointers must be 16-byte aligned (router_w, gu_q, gu_s, dn_q, dn_s, sh_*)");
     if (((uintptr_t)L->corr_bias | (uintptr_t)L->logit_bias) & 3) return sw_fail("corr_bias / logit_bias must be 4-byte aligned");
     return 0;
 }
@@ -309,9 +310,15 @@ static int sw_expert_path(int D, int I, int rows, int groups) {
 }
 
 // Which expert kernels a call will use: 0 CUDA cores, 1 mma.sync + cp.async, 2 mma.sync + TMA, 3 tcgen05.
-static int sw_resolve_path(const SwQ4Args &a, const void *gu_q, const void *dn_q, int D, int I, const SwUmmaScratch *um) {
+// forced >= 0 (SW_OPT_EXPERT_PATH) asks for that family; it is still lowered when the shapes do not fit it.
+// Every family reads the blobs 16 bytes at a time: alignment is checked at the entry points, not here.
+static int sw_resolve_path(const SwQ4Args &a, int D, int I, const SwUmmaScratch *um, int forced = -1) {
     int path = a.gs > 0 ? 0 : sw_expert_path(D, I, a.max_rows, a.max_groups);   // group scales: CUDA-core kernels
-    if (path >= 2 && (((uintptr_t)gu_q | (uintptr_t)dn_q) & 15)) path = 1;    // TMA wants 16-byte aligned blobs
+    if (forced >= 0 && a.gs == 0) {
+        path = forced;
+        if (path > 0 && (D % 128 || I % 128)) path = 0;
+        if (path >= 2 && !sw_tma_available()) path = 1;
+    }
     if (path == 3 && (!um || I % 128 || D % 256)) path = 2;                   // the tcgen05 kernels walk whole tile pairs
     return path;
 }
@@ -322,8 +329,8 @@ static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, 
                           const void *dn_q, const float *dn_s, const float *x, int rows_x, void *xp,
                           float *glu, float *slots, float *sums, int *status, int D, int I,
                           void (*mark)(void *, int), void *mark_ctx, const SwUmmaScratch *um = nullptr, bool x_packed = false,
-                          int *path_out = nullptr) {
-    const int path = sw_resolve_path(a, gu_q, dn_q, D, I, um);
+                          int *path_out = nullptr, int umma_terms = 2, int forced_path = -1) {
+    const int path = sw_resolve_path(a, D, I, um, forced_path);
     if (path_out) *path_out = path;
     if (path == 3) {
         // tcgen05 path: gather + split the token rows in packed-slot order, build the chunk list, two grouped GEMMs
@@ -331,13 +338,13 @@ static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, 
         const int P = a.max_rows, max_chunks = P / 128 + a.max_groups;
         __half *xh = (__half *)um->xg, *xl = xh + (size_t)P * D;
         __half *gh = (__half *)glu, *gl = gh + (size_t)P * I;
-        if (sw_launch_umma_gather(cfg, x, a.grow, P, D, xh, xl)) return -1;
+        if (sw_launch_umma_gather(cfg, x, a.grow, P, D, xh, umma_terms == 2 ? xl : nullptr, status)) return -1;
         if (sw_launch_umma_chunks(cfg, a, um->nchunks, um->chunks)) return -1;
         a.q = (const uint8_t *)gu_q; a.s = gu_s; a.KD = D; a.OUT = I;
-        if (sw_launch_q4_umma(cfg, a, xh, xl, gh, gl, um->nchunks, um->chunks, max_chunks, status, nexp * 2 * I, true)) return -1;
+        if (sw_launch_q4_umma(cfg, a, xh, xl, gh, gl, um->nchunks, um->chunks, max_chunks, status, nexp * 2 * I, true, umma_terms)) return -1;
         if (mark) mark(mark_ctx, 0);
         a.q = (const uint8_t *)dn_q; a.s = dn_s; a.KD = I; a.OUT = D;
-        if (sw_launch_q4_umma(cfg, a, gh, gl, slots, nullptr, um->nchunks, um->chunks, max_chunks, status, nexp * D, false)) return -1;
+        if (sw_launch_q4_umma(cfg, a, gh, gl, slots, nullptr, um->nchunks, um->chunks, max_chunks, status, nexp * D, false, umma_terms)) return -1;
         if (mark) mark(mark_ctx, 1);
         return 0;
     }
@@ -425,7 +432,7 @@ static int sw_expert_stage(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
     a.gexp = c->r.gexp; a.gbeg = c->r.gbeg; a.gcnt = c->r.gcnt; a.G = c->r.G; a.grow = c->r.grow;
     a.expert_lo = lo; a.expert_cnt = cnt;
     a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K; a.gs = L->gs;
-    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, nullptr, nullptr, &c->um, false, &c->last_path))
+    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, nullptr, nullptr, &c->um, false, &c->last_path, c->umma_terms, c->forced_path))
         return sw_fail("expert launch failed");
     return 0;
 }
@@ -556,7 +563,7 @@ static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
     a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K; a.gs = L->gs;
     // Packing x for the mma.sync kernels depends only on x too: it goes first on the second stream, off the
     // router -> top-k -> experts chain.
-    const int path = sw_resolve_path(a, L->gu_q, L->dn_q, L->D, L->I, &c->um);
+    const int path = sw_resolve_path(a, L->D, L->I, &c->um, c->forced_path);
     const bool prepack = !c->prof_on && (path == 1 || path == 2);
     if (overlap || prepack) {
         SwLaunchCfg acfg{c->num_sms, c->aux, c->dev};
@@ -580,7 +587,7 @@ static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
 
     auto mark = [](void *p, int which) { MarkCtx *m = (MarkCtx *)p; sw_prof_mark(m->c, which == 0 ? SW_ST_GATEUP : SW_ST_DOWN, m->st); };
     if (prepack) SW_CUDA(cudaStreamWaitEvent(st, c->ev_pack, 0));
-    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, mark, &mc, &c->um, prepack, &c->last_path))
+    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, mark, &mc, &c->um, prepack, &c->last_path, c->umma_terms, c->forced_path))
         return sw_fail("expert launch failed");
     if (overlap) {
         SW_CUDA(cudaStreamWaitEvent(st, c->ev_join, 0));
@@ -746,6 +753,21 @@ extern "C" int sw_moe_status(SwMoeCtx *c) {
 // 0 CUDA cores (k_q4_group), 1 mma.sync + cp.async (k_q4_mma), 2 mma.sync + TMA (k_q4_tma), 3 tcgen05 + TMEM (k_q4_umma); -1 before the first call.
 extern "C" int sw_moe_last_path(SwMoeCtx *c) { return c ? c->last_path : -1; }
 
+extern "C" int sw_moe_set_option(SwMoeCtx *c, int option, int value) {
+    if (!c) return sw_fail("null ctx");
+    if (option == SW_OPT_UMMA_TERMS) {
+        if (value != 1 && value != 2) return sw_fail("set_option: SW_OPT_UMMA_TERMS takes 1 or 2");
+        c->umma_terms = value;
+        return 0;
+    }
+    if (option == SW_OPT_EXPERT_PATH) {
+        if (value < -1 || value > 3) return sw_fail("set_option: SW_OPT_EXPERT_PATH takes -1 (choose) or 0..3");
+        c->forced_path = value;
+        return 0;
+    }
+    return sw_fail("set_option: unknown option %d", option);
+}
+
 // Runs a one-CTA kernel whose bounded wait cannot succeed (limit = `iters` polls of a barrier nobody arrives at),
 // clears the status word first, and returns the status bits afterwards: SW_ST_TIMEOUT (4) when the give-up path
 // worked.  The context stays usable.
@@ -864,6 +886,7 @@ static int lag_roundtrip(float *y, const float *x, size_t xn, size_t yn, F body)
 extern "C" int lag_cuda_matmul_bf16(float *y, const float *x, const void *W, int S, int I, int O) {
     if (sw_fault_injected()) return -1;
     if (!g_lag.ok || S <= 0 || I <= 0 || O <= 0 || (I & 7)) return -1;
+    if (!y || !x || !W || ((uintptr_t)W & 15)) return -1;                     // weight rows are read 16 bytes at a time
     SwLaunchCfg cfg{g_lag.num_sms, g_lag.st, g_lag.dev};
     return lag_roundtrip(y, x, (size_t)S * I * 4, (size_t)S * O * 4, [&] {
         return sw_launch_bf16_rows(cfg, (const float *)g_lag.dx.p, W, (float *)g_lag.dy.p, S, I, O);
@@ -872,6 +895,7 @@ extern "C" int lag_cuda_matmul_bf16(float *y, const float *x, const void *W, int
 extern "C" int lag_cuda_matmul_q8(float *y, const float *x, const void *W, int S, int I, int O) {
     if (sw_fault_injected()) return -1;
     if (!g_lag.ok || S <= 0 || I <= 0 || O <= 0) return -1;
+    if (!y || !x || !W || (((uintptr_t)W + (size_t)I * O) & 3)) return -1;      // the f32 scales follow the int8 block
     SwLaunchCfg cfg{g_lag.num_sms, g_lag.st, g_lag.dev};
     const int8_t *q8 = (const int8_t *)W;
     const float *scale = (const float *)(q8 + (size_t)I * O);
@@ -913,6 +937,8 @@ static int lag_group_core(float *acc, const float *x, const void *gu_q, const fl
                           const int *grow, const int *rowof, const float *w, int S, int K, int I, int D) {
     if (sw_fault_injected()) return -1;
     if (!g_lag.ok || S <= 0 || K <= 0 || G <= 0 || (D % 32) || (I % 32)) return -1;
+    if (!acc || !x || !gu_q || !gu_s || !dn_q || !dn_s || !gexp || !gbeg || !gcnt || !grow || !rowof || !w) return -1;
+    if (((uintptr_t)gu_q | (uintptr_t)gu_s | (uintptr_t)dn_q | (uintptr_t)dn_s) & 15) return -1;   // 128-bit loads, TMA tensor maps
     const int P = S * K;
     if (g_lag.dglu.ensure((size_t)P * I * 4) || g_lag.dslot.ensure((size_t)P * D * 4) || g_lag.dxp.ensure((size_t)S * D * 4) ||
         g_lag.dsums.ensure(((size_t)S + 64 + (size_t)P * (I / 8 + 1)) * 4)) return -1;
@@ -962,6 +988,7 @@ extern "C" int lag_cuda_expert_q4(float *out, const float *x, const void *p13, c
 extern "C" int lag_cuda_matmul_fp4(float *y, const float *x, const void *packed, const void *es, int S, int I, int O) {
     if (sw_fault_injected()) return -1;
     if (!g_lag.ok || S <= 0 || O <= 0 || I <= 0 || (I & 31)) return -1;          // scale blocks are 32 wide
+    if (!y || !x || !packed || !es || ((uintptr_t)packed & 15)) return -1;
     SwLaunchCfg cfg{g_lag.num_sms, g_lag.st, g_lag.dev};
     return lag_roundtrip(y, x, (size_t)S * I * 4, (size_t)S * O * 4, [&] {
         return sw_launch_fp4_rows(cfg, (const float *)g_lag.dx.p, packed, es, (float *)g_lag.dy.p, S, I, O);
@@ -974,6 +1001,7 @@ extern "C" int lag_cuda_moe_experts_fp4(float *out, const float *x, const void *
     if (sw_fault_injected()) return -1;
     if (!g_lag.ok || K < 0 || K > 4096 || I <= 0 || D <= 0 || (D & 31) || (I & 31)) return -1;
     if (K > 0 && (!sel || !w)) return -1;
+    if (!out || !x || !gu_q || !gu_es || !dn_q || !dn_es || (((uintptr_t)gu_q | (uintptr_t)dn_q) & 15)) return -1;
     const size_t ib = (size_t)(K > 0 ? K : 1) * 8;                                // sel [K] int32, then w [K] f32
     if (g_lag.didx.ensure(ib) || g_lag.hidx.ensure(ib) || g_lag.dglu.ensure((size_t)(K + 1) * I * 4) ||
         g_lag.dslot.ensure((size_t)(K + 1) * D * 4)) return -1;
@@ -991,6 +1019,7 @@ extern "C" int lag_cuda_moe_experts_fp4(float *out, const float *x, const void *
 extern "C" int lag_cuda_matmul_q4(float *y, const float *x, const void *packed, const void *scale, int S, int I, int O) {
     if (sw_fault_injected()) return -1;
     if (!g_lag.ok || S <= 0 || O <= 0 || I <= 0 || (I % 32)) return -1;
+    if (!y || !x || !packed || !scale || (((uintptr_t)packed | (uintptr_t)scale) & 15)) return -1;
     // a single group of S packed rows through the row-output form of the grouped kernel
     if (g_lag.dmisc.ensure(256 * 4)) return -1;
     int h[256] = {0};

@@ -116,10 +116,10 @@ int sw_launch_q4_tma(const SwLaunchCfg &c, const SwQ4Args &a, const SwMmaIO &io,
 int sw_launch_wait_runs_out(const SwLaunchCfg &c, int *status, unsigned limit);
 // sw_umma.cu: tcgen05/TMEM grouped GEMM for groups with many rows
 bool sw_umma_available();
-int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow, int P, int KD, void *hi, void *lo);
+int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow, int P, int KD, void *hi, void *lo, int *status);
 int sw_launch_umma_chunks(const SwLaunchCfg &c, const SwQ4Args &a, int *nchunks, void *chunks);
 int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_hi, const void *act_lo, void *Y0, void *Y1,
-                      const int *nchunks, const void *chunks, int max_chunks, int *status, long long wrows_total, bool gateup);
+                      const int *nchunks, const void *chunks, int max_chunks, int *status, long long wrows_total, bool gateup, int terms);
 int sw_launch_pack_bf16_planar(const SwLaunchCfg &c, const float *x, void *hi, void *lo, int rows, int KD);
 int sw_launch_bf16_umma(const SwLaunchCfg &c, const void *W0, const void *W1, const void *act_hi, const void *act_lo,
                         void *Y0, void *Y1, int T, int KD, int O, int *status, bool gateup);

@@ -1,29 +1,34 @@
 // Grouped int4 expert GEMM on the 5th-generation tensor cores (tcgen05 + TMEM)
 // for groups with many token rows (prefill, large decode batches).
 //
-// CTA tile: M = 128 weight rows x N <= 128 token rows of one expert group, K in
-// stages of 64 columns.  Fourteen warps, four roles:
-//   warp 12     TMA producer: per stage one/two 2D tiles of raw int4 weights
-//               (128 rows x 32 B) and the fp16 hi and lo activation tiles
-//               (R rows x 128 B, 128B swizzle = the K-major canonical layout the
-//               tensor core reads) into a ring of shared-memory stages
-//   warps 0-7   dequantise: two threads per tile row turn its 32 raw bytes into 64
-//               exact fp16 integers (nibble-8) and store them as one swizzled
-//               128-byte row of one of four A tiles in flight
-//   warp 13     one thread issues tcgen05.mma (kind::f16, f32 accumulate in TMEM):
-//               per 16-column step one MMA against the hi tile and one against
-//               the lo tile (x = hi + lo); tcgen05.commit releases the buffers
-//   warps 8-11  epilogue: tcgen05.ld the accumulator (two accumulators alternate,
-//               so the next tile's MMAs overlap this epilogue), apply the per-row
-//               scales and SiLU(gate)*up or store the f32 slot rows
-// For gate/up, tile row 2j is gate row j and tile row 2j+1 is up row j, so the two
-// halves of an output meet in neighbouring lanes of the epilogue.
+// D[weight rows, token rows] = W . X^T: 128 dequantised weight rows are the A operand
+// (M = 128), a chunk of <= 128 token rows of one expert group (padded to 16/32/64/128)
+// the B operand, f32 accumulators in tensor memory.  A CTA work item is a chunk times
+// a PAIR of weight tiles that share the chunk's activation tiles (gate/up: the gate
+// rows of 128 outputs and their up rows, so SiLU(gate)*up is lane-local in the
+// epilogue; down: two neighbouring tiles).  K runs in slots of 64 columns through a
+// ring of UM_STAGES shared-memory stages.  Fifteen warps, four roles:
+//   warp 12      TMA producer: per slot the raw int4 rows of both tiles (2 x 128 rows
+//                x 32 B) and the fp16 activation tile(s) (R rows x 128 B, 128B swizzle =
+//                the K-major canonical layout the tensor core reads)
+//   warps 0-7    dequantise, two groups of four: group t turns the raw rows of tile t
+//                into exact fp16 integers (nibble - 8) stored as swizzled 128-byte rows
+//                of one of four A tiles in flight
+//   warps 13,14  MMA issuers, one thread each, one per tile of the pair:
+//                tcgen05.mma kind::f16 per 16-column step against the hi tile and, with
+//                two terms, against the lo tile (x = hi + lo) into the same accumulator
+//                columns; one tcgen05.commit per slot returns the slot and the A tiles
+//   warps 8-11   epilogue: tcgen05.ld the two accumulators of the item (two buffers
+//                alternate, so the next item's MMAs overlap this epilogue), apply the
+//                per-row scales and SiLU(gate)*up, or store the f32 slot rows
 //
-// Activations for this kernel are fp16 hi/lo arrays [rows, K] whose columns are
-// permuted inside every group of eight to 0,4,1,5,2,6,3,7 -- the order in which
-// the nibble masks deliver a weight word -- so a dequantised word is one 16-byte
-// chunk of the A tile.  The token rows of gate/up are gathered into packed-slot
-// order by k_umma_gather (the reference gathers too, c/laguna.c:742-743).
+// Activations are fp16 arrays [rows, K] whose columns are permuted inside every group
+// of eight to 0,4,1,5,2,6,3,7 -- the order in which the nibble masks deliver a weight
+// word -- so a dequantised word is one 16-byte chunk of the A tile.  `terms` = 1 feeds
+// the tensor core fp16(x) alone (relative rounding 2^-12 per element); `terms` = 2 adds
+// the residual lo = fp16(x - hi) as a second MMA per step (f32-level accuracy, twice the
+// tensor work).  The token rows of gate/up are gathered into packed-slot order by
+// k_umma_gather (the reference gathers too, c/laguna.c:742-743).
 //
 // All mbarrier waits are bounded; on a timeout the CTA raises an abort flag, sets
 // SW_ST_TIMEOUT in the status word and still frees its tensor memory.
@@ -114,9 +119,10 @@ __device__ __forceinline__ void um_split(float v, __half &hi, __half &lo) {
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 k_umma_gather(const float *__restrict__ x, const int *__restrict__ grow, int P, int KD,
-              __half *__restrict__ hi, __half *__restrict__ lo) {
+              __half *__restrict__ hi, __half *__restrict__ lo, int *__restrict__ status) {
     const int cpr = KD >> 3;
     const size_t n = (size_t)P * cpr;
+    bool clamped = false;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
         const int slot = (int)(idx / cpr), c8 = (int)(idx - (size_t)slot * cpr);
         const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)grow[slot] * KD + c8 * 8);
@@ -124,10 +130,11 @@ k_umma_gather(const float *__restrict__ x, const int *__restrict__ grow, int P, 
         const float v[8] = {a.x, b.x, a.y, b.y, a.z, b.z, a.w, b.w};
         __half h[8], l[8];
 #pragma unroll
-        for (int i = 0; i < 8; i++) um_split(v[i], h[i], l[i]);
+        for (int i = 0; i < 8; i++) { clamped |= fabsf(v[i]) > 65504.f; um_split(v[i], h[i], l[i]); }
         reinterpret_cast<uint4 *>(hi)[idx] = *reinterpret_cast<uint4 *>(h);
-        reinterpret_cast<uint4 *>(lo)[idx] = *reinterpret_cast<uint4 *>(l);
+        if (lo) reinterpret_cast<uint4 *>(lo)[idx] = *reinterpret_cast<uint4 *>(l);
     }
+    if (clamped && status) atomicOr(status, SW_ST_RANGE);
 }
 
 // work list: one entry per (group, chunk of <=128 rows): {group index, first row of the chunk inside the group}
@@ -158,11 +165,12 @@ struct UmArgs {
     const int2 *chunks;
     int *status;
     int KD, OUT, expert_lo;
+    int terms;                     // fp16 terms per activation: 1 = hi only, 2 = hi + lo
 };
 
 template <bool GATEUP>
 __global__ void __launch_bounds__(UM_THREADS, 1)
-k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmW2,
+k_q4_umma(const __grid_constant__ CUtensorMap tmW,
           const __grid_constant__ CUtensorMap tmH16, const __grid_constant__ CUtensorMap tmH32,
           const __grid_constant__ CUtensorMap tmH64, const __grid_constant__ CUtensorMap tmH128,
           const __grid_constant__ CUtensorMap tmL16, const __grid_constant__ CUtensorMap tmL32,
@@ -208,12 +216,10 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
         const int2 c = a.chunks[ch]; gi = c.x; c0 = c.y;
     };
 
-    // Small token tiles pack two 64-column sub-stages into one ring slot (one barrier round trip and one
-    // weight TMA per 128 columns).
-    // Slot layout: [raw int4 of the tile pair: 256 rows x 32*KSUB B] then per sub-stage [hi tile: R x 128 B][lo tile: R x 128 B].
+    // Slot layout: [raw int4 of the tile pair: 256 rows x 32 B][hi tile: R x 128 B][lo tile: R x 128 B].
     // Raw rows: the 128 rows of tile 0 (gate rows), then the 128 rows of tile 1 (up rows).
     auto tile_rows = [](int n) { return n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : 128; };
-    auto substages = [&](int) { return 1; };                           // one 64-column sub-stage per ring slot
+    const bool two_terms = a.terms == 2;
 
     if (warp == UM_DQ_WARPS + 4) {
         // ------------------------------ TMA producer ------------------------------
@@ -222,26 +228,23 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
             for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
                 int gi, c0, pr; decode(item, gi, c0, pr);
                 const int e = a.gexp[gi] - a.expert_lo, n = min(128, a.gcnt[gi] - c0), row0 = a.gbeg[gi] + c0;
-                const int R = tile_rows(n), KSUB = substages(R);
+                const int R = tile_rows(n);
                 const CUtensorMap *th = R == 16 ? &tmH16 : R == 32 ? &tmH32 : R == 64 ? &tmH64 : &tmH128;
                 const CUtensorMap *tl = R == 16 ? &tmL16 : R == 32 ? &tmL32 : R == 64 ? &tmL64 : &tmL128;
-                const CUtensorMap *tw = KSUB == 2 ? &tmW2 : &tmW;
                 const int wrow = e * nrows_w + pr * OPP;                 // first weight row of the pair (gate rows for gate/up)
-                const unsigned rawA = 2u * UM_RAW_A * KSUB, bt = (unsigned)R * 128u;
-                for (int sl = 0; sl < NST / KSUB; sl++, kk++) {
+                const unsigned rawA = 2u * UM_RAW_A, bt = (unsigned)R * 128u;
+                for (int sl = 0; sl < NST; sl++, kk++) {
                     const int s = kk % UM_STAGES;
                     if (kk >= UM_STAGES && !um_bar_wait(um_s32(&b_raw_free[s]), ((kk / UM_STAGES) - 1) & 1, abortp)) {
                         atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break;
                     }
                     unsigned char *sp = smem + s * UM_STAGE_BYTES;
                     const unsigned bar = um_s32(&b_raw_full[s]);
-                    um_bar_expect(bar, rawA + 2u * KSUB * bt);
-                    um_tma_2d(um_s32(sp), tw, sl * 32 * KSUB, wrow, bar);                               // 128 rows
-                    um_tma_2d(um_s32(sp + rawA / 2), tw, sl * 32 * KSUB, wrow + (GATEUP ? OUT : 128), bar); // 128 rows
-                    for (int u = 0; u < KSUB; u++) {
-                        um_tma_2d(um_s32(sp + rawA + (2 * u) * bt), th, (sl * KSUB + u) * 64, row0, bar);
-                        um_tma_2d(um_s32(sp + rawA + (2 * u + 1) * bt), tl, (sl * KSUB + u) * 64, row0, bar);
-                    }
+                    um_bar_expect(bar, rawA + (two_terms ? 2u : 1u) * bt);
+                    um_tma_2d(um_s32(sp), &tmW, sl * 32, wrow, bar);                                  // 128 rows
+                    um_tma_2d(um_s32(sp + rawA / 2), &tmW, sl * 32, wrow + (GATEUP ? OUT : 128), bar);  // 128 rows
+                    um_tma_2d(um_s32(sp + rawA), th, sl * 64, row0, bar);
+                    if (two_terms) um_tma_2d(um_s32(sp + rawA + bt), tl, sl * 64, row0, bar);
                 }
             }
         }
@@ -277,7 +280,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
 #pragma unroll
                     for (int k = 0; k < 4; k++) {                       // 16 columns = 32 bytes per step
                         um_mma(d_tmem, da + 2 * k, dh + 2 * k, idesc, (st | k) ? 1u : 0u);
-                        um_mma(d_tmem, da + 2 * k, dl + 2 * k, idesc, 1u);
+                        if (two_terms) um_mma(d_tmem, da + 2 * k, dl + 2 * k, idesc, 1u);
                     }
                     // one commit per slot and issuer: when both have arrived the slot returns to the TMA warp and the
                     // pair's dequantised tiles to the dequantising warps
@@ -298,8 +301,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
         unsigned slot_base = 0;
         for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
             int gi, c0, pr; decode(item, gi, c0, pr);
-            const int R = tile_rows(min(128, a.gcnt[gi] - c0)), KSUB = substages(R);
-            const int pitch = 32 * KSUB;                                // bytes per raw row in the slot
+            const int pitch = 32;                                       // bytes per raw row in the slot
             int rawoff[2], dstoff[2];
 #pragma unroll
             for (int i = 0; i < 2; i++) {
@@ -310,14 +312,13 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
                 dstoff[i] = trow * 128 + (((h * 4) ^ (trow & 7)) << 4);  // chunk (4h + j) goes to (4h + j) ^ (trow & 7)
             }
             for (int st = 0; st < NST; st++) {
-                const int u = st % KSUB;
-                const unsigned ks = slot_base + st / KSUB, kk = 2 * ks + tsel, b = kk % UM_ABUF;
+                const unsigned ks = slot_base + st, kk = 2 * ks + tsel, b = kk % UM_ABUF;
                 const int s = ks % UM_STAGES;
                 bool ok = um_bar_wait(um_s32(&b_raw_full[s]), (ks / UM_STAGES) & 1, abortp);
                 // A tile b was last read by the MMAs of the slot two back: wait until that slot is done
                 if (ok && ks >= 2) ok = um_bar_wait(um_s32(&b_raw_free[(ks - 2) % UM_STAGES]), ((ks - 2) / UM_STAGES) & 1, abortp);
                 if (!ok) { if (lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; } break; }
-                const unsigned char *raw = smem + s * UM_STAGE_BYTES + u * 32;
+                const unsigned char *raw = smem + s * UM_STAGE_BYTES;
                 unsigned char *dstb = a16 + b * UM_A16;
                 uint4 w[2];
 #pragma unroll
@@ -336,13 +337,14 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
                 __syncwarp();
                 if (lane == 0) um_bar_arrive(um_s32(&b_a_full[b]));
             }
-            slot_base += NST / KSUB;
+            slot_base += NST;
         }
     } else {
         // ------------------------------ epilogue (four warps, one TMEM lane quarter each) ------------------------------
         const int q = warp & 3;                                         // TMEM lane quarter of this warp
         const int trow = q * 32 + lane;                                 // tile row held by this thread
         unsigned nitem = 0;
+        bool clamped = false;
         for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, nitem++) {
             int gi, c0, pr; decode(item, gi, c0, pr);
             const int e = a.gexp[gi] - a.expert_lo, n = min(128, a.gcnt[gi] - c0), row0 = a.gbeg[gi] + c0;
@@ -371,8 +373,10 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
                             const float gv = g[j] * sg;
                             const float y = (gv / (1.f + expf(-gv))) * (u[j] * su);
                             __half hi, lo; um_split(y, hi, lo);
+                            clamped |= fabsf(y) > 65504.f;
                             const size_t pos = (size_t)(row0 + cb + j) * OUT + pcol;
-                            Yh[pos] = hi; Yl[pos] = lo;
+                            Yh[pos] = hi;
+                            if (two_terms) Yl[pos] = lo;
                         }
                     }
                 }
@@ -395,6 +399,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUten
             __syncwarp();
             if (lane == 0) um_bar_arrive(um_s32(&b_acc_free[qb]));
         }
+        if (clamped) atomicOr(a.status, SW_ST_RANGE);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -437,12 +442,12 @@ static int um_make_map(CUtensorMap *m, CUtensorMapDataType dt, int esize, const 
 
 bool sw_umma_available() { return um_get_encode() != nullptr; }
 
-int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow, int P, int KD, void *hi, void *lo) {
+int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow, int P, int KD, void *hi, void *lo, int *status) {
     if (P <= 0) return 0;
     size_t n = (size_t)P * (KD / 8);
     long long grid = (long long)((n + 255) / 256);
     if (grid > (long long)c.num_sms * 16) grid = (long long)c.num_sms * 16;
-    k_umma_gather<<<(unsigned)grid, 256, 0, c.stream>>>(x, grow, P, KD, (__half *)hi, (__half *)lo);
+    k_umma_gather<<<(unsigned)grid, 256, 0, c.stream>>>(x, grow, P, KD, (__half *)hi, (__half *)lo, status);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
@@ -456,13 +461,14 @@ int sw_launch_umma_chunks(const SwLaunchCfg &c, const SwQ4Args &a, int *nchunks,
 // act_hi/act_lo: fp16 [max_rows, KD] in packed-slot order (permuted columns).
 // gate/up: Y0/Y1 = fp16 hi/lo [max_rows, OUT]; down: Y0 = f32 [max_rows, OUT].
 int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_hi, const void *act_lo, void *Y0, void *Y1,
-                      const int *nchunks, const void *chunks, int max_chunks, int *status, long long wrows_total, bool gateup) {
+                      const int *nchunks, const void *chunks, int max_chunks, int *status, long long wrows_total, bool gateup, int terms) {
     if (a.max_rows <= 0) return 0;
+    if (terms != 1 && terms != 2) return -1;
+    if (terms == 1) act_lo = act_hi;                                    // never read; keeps the tensor maps valid
     if (a.KD % 64 || a.OUT <= 0 || ((uintptr_t)a.q & 15)) return -1;
     if ((a.OUT % (gateup ? 128 : 256)) != 0) return -1;                  // whole tile pairs only
-    CUtensorMap tw, tw2, th[4], tl[4];
+    CUtensorMap tw, th[4], tl[4];
     if (um_make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.q, a.KD / 2, wrows_total, 32, 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
-    if (um_make_map(&tw2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.q, a.KD / 2, wrows_total, 64, 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
     const int R[4] = {16, 32, 64, 128};
     for (int i = 0; i < 4; i++) {
         if (um_make_map(&th[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act_hi, a.KD, a.max_rows, 64, R[i], CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
@@ -476,14 +482,14 @@ int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_h
             return 1; }) <= 0) return -1;
     UmArgs ka;
     ka.Ws = a.s; ka.Y0 = Y0; ka.Y1 = Y1; ka.gexp = a.gexp; ka.gbeg = a.gbeg; ka.gcnt = a.gcnt; ka.nchunks = nchunks;
-    ka.chunks = (const int2 *)chunks; ka.status = status; ka.KD = a.KD; ka.OUT = a.OUT; ka.expert_lo = a.expert_lo;
+    ka.chunks = (const int2 *)chunks; ka.status = status; ka.KD = a.KD; ka.OUT = a.OUT; ka.expert_lo = a.expert_lo; ka.terms = terms;
     const int pairs = a.OUT / (gateup ? 128 : 256);
     long long items = (long long)max_chunks * pairs;
     long long grid = c.num_sms;                        // one CTA per SM (shared memory and tensor memory are sized for that)
     if (grid > items) grid = items;
     if (grid < 1) grid = 1;
-    if (gateup) k_q4_umma<true><<<(unsigned)grid, UM_THREADS, SMEM, c.stream>>>(tw, tw2, th[0], th[1], th[2], th[3], tl[0], tl[1], tl[2], tl[3], ka);
-    else k_q4_umma<false><<<(unsigned)grid, UM_THREADS, SMEM, c.stream>>>(tw, tw2, th[0], th[1], th[2], th[3], tl[0], tl[1], tl[2], tl[3], ka);
+    if (gateup) k_q4_umma<true><<<(unsigned)grid, UM_THREADS, SMEM, c.stream>>>(tw, th[0], th[1], th[2], th[3], tl[0], tl[1], tl[2], tl[3], ka);
+    else k_q4_umma<false><<<(unsigned)grid, UM_THREADS, SMEM, c.stream>>>(tw, th[0], th[1], th[2], th[3], tl[0], tl[1], tl[2], tl[3], ka);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -107,3 +107,38 @@ class ExpertParallelMoe:
         cur.wait_stream(side)
         g_finish.replay()
         return out
+
+    def timed_segments(self, layers, xs, outs, steps):
+        """Mean ms of the five segments of a step on this rank, from CUDA events on the launching streams: the
+        all-gather, the route + resident-experts graph, the reduce-scatter, the shared-expert graph (side stream) and
+        the finish graph.  Needs prepare() to have recorded the graphs of every (layer, batch) pair used."""
+        names = ("all_gather", "route_experts", "reduce_scatter", "shared", "finish")
+        tot = dict.fromkeys(names, 0.0)
+        dev = xs[0].device
+        cur = torch.cuda.current_stream(dev)
+        n = 0
+        for i in range(steps):
+            layer, x, out = layers[i % len(layers)], xs[i % len(xs)], outs[i % len(outs)]
+            gs = self._graphs.get((id(layer), x.data_ptr(), out.data_ptr()))
+            if gs is None:
+                continue
+            g_shared, g_experts, g_finish, _ = gs
+            X, partial, routed = self._bufs["X"], self._bufs["partial"], self._bufs["routed"]
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(8)]
+            side = self._side
+            side.wait_stream(cur)
+            ev[0].record(side); g_shared.replay(side); ev[1].record(side)
+            ev[2].record(cur)
+            dist.all_gather_into_tensor(X, x, group=self.group); ev[3].record(cur)
+            g_experts.replay(); ev[4].record(cur)
+            dist.reduce_scatter_tensor(routed, partial, op=dist.ReduceOp.SUM, group=self.group); ev[5].record(cur)
+            cur.wait_stream(side); ev[6].record(cur)
+            g_finish.replay(); ev[7].record(cur)
+            torch.cuda.synchronize(dev)
+            tot["shared"] += ev[0].elapsed_time(ev[1]); tot["all_gather"] += ev[2].elapsed_time(ev[3])
+            tot["route_experts"] += ev[3].elapsed_time(ev[4]); tot["reduce_scatter"] += ev[4].elapsed_time(ev[5])
+            tot["finish"] += ev[6].elapsed_time(ev[7])
+            n += 1
+        if n == 0:
+            raise RuntimeError("no recorded graphs: call prepare() first")
+        return {k: v / n for k, v in tot.items()}

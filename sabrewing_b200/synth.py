@@ -161,12 +161,16 @@ def make_layer_device(cfg, device, layer_index=0):
     else:
         out["logit_bias"] = None
 
+    seven = torch.full((), 7.0, dtype=torch.float32, device=device)
+
     def quant_dev(rows, cols, nrep):
         q = torch.empty((nrep * rows, cols // 2), dtype=torch.uint8, device=device)
         s = torch.empty((nrep * rows,), dtype=torch.float32, device=device)
         for e in range(nrep):
             w = torch.randn((rows, cols), generator=g, device=device) * 0.02
-            sc = (w.abs().amax(dim=1) / 7.0).clamp_min(1e-12)
+            # tensor / tensor: a true division (torch turns a division by a Python scalar into a multiplication by
+            # its reciprocal, which is one ulp off the reference's max|w| / 7.0f on some rows)
+            sc = (w.abs().amax(dim=1) / seven).clamp_min(1e-12)
             v = torch.round(w / sc[:, None]).clamp_(-8, 7).to(torch.int32) + 8
             q[e * rows:(e + 1) * rows] = (v[:, 0::2] | (v[:, 1::2] << 4)).to(torch.uint8)
             s[e * rows:(e + 1) * rows] = sc

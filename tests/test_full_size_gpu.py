@@ -23,15 +23,17 @@ pytestmark = pytest.mark.gpu
 OUT_TOL = 1e-3
 W_TOL = 5e-7
 
-# (config, token rows, rows whose outputs are checked (0 = all), expected expert path)
+# (config, token rows, rows whose outputs are checked (0 = all), expected expert path, fp16 terms on the tcgen05 path)
 CASES = [
-    ("c1", 32, 0, 2),       # OLMoE-shaped, softmax, no shared expert
-    ("c2", 1, 0, 2),        # Laguna-shaped decode batch 1
-    ("c2", 32, 0, 2),       # ... batch 32 (the headline)
-    ("c2", 256, 0, 2),      # ... batch 256
-    ("c4", 256, 0, 2),      # wide layer, 384 experts, decode batch 256
-    ("c3", 4096, 64, 3),    # prefill, Zipf-skewed routing: tcgen05 path
-    ("c5", 1024, 64, 3),    # very large layer, 16 rows per expert on one GPU: tcgen05 path
+    ("c1", 32, 0, 2, 2),       # OLMoE-shaped, softmax, no shared expert
+    ("c2", 1, 0, 2, 2),        # Laguna-shaped decode batch 1
+    ("c2", 32, 0, 2, 2),       # ... batch 32 (the headline)
+    ("c2", 256, 0, 2, 2),      # ... batch 256
+    ("c4", 256, 0, 2, 2),      # wide layer, 384 experts, decode batch 256
+    ("c3", 4096, 64, 3, 2),    # prefill, Zipf-skewed routing: tcgen05 path, activations as two fp16 terms
+    ("c3", 4096, 64, 3, 1),    # ... as one fp16 term (half the tensor work): same ids, output error reported
+    ("c5", 1024, 64, 3, 2),    # very large layer, 16 rows per expert on one GPU: tcgen05 path
+    ("c5", 1024, 64, 3, 1),
 ]
 
 
@@ -56,9 +58,9 @@ def _min_margin(scores, bias, K):
     return float((part[:, 1] - part[:, 0]).min())           # k-th minus (k+1)-th
 
 
-@pytest.mark.parametrize("name,T,subset,path", CASES)
-def test_full_size_config(orc, name, T, subset, path):
-    from sabrewing_b200 import synth
+@pytest.mark.parametrize("name,T,subset,path,terms", CASES)
+def test_full_size_config(orc, name, T, subset, path, terms):
+    from sabrewing_b200 import synth, capi
     from sabrewing_b200.moe_block import MoeBlock, MoeLayer, desc_from_config
     cfg = synth.CONFIGS[name]
     arrays = synth.make_layer_device(cfg, "cuda:0", 0)
@@ -73,6 +75,7 @@ def test_full_size_config(orc, name, T, subset, path):
     hin = np.random.default_rng(cfg.seed + 5).standard_normal(x.shape).astype(np.float32)
 
     blk = MoeBlock("cuda:0", T, cfg.E, cfg.K, cfg.D, cfg.I, cfg.SI)
+    assert blk.lib.sw_moe_set_option(blk.ctx, capi.OPT_UMMA_TERMS, terms) == 0
     xd = torch.from_numpy(x).cuda(); out = torch.from_numpy(hin).cuda()
     blk.forward(desc, layer, xd, out)
     torch.cuda.synchronize()
@@ -101,7 +104,7 @@ def test_full_size_config(orc, name, T, subset, path):
         want = want + orc.shared_rows(host, xs, exact=1)
     delta = out.cpu().numpy()[rows] - hin[rows]
     err = rel_l2(delta, want)
-    print("%s T=%d: output rel-L2 %.3e on %d rows, path %d" % (name, T, err, len(rows), path))
+    print("%s T=%d: output rel-L2 %.3e on %d rows, path %d, fp16 terms %d" % (name, T, err, len(rows), path, terms))
     assert err < OUT_TOL, (err, note)
     if not subset and T <= 32:
         # the whole block in one call of the checker (residual included), as the scaled cases do

@@ -410,26 +410,42 @@ def test_small_groups_take_the_tma_path_and_odd_widths_the_cuda_cores(orc):
     run_case(synth_case("c2", corr_bias_std=0.01, T=8, D=384, E=12, K=3, I=96, SI=64), orc, path=0)
 
 
-def test_misaligned_blob_falls_back_to_the_cp_async_kernels(orc):
-    """An int4 blob that is not 16-byte aligned cannot sit under a TMA tensor map: the mma.sync + cp.async kernels
-    (path 1) take over, same results."""
+def test_every_kernel_family_on_one_case(orc):
+    """The same layer through each expert-kernel family (SW_OPT_EXPERT_PATH): CUDA cores, mma.sync + cp.async,
+    mma.sync + TMA, tcgen05; each must report the family that ran and meet the same bars."""
+    from sabrewing_b200 import capi
+    case = synth_case("c3", corr_bias_std=0.01, T=160, D=512, I=256, SI=128, E=16, K=4)
+    want = orc.moe_group(case.host, case.x, case.hin, exact=1)
+    for path in (0, 1, 2, 3):
+        blk, layer, desc = make_block(case)
+        assert blk.lib.sw_moe_set_option(blk.ctx, capi.OPT_EXPERT_PATH, path) == 0
+        x = torch.from_numpy(case.x).cuda(); out = torch.from_numpy(case.hin).cuda()
+        blk.forward(desc, layer, x, out)
+        torch.cuda.synchronize()
+        assert blk.status() == 0 and blk.lib.sw_moe_last_path(blk.ctx) == path
+        check_routing(blk.routing(), want)
+        assert rel_l2(out.cpu().numpy() - case.hin, want["out"] - case.hin) < OUT_TOL, path
+        blk.close()
+
+
+def test_misaligned_weight_blob_is_refused(orc):
+    """Every expert kernel reads the int4 blobs 16 bytes at a time: a blob 8 bytes off that alignment is refused with an
+    error text before anything is launched."""
+    from sabrewing_b200 import capi
     from sabrewing_b200.moe_block import MoeBlock, MoeLayer, desc_from_config
     case = synth_case("c2", corr_bias_std=0.01, T=8, D=512, E=32, K=4, I=128, SI=128)
     cfg = case.cfg
     blk = MoeBlock("cuda:0", 8, cfg.E, cfg.K, cfg.D, cfg.I, cfg.SI)
     layer = MoeLayer(cfg.D, cfg.I, cfg.SI, case.a, "cuda:0")
-    pad = torch.empty(layer.gu_q.numel() + 16, dtype=torch.uint8, device="cuda")     # same bytes, 8 bytes off alignment
-    off = (8 - pad.data_ptr() % 16) % 16
-    shifted = pad[off:off + layer.gu_q.numel()].view(layer.gu_q.shape); shifted.copy_(layer.gu_q)
-    layer.gu_q = shifted
-    assert layer.gu_q.data_ptr() % 16 == 8
-    x = torch.from_numpy(case.x).cuda(); out = torch.from_numpy(case.hin).cuda()
-    blk.forward(desc_from_config(cfg), layer, x, out)
-    torch.cuda.synchronize()
-    assert blk.lib.sw_moe_last_path(blk.ctx) == 1 and blk.status() == 0
-    want = orc.moe_group(case.host, case.x, case.hin, exact=1)
-    check_routing(blk.routing(), want)
-    assert rel_l2(out.cpu().numpy() - case.hin, want["out"] - case.hin) < OUT_TOL
+    l = layer.c(); l.gu_q = layer.gu_q.data_ptr() + 8
+    d = desc_from_config(cfg).c()
+    x = torch.from_numpy(case.x).cuda(); out = torch.zeros_like(x)
+    l0 = blk.lib.sw_launch_count()
+    assert blk.lib.sw_moe_forward(blk.ctx, C.byref(d), C.byref(l), x.data_ptr(), out.data_ptr(), 8, None) == -1
+    assert "16-byte" in capi.last_error() and blk.lib.sw_launch_count() == l0
+    lib = _lag()
+    y = np.zeros((1, 8), np.float32); xx = np.zeros((1, 64), np.float32)
+    assert lib.lag_cuda_matmul_q4(y.ctypes.data, xx.ctypes.data, layer.gu_q.data_ptr() + 8, layer.gu_s.data_ptr(), 1, 64, 8) == -1
     blk.close()
 
 
