@@ -53,6 +53,7 @@ def parse():
     ap.add_argument("--cpu-reps", type=int, default=12)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="N=1: only the headline workload (no other batches, no GPU baseline)")
+    ap.add_argument("--umma-terms", type=int, default=0, help="fp16 terms per activation on the tcgen05 path (0 = the library's default)")
     ap.add_argument("--no-graph", action="store_true", help="launch the kernels of every step one by one instead of replaying CUDA graphs")
     return ap.parse_args()
 
@@ -252,6 +253,8 @@ def roofline_entry(name, cfg, T, per, G, ms_per_step, peaks):
 class Single:
     """One single-GPU workload: resident layers, token batches, a block and (optionally) a graph per step pattern."""
 
+    umma_terms = 0           # 0: the library's default
+
     def __init__(self, name, cfg, T, layers, dev, use_graph=True):
         import numpy as np
         import torch
@@ -263,6 +266,8 @@ class Single:
         self.xs = [x.to(dev) for x in self.xs_host]
         self.outs = [torch.zeros_like(x) for x in self.xs]
         self.block = MoeBlock(dev, T, cfg.E, cfg.K, cfg.D, cfg.I, cfg.SI)
+        if Single.umma_terms:
+            self.block._chk(self.block.lib.sw_moe_set_option(self.block.ctx, 1, Single.umma_terms), "sw_moe_set_option")
         self.graphs = {}
         if use_graph:
             L = len(layers)
@@ -442,6 +447,7 @@ def run_single(args):
     peaks = load_peaks()
     cfg = synth.CONFIGS[args.workload]
     T = args.batch or cfg.T
+    Single.umma_terms = args.umma_terms
     sampler = ClockSampler(0)
     sampler.start()
 

@@ -211,12 +211,14 @@ int  sw_moe_get_routing(SwMoeCtx *ctx, int *sel, float *w, float *scores, int *G
  * throughout, c/moe_quant.h:45-217). */
 int  sw_moe_status(SwMoeCtx *ctx);
 /* Context options.  SW_OPT_UMMA_TERMS: how the tcgen05 grouped GEMM (groups averaging >= 16
- * rows: prefill, large batches) feeds f32 activations to the fp16 tensor cores.  2 = two
- * fp16 terms, x = hi + lo, two MMAs per step: f32-level accuracy (measured ~1e-5 relative
- * L2 on the 4096-token prefill).  1 = fp16(x) alone, half the tensor work: each activation
- * is rounded to 11 significant bits, measured relative L2 of the block output against the
- * reference's exact f32 path stated with the results (bar: 1e-3).  The decode kernels
- * (small groups) always use both terms.
+ * rows: prefill, large batches) feeds f32 activations to the fp16 tensor cores.
+ * 1 (default) = fp16(x) alone: each activation, and each SiLU*up value entering the down
+ * product, is rounded to 11 significant bits; measured relative L2 of the block output
+ * against the reference's exact f32 path: 2.7e-4 on the 4096-token Laguna-shaped prefill,
+ * 5.6e-5 on the 1024-token very large layer (bar 1e-3).  2 = two fp16 terms, x = hi + lo,
+ * two MMAs per step: f32-level accuracy (1.2e-5 / 1.8e-5 on the same cases) at twice the
+ * tensor work.  Routing is identical either way.  The decode kernels (small groups) always
+ * use both terms.
  * SW_OPT_EXPERT_PATH: -1 (default) lets the library choose the expert kernels by shape
  * and mean group size; 0..3 asks for one family (numbering of sw_moe_last_path), lowered
  * when the shapes do not fit it.  For tests and measurements.

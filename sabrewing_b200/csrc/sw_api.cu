@@ -119,7 +119,7 @@ struct SwMoeCtx {
     float *sums = nullptr;       // row sums of x and partial row sums of the SiLU*up rows
     int lastT = 0, lastK = 0, lastE = 0;
     int last_path = -1;          // expert kernels of the last experts/forward call (sw_moe_last_path)
-    int umma_terms = 2;
+    int umma_terms = 1;
     int forced_path = -1;        // SW_OPT_EXPERT_PATH: -1 = choose by shape and group size          // fp16 terms per activation on the tcgen05 path: 1 = hi only, 2 = hi + lo
     int cap_on = 0, cap_prof = 0; long long cap_l0 = 0;   // open stage capture (sw_moe_capture_begin)
     // a shared-expert result left by sw_moe_shared for the next sw_moe_finish of the same row count

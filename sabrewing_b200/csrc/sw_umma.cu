@@ -7,7 +7,7 @@
 // a PAIR of weight tiles that share the chunk's activation tiles (gate/up: the gate
 // rows of 128 outputs and their up rows, so SiLU(gate)*up is lane-local in the
 // epilogue; down: two neighbouring tiles).  K runs in slots of 64 columns through a
-// ring of UM_STAGES shared-memory stages.  Fifteen warps, four roles:
+// ring of shared-memory slots (six with one fp16 term, four with two).  Fifteen warps, four roles:
 //   warp 12      TMA producer: per slot the raw int4 rows of both tiles (2 x 128 rows
 //                x 32 B) and the fp16 activation tile(s) (R rows x 128 B, 128B swizzle =
 //                the K-major canonical layout the tensor core reads)
@@ -37,10 +37,15 @@
 #include <cuda_fp16.h>
 #include <stdlib.h>
 
-#define UM_STAGES 4
+#define UM_MAX_STAGES 6
 #define UM_RAW_A 4096                    // 128 rows x 32 B of int4
 #define UM_BT 16384                      // one activation tile: 128 rows x 128 B
-#define UM_STAGE_BYTES (2 * UM_RAW_A + 2 * UM_BT)   // a pair of weight tiles shares the activation tiles of a slot
+// A ring slot holds the raw rows of a pair of weight tiles and the activation tile(s) they share: 24 KB with one
+// fp16 term (six slots in flight), 40 KB with two (four slots).  The ring's depth is what hides the latency of the
+// weight stream: a slot is refilled only when its MMAs have retired.
+#define UM_STAGE_BYTES(terms) (2 * UM_RAW_A + (terms) * UM_BT)
+#define UM_STAGES_FOR(terms) ((terms) == 1 ? 6 : 4)
+#define UM_RING_BYTES (4 * UM_STAGE_BYTES(2))        // 160 KB: four slots of 40 KB, or six of 24 KB
 #define UM_A16 16384                     // dequantised A tile: 128 rows x 64 fp16
 #define UM_WAIT_LIMIT (1u << 24)
 #define UM_ABUF 4                        // dequantised A tiles in flight
@@ -177,11 +182,12 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
           const __grid_constant__ CUtensorMap tmL64, const __grid_constant__ CUtensorMap tmL128,
           const UmArgs a) {
     extern __shared__ unsigned char um_dyn[];
-    __shared__ unsigned long long b_raw_full[UM_STAGES], b_raw_free[UM_STAGES], b_a_full[UM_ABUF], b_a_free[UM_ABUF], b_acc_full[4], b_acc_free[2];
+    __shared__ unsigned long long b_raw_full[UM_MAX_STAGES], b_raw_free[UM_MAX_STAGES], b_a_full[UM_ABUF], b_a_free[UM_ABUF], b_acc_full[4], b_acc_free[2];
     __shared__ unsigned s_tmem;
     __shared__ int s_abort;
     unsigned char *smem = (unsigned char *)(((uintptr_t)um_dyn + 1023) & ~(uintptr_t)1023);
-    unsigned char *a16 = smem + UM_STAGES * UM_STAGE_BYTES;             // UM_ABUF dequantised A tiles
+    const unsigned STG = UM_STAGES_FOR(a.terms), SBYTES = UM_STAGE_BYTES(a.terms);   // ring depth and slot size
+    unsigned char *a16 = smem + UM_RING_BYTES;                          // UM_ABUF dequantised A tiles
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KD = a.KD, OUT = a.OUT;
     const int nrows_w = GATEUP ? 2 * OUT : OUT;
@@ -194,7 +200,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
     volatile int *abortp = &s_abort;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < UM_STAGES; i++) { um_bar_init(um_s32(&b_raw_full[i]), 1); um_bar_init(um_s32(&b_raw_free[i]), 2); }
+        for (int i = 0; i < UM_MAX_STAGES; i++) { um_bar_init(um_s32(&b_raw_full[i]), 1); um_bar_init(um_s32(&b_raw_free[i]), 2); }
         for (int i = 0; i < UM_ABUF; i++) { um_bar_init(um_s32(&b_a_full[i]), UM_DQ_WARPS / 2); um_bar_init(um_s32(&b_a_free[i]), 1); }
         for (int i = 0; i < 4; i++) um_bar_init(um_s32(&b_acc_full[i]), 1);
         for (int i = 0; i < 2; i++) um_bar_init(um_s32(&b_acc_free[i]), 4);
@@ -234,11 +240,11 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
                 const int wrow = e * nrows_w + pr * OPP;                 // first weight row of the pair (gate rows for gate/up)
                 const unsigned rawA = 2u * UM_RAW_A, bt = (unsigned)R * 128u;
                 for (int sl = 0; sl < NST; sl++, kk++) {
-                    const int s = kk % UM_STAGES;
-                    if (kk >= UM_STAGES && !um_bar_wait(um_s32(&b_raw_free[s]), ((kk / UM_STAGES) - 1) & 1, abortp)) {
+                    const unsigned s = kk % STG;
+                    if (kk >= STG && !um_bar_wait(um_s32(&b_raw_free[s]), ((kk / STG) - 1) & 1, abortp)) {
                         atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break;
                     }
-                    unsigned char *sp = smem + s * UM_STAGE_BYTES;
+                    unsigned char *sp = smem + s * SBYTES;
                     const unsigned bar = um_s32(&b_raw_full[s]);
                     um_bar_expect(bar, rawA + (two_terms ? 2u : 1u) * bt);
                     um_tma_2d(um_s32(sp), &tmW, sl * 32, wrow, bar);                                  // 128 rows
@@ -272,11 +278,11 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
                 const unsigned bt = (unsigned)R * 128u;
                 bool ok = true;
                 for (int st = 0; st < NST; st++, ks++) {
-                    const unsigned s = ks % UM_STAGES, kk = 2 * ks + t, b = kk % UM_ABUF;
+                    const unsigned s = ks % STG, kk = 2 * ks + t, b = kk % UM_ABUF;
                     if (!um_bar_wait(um_s32(&b_a_full[b]), (kk / UM_ABUF) & 1, abortp)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t da = um_desc(um_s32(a16 + b * UM_A16));
-                    const uint64_t dh = um_desc(um_s32(smem + s * UM_STAGE_BYTES + 2 * UM_RAW_A)), dl = um_desc(um_s32(smem + s * UM_STAGE_BYTES + 2 * UM_RAW_A + bt));
+                    const uint64_t dh = um_desc(um_s32(smem + s * SBYTES + 2 * UM_RAW_A)), dl = um_desc(um_s32(smem + s * SBYTES + 2 * UM_RAW_A + bt));
 #pragma unroll
                     for (int k = 0; k < 4; k++) {                       // 16 columns = 32 bytes per step
                         um_mma(d_tmem, da + 2 * k, dh + 2 * k, idesc, (st | k) ? 1u : 0u);
@@ -313,12 +319,12 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
             }
             for (int st = 0; st < NST; st++) {
                 const unsigned ks = slot_base + st, kk = 2 * ks + tsel, b = kk % UM_ABUF;
-                const int s = ks % UM_STAGES;
-                bool ok = um_bar_wait(um_s32(&b_raw_full[s]), (ks / UM_STAGES) & 1, abortp);
+                const unsigned s = ks % STG;
+                bool ok = um_bar_wait(um_s32(&b_raw_full[s]), (ks / STG) & 1, abortp);
                 // A tile b was last read by the MMAs of the slot two back: wait until that slot is done
-                if (ok && ks >= 2) ok = um_bar_wait(um_s32(&b_raw_free[(ks - 2) % UM_STAGES]), ((ks - 2) / UM_STAGES) & 1, abortp);
+                if (ok && ks >= 2) ok = um_bar_wait(um_s32(&b_raw_free[(ks - 2) % STG]), ((ks - 2) / STG) & 1, abortp);
                 if (!ok) { if (lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; } break; }
-                const unsigned char *raw = smem + s * UM_STAGE_BYTES;
+                const unsigned char *raw = smem + s * SBYTES;
                 unsigned char *dstb = a16 + b * UM_A16;
                 uint4 w[2];
 #pragma unroll
@@ -474,7 +480,8 @@ int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_h
         if (um_make_map(&th[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act_hi, a.KD, a.max_rows, 64, R[i], CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
         if (um_make_map(&tl[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act_lo, a.KD, a.max_rows, 64, R[i], CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
     }
-    constexpr int SMEM = UM_STAGES * UM_STAGE_BYTES + UM_ABUF * UM_A16 + 1024;
+    static_assert(UM_STAGES_FOR(1) * UM_STAGE_BYTES(1) <= UM_RING_BYTES && UM_STAGES_FOR(2) * UM_STAGE_BYTES(2) <= UM_RING_BYTES, "ring sizes");
+    constexpr int SMEM = UM_RING_BYTES + UM_ABUF * UM_A16 + 1024;
     static SwPerDevice attr;
     if (attr.get(c.dev, [] {
             if (cudaFuncSetAttribute(k_q4_umma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
