@@ -54,6 +54,9 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="N=1: only the headline workload (no other batches, no GPU baseline)")
     ap.add_argument("--umma-terms", type=int, default=0, help="fp16 terms per activation on the tcgen05 path (0 = the library's default)")
+    ap.add_argument("--ep-scheme", default="auto", choices=["auto", "replicate", "alltoall"],
+                    help="N>1: exchange scheme (auto: replicate up to 256 rows per rank, all-to-all above)")
+    ap.add_argument("--ep-python", action="store_true", help="N>1: drive the exchange from Python (three graph replays and two NCCL calls per step) instead of the in-library step")
     ap.add_argument("--no-graph", action="store_true", help="launch the kernels of every step one by one instead of replaying CUDA graphs")
     return ap.parse_args()
 
@@ -542,9 +545,13 @@ def run_parallel(args):
     xs = [x.to(dev) for x in xs_host]
     outs = [torch.zeros_like(x) for x in xs]
     block = MoeBlock(dev, T * world, cfg.E, cfg.K, cfg.D, cfg.I, cfg.SI)
-    ep = ExpertParallelMoe(block, desc)
-    # this rank's kernels of a step as three graphs per (layer, batch) pair; the collectives stay NCCL calls
-    if not args.no_graph:
+    scheme = args.ep_scheme if args.ep_scheme != "auto" else ("replicate" if T <= 256 else "alltoall")
+    ep = ExpertParallelMoe(block, desc, scheme=scheme)
+    native = not args.ep_python
+    if native:
+        ep.native_init(T, cfg.D, dev)                 # the step is one call into the library, NCCL enqueued there
+    # (Python exchange) this rank's kernels of a step as three graphs per (layer, batch) pair; the collectives stay NCCL calls
+    if not native and not args.no_graph and scheme == "replicate":
         try:
             for li in range(len(layers)):
                 for bi in range(NB):
@@ -585,13 +592,22 @@ def run_parallel(args):
             "config": {"workload": workload_name(cfg, T, world), "global_batch": T * world, "layers_cycled": len(layers),
                        "l2": "inputs larger than L2: steps cycle over %d layers (%.2f GB of expert blobs each per GPU) and %d token batches"
                              % (len(layers), layers[0].expert_bytes() / 1e9, NB),
-                       "parallelism": "ep%d" % world,
-                       "launch": "three graph replays and two NCCL calls per step" if ep._graphs else "one launch per kernel"},
+                       "parallelism": "ep%d" % world, "exchange": scheme,
+                       "launch": ("one library call per step (sw_ep_forward: kernels and NCCL collectives enqueued by the library)" if native else
+                                  "three graph replays and two NCCL calls per step" if ep._graphs else "one launch per kernel")},
             "clocks": clocks, "gpu_launches": int(launches)}
 
     # ---- where a step's time goes: CUDA events around the five segments (max over ranks of each segment's mean) ----
     try:
-        seg = ep.timed_segments(layers, xs, outs, min(args.steps, 50))
+        if native:
+            seg, nseg = {}, min(args.steps, 50)
+            for i in range(nseg):
+                ep.native_forward(layers[i % len(layers)], xs[i % NB], outs[i % NB], timed=True)
+                torch.cuda.synchronize()
+                for k, v in ep.native_segments().items():
+                    seg[k] = seg.get(k, 0.0) + v / nseg
+        else:
+            seg = ep.timed_segments(layers, xs, outs, min(args.steps, 50))
         names = sorted(seg)
         tt = torch.tensor([seg[k] for k in names], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
@@ -638,6 +654,7 @@ def run_parallel(args):
                    "api": "ExpertParallelMoe.forward with per-step pinned H2D of x and D2H of out on every rank"}
 
     # ---- strong-scaling reference point: the same GLOBAL batch on one GPU holding all experts (rank 0 alone) ----
+    ep.close()
     del ep, block, layers
     torch.cuda.empty_cache()
     barrier()

@@ -177,6 +177,42 @@ void *sw_moe_capture_stream(SwMoeCtx *ctx);
 int  sw_moe_capture_begin(SwMoeCtx *ctx);
 int  sw_moe_capture_end(SwMoeCtx *ctx, SwMoeGraph **graph);
 
+/* Grouped experts for routing GIVEN by the caller: sel [T,K] int32 in rank order (-1 =
+ * the pair contributes nothing) and w [T,K] f32, device memory.  routed[T,D] = sum over the
+ * resident experts of w * expert(x), unscaled, overwritten; the rows are grouped by expert
+ * on the device as after sw_moe_route (c/laguna.c:709-723).  For drivers that route
+ * elsewhere: another GPU (sw_ep_*), or the host as the lag_cuda_* callers do. */
+int  sw_moe_experts_routed(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer, const float *x,
+                           const int *sel, const float *w, float *routed, int T, void *stream);
+
+/* ------------------------------------------------------------------------- */
+/* 3. Expert-parallel step over the GPUs of one node (one process per GPU)    */
+/* ------------------------------------------------------------------------- */
+/* Experts sharded contiguously over the ranks (rank g owns experts [g*E/N, (g+1)*E/N),
+ * the first E % N ranks one more), router and shared expert replicated, T rows per
+ * rank.  The reference has no multi-process layer (its multi-device code is peer
+ * copies and per-device grouping on the host, c/backend_cuda.cu:1444-1466,
+ * c/colibri.c:3506-3607).  One call is one step: the NCCL collectives are enqueued
+ * from inside the library on the caller's stream, between its kernels.  NCCL is
+ * loaded at run time (libnccl.so.2); hosts that never call sw_ep_* need none.
+ *   SW_EP_REPLICATE: all-gather rows, route all N*T rows on every rank, resident
+ *     experts, reduce-scatter the partial sums (decode-size batches).
+ *   SW_EP_ALLTOALL: route own rows, send each row once to every GPU holding one of
+ *     its experts (with ids and weights), experts there, one pre-weighted partial
+ *     sum per row back, added in GPU order (large batches).  One host sync per step
+ *     to size the sends.
+ * sw_ep_unique_id: 128 bytes from rank 0 that every rank passes to sw_ep_create (the
+ * host distributes them; any transport).  ctx must hold N*T rows.  Not thread-safe per
+ * SwEp; 0 = ok, -1 = error with sw_last_error(). */
+enum { SW_EP_REPLICATE = 0, SW_EP_ALLTOALL = 1 };
+typedef struct SwEp SwEp;
+int  sw_ep_unique_id(void *id128);
+int  sw_ep_create(SwEp **ep, SwMoeCtx *ctx, const void *id128, int world, int rank, int rows_per_rank, int D, int topk);
+void sw_ep_destroy(SwEp *ep);
+int  sw_ep_forward(SwEp *ep, const SwMoeDesc *desc, const SwMoeLayer *layer, const float *x, float *out, int T,
+                   int scheme, int timed, void *stream);
+int  sw_ep_segments(SwEp *ep, float *ms, int scheme);
+
 /* Routing without any allocation (no counterpart in the reference, which sizes its
  * scratch with cudaMalloc on demand, c/backend_cuda_laguna.cu:471-493): router
  * logits -> gate -> top-k -> combine weights for T <= 8 rows, n_experts <= 512,

@@ -9,7 +9,8 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libsabrewing_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-         "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--use_fast_math=false"]
+         "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+LIBS = ["-ldl"]            # NCCL is looked up with dlopen at run time, not linked
 
 
 def sources():
@@ -28,8 +29,7 @@ def build(force=False, verbose=False):
     """Compile every .cu under csrc/ into one shared library.  Returns its path."""
     if not force and not stale():
         return LIB
-    flags = [f for f in FLAGS if not f.startswith("--use_fast_math")]
-    cmd = [NVCC] + flags + (["-Xptxas", "-v"] if verbose else []) + ["-shared", "-o", LIB] + sources()
+    cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-shared", "-o", LIB] + sources() + LIBS
     env = dict(os.environ)
     env.pop("CC", None); env.pop("CXX", None)
     r = subprocess.run(cmd, capture_output=True, text=True, env=env)

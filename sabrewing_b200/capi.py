@@ -13,6 +13,7 @@ ROUTE_SIGMOID, ROUTE_SOFTMAX, ROUTE_SOFTPLUS = 0, 1, 2
 SHARED_NONE, SHARED_UNSCALED = 0, 1
 DTYPE_F32, DTYPE_BF16 = 0, 1
 OPT_UMMA_TERMS, OPT_EXPERT_PATH = 1, 2
+EP_REPLICATE, EP_ALLTOALL = 0, 1
 
 
 class SwMoeDesc(C.Structure):
@@ -58,6 +59,12 @@ SIGNATURES = {
     "sw_moe_experts": (_i, [_vp, _pd, _pl, _vp, _vp, _i, _vp]),
     "sw_moe_finish": (_i, [_vp, _pd, _pl, _vp, _vp, _vp, _i, _vp]),
     "sw_moe_shared": (_i, [_vp, _pd, _pl, _vp, _i, _vp]),
+    "sw_moe_experts_routed": (_i, [_vp, _pd, _pl, _vp, _vp, _vp, _vp, _i, _vp]),
+    "sw_ep_unique_id": (_i, [_vp]),
+    "sw_ep_create": (_i, [C.POINTER(_vp), _vp, _vp, _i, _i, _i, _i, _i]),
+    "sw_ep_destroy": (None, [_vp]),
+    "sw_ep_forward": (_i, [_vp, _pd, _pl, _vp, _vp, _i, _i, _i, _vp]),
+    "sw_ep_segments": (_i, [_vp, C.POINTER(C.c_float), _i]),
     "sw_moe_capture_stream": (_vp, [_vp]),
     "sw_moe_capture_begin": (_i, [_vp]),
     "sw_moe_capture_end": (_i, [_vp, C.POINTER(_vp)]),

@@ -71,6 +71,10 @@ static int sw_fail(const char *fmt, ...) {
 }
 extern "C" const char *sw_last_error(void) { return g_err; }
 int sw_noalloc_fail(const char *msg) { return sw_fail("%s", msg); }
+int sw_fail_text(const char *fmt, ...) {
+    va_list ap; va_start(ap, fmt); vsnprintf(g_err, sizeof g_err, fmt, ap); va_end(ap);
+    return -1;
+}
 
 // A CUDA error is sticky only for faults; plain API failures (OOM, bad argument)
 // are cleared so that the next call starts clean (the reference's hygiene rule,
@@ -338,7 +342,7 @@ static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, 
         const int P = a.max_rows, max_chunks = P / 128 + a.max_groups;
         __half *xh = (__half *)um->xg, *xl = xh + (size_t)P * D;
         __half *gh = (__half *)glu, *gl = gh + (size_t)P * I;
-        if (sw_launch_umma_gather(cfg, x, a.grow, P, D, xh, umma_terms == 2 ? xl : nullptr, status)) return -1;
+        if (sw_launch_umma_gather(cfg, x, a.grow, a.G + 1, P, D, xh, umma_terms == 2 ? xl : nullptr, status)) return -1;
         if (sw_launch_umma_chunks(cfg, a, um->nchunks, um->chunks)) return -1;
         a.q = (const uint8_t *)gu_q; a.s = gu_s; a.KD = D; a.OUT = I;
         if (sw_launch_q4_umma(cfg, a, xh, xl, gh, gl, um->nchunks, um->chunks, max_chunks, status, nexp * 2 * I, true, umma_terms)) return -1;
@@ -503,6 +507,38 @@ extern "C" int sw_moe_experts(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
     SwLaunchCfg cfg{c->num_sms, st, c->dev};
     int lo, cnt; sw_resident(d, L, &lo, &cnt);
     if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, nullptr, 0, routed, T, d->topk, L->D, 1.f, 0, lo, cnt)) return sw_fail("combine launch failed");
+    return 0;
+}
+
+SwRouting *sw_ctx_routing(SwMoeCtx *c) { return &c->r; }
+void sw_ctx_info(const SwMoeCtx *c, int *dev, int *num_sms, int *maxT, void **aux_stream) {
+    if (dev) *dev = c->dev;
+    if (num_sms) *num_sms = c->num_sms;
+    if (maxT) *maxT = c->maxT;
+    if (aux_stream) *aux_stream = (void *)c->aux;
+}
+
+// routed[T,D] = sum over the resident experts of w * expert(x) for routing GIVEN by the caller: sel [T,K] int32 (rank
+// order; SW_NO_EXPERT = -1 entries contribute nothing) and w [T,K] f32 in device memory.  The rows are grouped by
+// expert on the device exactly as after sw_moe_route.  For drivers that route elsewhere (another GPU, the host).
+extern "C" int sw_moe_experts_routed(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x,
+                                     const int *sel, const float *w, float *routed, int T, void *stream) {
+    SW_GATE();
+    if (sw_check(c, d, L, T)) return -1;
+    if (T == 0) return 0;
+    if (sw_validate_rows(x, routed, x, "experts_routed")) return -1;
+    if (!sel || !w) return sw_fail("experts_routed: null routing");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int K = d->topk, E = d->n_experts;
+    const size_t nb = (size_t)T * K * 4;
+    if (sel != c->r.sel) SW_CUDA(cudaMemcpyAsync(c->r.sel, sel, nb, cudaMemcpyDeviceToDevice, st));
+    if (w != c->r.w) SW_CUDA(cudaMemcpyAsync(c->r.w, w, nb, cudaMemcpyDeviceToDevice, st));
+    SwLaunchCfg cfg{c->num_sms, st, c->dev};
+    if (sw_launch_dispatch(cfg, c->r, T, K, E)) return sw_fail("dispatch launch failed");
+    c->last_stream = st; c->lastT = T; c->lastK = K; c->lastE = E;
+    if (sw_expert_stage(c, d, L, x, T, st)) return -1;
+    int lo, cnt; sw_resident(d, L, &lo, &cnt);
+    if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, nullptr, 0, routed, T, K, L->D, 1.f, 0, lo, cnt)) return sw_fail("combine launch failed");
     return 0;
 }
 
@@ -912,7 +948,7 @@ static int lag_stage_idx(LagIdx *d, const int *gexp, const int *gbeg, const int 
     if (g_lag.didx.ensure(bytes) || g_lag.hidx.ensure(bytes)) return -1;
     int *h = (int *)g_lag.hidx.p;
     for (int i = 0; i < 64; i++) h[i] = 0;
-    h[0] = G;
+    h[0] = G; h[1] = P;                             // groups, packed rows
     int *hp = h + 64;
     memcpy(hp, gexp, (size_t)G * 4); hp += G;
     memcpy(hp, gbeg, (size_t)G * 4); hp += G;

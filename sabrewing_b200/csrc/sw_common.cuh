@@ -9,6 +9,7 @@
 #define SW_FULL_MASK 0xffffffffu
 #define SW_MAX_EXPERTS 1024     // top-k keeps <= 32 scores per lane
 #define SW_MAX_TOPK 32
+#define SW_NO_EXPERT (-1)       // sel entry of a (row, rank) pair that selects nothing: skipped by dispatch and combine
 
 // Status bits written by kernels into SwRouting::status.
 #define SW_ST_BAD_EXPERT 1
@@ -22,7 +23,7 @@ struct SwRouting {
     float *scores;   // [T,E] logits in, gate scores out
     int   *sel;      // [T,K] expert ids, rank order
     float *w;        // [T,K] combine weights
-    int   *G;        // [1]   number of non-empty groups
+    int   *G;        // [2]   number of non-empty groups; number of (row, rank) pairs that selected an expert
     int   *gexp, *gbeg, *gcnt;   // [E]
     int   *grow;     // [T*K] packed row -> token row
     int   *rowof;    // [T*K] (token, rank) -> packed row
@@ -71,6 +72,12 @@ const SwTuning &sw_tuning();
 
 void sw_count_launch(int n = 1);
 
+// internal views of a context for the other translation units (sw_ep.cu, sw_glm.cu)
+struct SwMoeCtx;
+SwRouting *sw_ctx_routing(SwMoeCtx *c);
+void sw_ctx_info(const SwMoeCtx *c, int *dev, int *num_sms, int *maxT, void **aux_stream);
+int sw_fail_text(const char *fmt, ...);          // sets the thread's last-error text, returns -1
+
 // sw_route.cu
 int sw_launch_router_logits(const SwLaunchCfg &c, const float *x, const void *W, int w_dtype,
                             const float *logit_bias, float *rl, int T, int D, int E);
@@ -116,7 +123,7 @@ int sw_launch_q4_tma(const SwLaunchCfg &c, const SwQ4Args &a, const SwMmaIO &io,
 int sw_launch_wait_runs_out(const SwLaunchCfg &c, int *status, unsigned limit);
 // sw_umma.cu: tcgen05/TMEM grouped GEMM for groups with many rows
 bool sw_umma_available();
-int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow, int P, int KD, void *hi, void *lo, int *status);
+int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow, const int *npairs, int P, int KD, void *hi, void *lo, int *status);
 int sw_launch_umma_chunks(const SwLaunchCfg &c, const SwQ4Args &a, int *nchunks, void *chunks);
 int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_hi, const void *act_lo, void *Y0, void *Y1,
                       const int *nchunks, const void *chunks, int max_chunks, int *status, long long wrows_total, bool gateup, int terms);

@@ -202,6 +202,7 @@ __device__ __forceinline__ void sw_dispatch_block(int *sm, const int *sel, int n
     const int s0 = min(warp * seg, npairs), s1 = min(s0 + seg, npairs);
     for (int i = s0 + lane; i < s1; i += 32) {
         int e = __ldcg(sel + i);
+        if (e == SW_NO_EXPERT) continue;                       // a pair that contributes nothing (rows routed elsewhere)
         if (e < 0 || e >= E) { atomicOr(status, SW_ST_BAD_EXPERT); continue; }
         atomicAdd(&wh[warp * E + e], 1);
     }
@@ -246,7 +247,7 @@ __device__ __forceinline__ void sw_dispatch_block(int *sm, const int *sel, int n
             if (ce > 0) { gexp[gidx] = e; gbeg[gidx] = excl; gcnt[gidx] = ce; gidx++; }
             excl += ce;
         }
-        if (tid == 0) *Gout = s_gsum[31];
+        if (tid == 0) { Gout[0] = s_gsum[31]; Gout[1] = s_wsum[31]; }   // groups, and pairs that selected an expert
     }
     __syncthreads();
 

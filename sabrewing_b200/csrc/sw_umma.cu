@@ -123,9 +123,10 @@ __device__ __forceinline__ void um_split(float v, __half &hi, __half &lo) {
 // group of eight in the order 0,4,1,5,2,6,3,7
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-k_umma_gather(const float *__restrict__ x, const int *__restrict__ grow, int P, int KD,
+k_umma_gather(const float *__restrict__ x, const int *__restrict__ grow, const int *__restrict__ npairs, int P, int KD,
               __half *__restrict__ hi, __half *__restrict__ lo, int *__restrict__ status) {
     const int cpr = KD >> 3;
+    P = min(P, *npairs);                         // packed rows the dispatch filled (pairs that selected no expert leave none)
     const size_t n = (size_t)P * cpr;
     bool clamped = false;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
@@ -448,12 +449,12 @@ static int um_make_map(CUtensorMap *m, CUtensorMapDataType dt, int esize, const 
 
 bool sw_umma_available() { return um_get_encode() != nullptr; }
 
-int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow, int P, int KD, void *hi, void *lo, int *status) {
+int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow, const int *npairs, int P, int KD, void *hi, void *lo, int *status) {
     if (P <= 0) return 0;
     size_t n = (size_t)P * (KD / 8);
     long long grid = (long long)((n + 255) / 256);
     if (grid > (long long)c.num_sms * 16) grid = (long long)c.num_sms * 16;
-    k_umma_gather<<<(unsigned)grid, 256, 0, c.stream>>>(x, grow, P, KD, (__half *)hi, (__half *)lo, status);
+    k_umma_gather<<<(unsigned)grid, 256, 0, c.stream>>>(x, grow, npairs, P, KD, (__half *)hi, (__half *)lo, status);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -187,6 +187,15 @@ class MoeBlock:
                                           x.shape[0], self._stream(stream)), "sw_moe_experts")
         return routed
 
+    def experts_routed(self, desc, layer, x, sel, w, routed, stream=None):
+        """routed = weighted sum over the resident experts for routing given by the caller (sel int32 [T,K] with -1 =
+        no expert, w f32 [T,K]; device tensors)."""
+        d, l = desc.c(), layer.c()
+        self._last = (x.shape[0], desc.topk, desc.n_experts)
+        self._chk(self.lib.sw_moe_experts_routed(self.ctx, C.byref(d), C.byref(l), x.data_ptr(), sel.data_ptr(), w.data_ptr(),
+                                                 routed.data_ptr(), x.shape[0], self._stream(stream)), "sw_moe_experts_routed")
+        return routed
+
     def shared(self, desc, layer, x, stream=None):
         """The shared expert of x ahead of time; the next finish() with as many rows uses it."""
         d, l = desc.c(), layer.c()
