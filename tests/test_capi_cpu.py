@@ -26,6 +26,24 @@ def test_library_exports_every_declared_symbol():
     assert sorted(capi.SIGNATURES) == names
 
 
+def test_glm_boundary_symbols_are_exported():
+    """Every coli_cuda_* entry point include/sabrewing_b200_glm.h declares is exported by the library."""
+    from sabrewing_b200 import build, capi
+    build.build()
+    text = open(os.path.join(ROOT, "include", "sabrewing_b200_glm.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = sorted(set(re.findall(r"\b(coli_cuda_[a-z0-9_]+)\s*\(", text)))
+    assert len(names) >= 30
+    l = C.CDLL(capi.LIB_PATH)
+    for n in names:
+        assert hasattr(l, n), n
+    # without a device the set-up reports failure (0) and the engine keeps its CPU path
+    import torch
+    if not torch.cuda.is_available():
+        assert l.coli_cuda_init((C.c_int * 1)(0), 1) == 0
+        assert l.coli_cuda_device_count() == 0
+
+
 def test_struct_layouts_match_reference_descriptor():
     from sabrewing_b200 import capi
     # MoeDesc (c/moe_arch.h:33-41): 5 ints, float, enum -> 28 bytes, fields in this order
