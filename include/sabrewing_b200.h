@@ -138,6 +138,12 @@ void sw_moe_ctx_destroy(SwMoeCtx *ctx);
  * follow c/moe_block.h:51 / c/laguna.c:781. */
 int  sw_moe_forward(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer,
                     const float *x, float *out, int T, void *stream);
+/* The layer tail with the residual stream resident on the device: h[T,D] += MoE(rmsnorm(h) * norm_w)
+ * (c/laguna.c:1119 then :1126; rmsnorm_row c/moe_math.h:58-62: sum of squares in double).  The
+ * normalised rows stay in the context; nothing crosses the host.  sw_rmsnorm is the norm alone. */
+int  sw_moe_forward_norm(SwMoeCtx *ctx, const SwMoeDesc *desc, const SwMoeLayer *layer, float *h,
+                         const float *norm_w, float eps, int T, void *stream);
+int  sw_rmsnorm(const float *x, const float *w, float *y, int T, int D, float eps, void *stream);
 /* Same through HOST buffers: pinned staging, H2D, the block, D2H, stream sync --
  * the shape of a reference lag_cuda_* call (c/backend_cuda_laguna.cu:516-546).
  * out_host is read and updated in place. */

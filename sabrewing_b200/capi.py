@@ -52,6 +52,8 @@ SIGNATURES = {
     "sw_moe_ctx_destroy": (None, [_vp]),
     "sw_moe_forward": (_i, [_vp, _pd, _pl, _vp, _vp, _i, _vp]),
     "sw_moe_forward_host": (_i, [_vp, _pd, _pl, _vp, _vp, _i]),
+    "sw_moe_forward_norm": (_i, [_vp, _pd, _pl, _vp, _vp, _f, _i, _vp]),
+    "sw_rmsnorm": (_i, [_vp, _vp, _vp, _i, _i, _f, _vp]),
     "sw_moe_graph_create": (_i, [_vp, _pd, _pl, _vp, _vp, _i, C.POINTER(_vp)]),
     "sw_moe_graph_launch": (_i, [_vp, _vp]),
     "sw_moe_graph_destroy": (None, [_vp]),

@@ -577,6 +577,30 @@ extern "C" int sw_moe_forward(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
     return sw_forward_impl(c, d, L, x, out, T, stream, true);
 }
 
+// h += MoE(rmsnorm(h) * norm_w): the reference's layer tail (c/laguna.c:1119,1126) with the residual stream h kept
+// on the device; the normalised rows live in the context until the block has consumed them.
+extern "C" int sw_moe_forward_norm(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, float *h, const float *norm_w, float eps, int T, void *stream) {
+    SW_GATE();
+    if (sw_check(c, d, L, T)) return -1;
+    if (T == 0) return 0;
+    if (sw_validate_rows(h, norm_w, h, "forward_norm")) return -1;
+    SwLaunchCfg cfg{c->num_sms, (cudaStream_t)stream, c->dev};
+    if (sw_launch_rmsnorm(cfg, h, norm_w, c->dx, T, L->D, eps)) return sw_fail("rmsnorm launch failed");
+    return sw_forward_impl(c, d, L, c->dx, h, T, stream, true);
+}
+// y[T,D] = rmsnorm(x) * w on the device (c/moe_math.h:58-62); x == y is allowed.
+extern "C" int sw_rmsnorm(const float *x, const float *w, float *y, int T, int D, float eps, void *stream) {
+    if (!x || !w || !y || T < 0 || D <= 0 || (D & 3)) return sw_fail("rmsnorm: bad argument (D must be a multiple of 4)");
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) return sw_fail("rmsnorm: buffers must be 16-byte aligned");
+    if (T == 0) return 0;
+    int dev = 0, sms = 0;
+    SW_CUDA(cudaGetDevice(&dev));
+    SW_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    SwLaunchCfg cfg{sms, (cudaStream_t)stream, dev};
+    if (sw_launch_rmsnorm(cfg, x, w, y, T, D, eps)) return sw_fail("rmsnorm launch failed");
+    return 0;
+}
+
 static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, float *out, int T, void *stream, bool accumulate) {
     if (sw_check(c, d, L, T)) return -1;
     if (T == 0) return 0;
@@ -924,6 +948,28 @@ extern "C" int lag_cuda_matmul_bf16(float *y, const float *x, const void *W, int
     if (!g_lag.ok || S <= 0 || I <= 0 || O <= 0 || (I & 7)) return -1;
     if (!y || !x || !W || ((uintptr_t)W & 15)) return -1;                     // weight rows are read 16 bytes at a time
     SwLaunchCfg cfg{g_lag.num_sms, g_lag.st, g_lag.dev};
+    // tensor cores when the shapes fit: x as two bf16 terms (hi + lo), weights exact, f32 accumulate.  Many rows:
+    // the dense tcgen05 GEMM; few rows: mma.sync over slices of the contraction, partial sums added in slice order.
+    const bool tc = !sw_tuning().force_simt && I % 32 == 0 && O % 4 == 0;
+    if (tc && S >= 128 && I % 64 == 0 && sw_umma_available()) {
+        if (g_lag.dxp.ensure((size_t)S * I * 4) || g_lag.dmisc.ensure(1024)) return -1;
+        return lag_roundtrip(y, x, (size_t)S * I * 4, (size_t)S * O * 4, [&] {
+            __nv_bfloat16 *xh = (__nv_bfloat16 *)g_lag.dxp.p, *xl = xh + (size_t)S * I;
+            int *status = (int *)g_lag.dmisc.p + 128;
+            if (cudaMemsetAsync(status, 0, 4, g_lag.st) != cudaSuccess) { cudaGetLastError(); return -1; }
+            if (sw_launch_pack_bf16_planar(cfg, (const float *)g_lag.dx.p, xh, xl, S, I)) return -1;
+            return sw_launch_bf16_umma(cfg, W, nullptr, xh, xl, g_lag.dy.p, nullptr, S, I, O, status, false);
+        });
+    }
+    if (tc) {
+        const int ks = sw_shared_slices(cfg.num_sms, (O + 15) / 16, I);
+        if (g_lag.dxp.ensure((size_t)S * I * 4) || g_lag.dslot.ensure((size_t)ks * S * O * 4)) return -1;
+        return lag_roundtrip(y, x, (size_t)S * I * 4, (size_t)S * O * 4, [&] {
+            if (sw_launch_pack_bf16(cfg, (const float *)g_lag.dx.p, g_lag.dxp.p, S, I)) return -1;
+            if (sw_launch_bf16_mma(cfg, W, nullptr, g_lag.dxp.p, (float *)g_lag.dslot.p, S, I, O, ks, false)) return -1;
+            return sw_launch_sum_slices(cfg, (const float *)g_lag.dslot.p, ks, (size_t)S * O, (float *)g_lag.dy.p);
+        });
+    }
     return lag_roundtrip(y, x, (size_t)S * I * 4, (size_t)S * O * 4, [&] {
         return sw_launch_bf16_rows(cfg, (const float *)g_lag.dx.p, W, (float *)g_lag.dy.p, S, I, O);
     });
@@ -1064,12 +1110,21 @@ extern "C" int lag_cuda_matmul_q4(float *y, const float *x, const void *packed, 
     if (cudaStreamSynchronize(g_lag.st) != cudaSuccess) { cudaGetLastError(); return -1; }   // h is a stack buffer
     int *dm = (int *)g_lag.dmisc.p;
     SwLaunchCfg cfg{g_lag.num_sms, g_lag.st, g_lag.dev};
+    // tensor cores when the shapes fit: the S rows are one group of the TMA-staged int4 kernel (row-output form)
+    const bool tc = !sw_tuning().force_simt && sw_tuning().expert_pref >= 2 && I % 128 == 0 && sw_tma_available();
+    if (tc && (g_lag.dxp.ensure((size_t)S * I * 4) || g_lag.dsums.ensure(((size_t)S + 64) * 4))) return -1;
     return lag_roundtrip(y, x, (size_t)S * I * 4, (size_t)S * O * 4, [&] {
         SwQ4Args a{};
         a.G = dm; a.gexp = dm + 64; a.gbeg = dm + 65; a.gcnt = dm + 66; a.grow = nullptr;
         a.expert_lo = 0; a.expert_cnt = 1; a.max_groups = 1; a.max_rows = S;
         a.q = (const uint8_t *)packed; a.s = (const float *)scale; a.X = (const float *)g_lag.dx.p; a.Y = (float *)g_lag.dy.p;
         a.KD = I; a.OUT = O;
+        if (tc) {
+            if (sw_launch_pack_act(cfg, (const float *)g_lag.dx.p, g_lag.dxp.p, (float *)g_lag.dsums.p, S, I)) return -1;
+            SwMmaIO io{g_lag.dxp.p, (const float *)g_lag.dsums.p, 1, g_lag.dy.p, nullptr};
+            const int mt = (O + 127) / 128 >= cfg.num_sms * 4 ? 2 : 1;
+            return sw_launch_q4_tma(cfg, a, io, dm + 128, O, false, mt);
+        }
         return sw_launch_q4_down(cfg, a);
     });
 }

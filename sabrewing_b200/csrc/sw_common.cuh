@@ -148,6 +148,8 @@ int sw_launch_combine(const SwLaunchCfg &c, const float *slots, const int *rowof
                       float route_scale, int mode, int expert_lo, int expert_cnt);
 int sw_launch_finish(const SwLaunchCfg &c, const float *routed, const float *add, int add_slices, float *out,
                      int T, int D, float route_scale, int has_add);
+int sw_launch_rmsnorm(const SwLaunchCfg &c, const float *x, const float *w, float *y, int T, int D, float eps);
+int sw_launch_sum_slices(const SwLaunchCfg &c, const float *part, int KS, size_t n, float *y);
 // fp4 (e2m1 + ue8m0 block-32) products of the lag_cuda_* tier (sw_fp4.cu)
 int sw_launch_fp4_rows(const SwLaunchCfg &c, const float *x, const void *P, const void *ES, float *y, int S, int I, int O);
 int sw_launch_fp4_experts(const SwLaunchCfg &c, const float *x, const void *gu_q, const void *gu_es, const void *dn_q,

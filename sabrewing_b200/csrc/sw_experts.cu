@@ -418,3 +418,71 @@ int sw_launch_finish(const SwLaunchCfg &c, const float *routed, const float *add
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
+
+// ---------------------------------------------------------------------------
+// RMSNorm of rows, the reference's rmsnorm_row (c/moe_math.h:58-62): sum of squares in double, inv = 1 / sqrtf(
+// (float)(ss / D) + eps), y = x * inv * w.  One CTA per row; the double partial sums are reduced in a fixed tree.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+k_rmsnorm_rows(const float *__restrict__ x, const float *__restrict__ w, float *__restrict__ y, int T, int D, float eps) {
+    __shared__ double s_part[8];
+    __shared__ float s_inv;
+    for (int r = blockIdx.x; r < T; r += gridDim.x) {
+        const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)r * D);
+        double ss = 0.0;
+        for (int i = threadIdx.x; i < (D >> 2); i += 256) {
+            const float4 v = xr[i];
+            ss += (double)v.x * v.x; ss += (double)v.y * v.y; ss += (double)v.z * v.z; ss += (double)v.w * v.w;
+        }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) ss += __shfl_xor_sync(SW_FULL_MASK, ss, off);
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t = 0.0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) t += s_part[i];
+            s_inv = 1.f / sqrtf((float)(t / D) + eps);
+        }
+        __syncthreads();
+        const float inv = s_inv;
+        const float4 *wr = reinterpret_cast<const float4 *>(w);
+        float4 *yr = reinterpret_cast<float4 *>(y + (size_t)r * D);
+        for (int i = threadIdx.x; i < (D >> 2); i += 256) {
+            const float4 v = xr[i], g = wr[i];
+            yr[i] = make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+        }
+    }
+}
+int sw_launch_rmsnorm(const SwLaunchCfg &c, const float *x, const float *w, float *y, int T, int D, float eps) {
+    if (T <= 0) return 0;
+    if (D % 4) return -1;
+    const int grid = T < c.num_sms * 8 ? T : c.num_sms * 8;
+    k_rmsnorm_rows<<<grid, 256, 0, c.stream>>>(x, w, y, T, D, eps);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// y[i] = sum over the slices, in slice order, of part[k][i]
+__global__ void __launch_bounds__(256)
+k_sum_slices(const float *__restrict__ part, int KS, size_t n4, float *__restrict__ y) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n4; idx += (size_t)gridDim.x * blockDim.x) {
+        float4 a = reinterpret_cast<const float4 *>(part)[idx];
+        for (int k = 1; k < KS; k++) {
+            const float4 b = reinterpret_cast<const float4 *>(part)[(size_t)k * n4 + idx];
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        reinterpret_cast<float4 *>(y)[idx] = a;
+    }
+}
+int sw_launch_sum_slices(const SwLaunchCfg &c, const float *part, int KS, size_t n, float *y) {
+    if (!n) return 0;
+    if (n % 4) return -1;
+    const size_t n4 = n / 4;
+    long long grid = (long long)((n4 + 255) / 256);
+    if (grid > (long long)c.num_sms * 8) grid = (long long)c.num_sms * 8;
+    k_sum_slices<<<(unsigned)grid, 256, 0, c.stream>>>(part, KS, n4, y);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}

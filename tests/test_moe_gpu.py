@@ -549,3 +549,52 @@ def test_two_devices_in_one_process(orc):
         assert blk.status() == 0 and blk.lib.sw_moe_last_path(blk.ctx) == 3
         assert rel_l2(out.cpu().numpy() - case.hin, want["out"] - case.hin) < OUT_TOL
         blk.close()
+
+
+def test_rmsnorm_and_the_layer_tail_on_a_resident_residual_stream(orc):
+    """h += MoE(rmsnorm(h) * w) with h resident on the device (c/laguna.c:1119,1126); the norm alone is the reference's
+    rmsnorm_row (c/moe_math.h:58-62) to the last bit on all but double-rounding coincidences."""
+    from sabrewing_b200 import capi
+    case = synth_case("c2", corr_bias_std=0.01, T=24, D=1024, E=32, K=4, I=256, SI=256)
+    cfg = case.cfg
+    rng = np.random.default_rng(9)
+    h0 = (rng.standard_normal((24, cfg.D)) * 3.0).astype(np.float32)
+    wn = (1 + 0.1 * rng.standard_normal(cfg.D)).astype(np.float32)
+    xn = orc.rmsnorm_rows(h0, wn, 1e-6)
+    lib = capi.lib()
+    hd = torch.from_numpy(h0).cuda(); wd = torch.from_numpy(wn).cuda(); yd = torch.empty_like(hd)
+    assert lib.sw_rmsnorm(hd.data_ptr(), wd.data_ptr(), yd.data_ptr(), 24, cfg.D, 1e-6, None) == 0
+    torch.cuda.synchronize()
+    got = yd.cpu().numpy()
+    assert (got != xn).mean() < 1e-3 and np.abs(got - xn).max() <= 2.4e-7 * np.abs(xn).max()
+    blk, layer, desc = make_block(case)
+    d, l = desc.c(), layer.c()
+    assert lib.sw_moe_forward_norm(blk.ctx, C.byref(d), C.byref(l), hd.data_ptr(), wd.data_ptr(), 1e-6, 24, None) == 0, capi.last_error()
+    torch.cuda.synchronize()
+    assert blk.status() == 0
+    want = orc.moe_group(case.host, xn, h0, exact=1)
+    check_routing(blk.routing(), want)
+    assert rel_l2(hd.cpu().numpy() - h0, want["out"] - h0) < OUT_TOL
+    blk.close()
+
+
+def test_lag_resident_matmuls_on_tensor_cores(orc):
+    """The resident GEMMs either side of the block (c/backend_cuda_laguna.h:32-40) at widths the tensor-core kernels
+    take: few rows (mma.sync) and many rows (tcgen05 for bf16); same bars as the reference's self-test."""
+    from sabrewing_b200 import synth
+    l = _lag()
+    rng = np.random.default_rng(77)
+    I, O = 2048, 1536
+    p = rng.integers(0, 256, (O, I // 2), dtype=np.uint8)
+    sc = (0.01 + rng.random(O, dtype=np.float32) * 0.05).astype(np.float32)
+    Wb = synth.f32_to_bf16(rng.random((O, I), dtype=np.float32) * 2 - 1)
+    dp, ds, dW = _up(l, p), _up(l, sc), _up(l, Wb)
+    for S in (1, 5, 200):
+        x = (rng.random((S, I), dtype=np.float32) * 2 - 1)
+        y = np.empty((S, O), np.float32)
+        assert l.lag_cuda_matmul_q4(y.ctypes.data, x.ctypes.data, dp, ds, S, I, O) == 0
+        assert rel_l2(y, orc.matmul_q4(x, p, sc, 1)) < 1e-5
+        assert l.lag_cuda_matmul_bf16(y.ctypes.data, x.ctypes.data, dW, S, I, O) == 0
+        assert rel_l2(y, orc.matmul_bf16(x, Wb, 1)) < 1e-5
+    for d in (dp, ds, dW):
+        l.lag_cuda_free(d)
