@@ -155,6 +155,14 @@ class MoeBlock:
                                           self._stream(stream)), "sw_moe_forward")
         return out
 
+    def forward_norm(self, desc, layer, h, norm_w, eps, stream=None):
+        """h[T,D] += MoE(rmsnorm(h) * norm_w): the layer tail with the residual stream on the device (c/laguna.c:1119,1126)."""
+        d, l = desc.c(), layer.c()
+        self._last = (h.shape[0], desc.topk, desc.n_experts)
+        self._chk(self.lib.sw_moe_forward_norm(self.ctx, C.byref(d), C.byref(l), h.data_ptr(), norm_w.data_ptr(), eps, h.shape[0],
+                                               self._stream(stream)), "sw_moe_forward_norm")
+        return h
+
     def graph(self, desc, layer, x, out):
         """Capture forward(desc, layer, x, out) into a CUDA graph (runs the block twice on `out` while doing so)."""
         d, l = desc.c(), layer.c()

@@ -568,8 +568,7 @@ def test_rmsnorm_and_the_layer_tail_on_a_resident_residual_stream(orc):
     got = yd.cpu().numpy()
     assert (got != xn).mean() < 1e-3 and np.abs(got - xn).max() <= 2.4e-7 * np.abs(xn).max()
     blk, layer, desc = make_block(case)
-    d, l = desc.c(), layer.c()
-    assert lib.sw_moe_forward_norm(blk.ctx, C.byref(d), C.byref(l), hd.data_ptr(), wd.data_ptr(), 1e-6, 24, None) == 0, capi.last_error()
+    blk.forward_norm(desc, layer, hd, wd, 1e-6)
     torch.cuda.synchronize()
     assert blk.status() == 0
     want = orc.moe_group(case.host, xn, h0, exact=1)
@@ -579,8 +578,9 @@ def test_rmsnorm_and_the_layer_tail_on_a_resident_residual_stream(orc):
 
 
 def test_lag_resident_matmuls_on_tensor_cores(orc):
-    """The resident GEMMs either side of the block (c/backend_cuda_laguna.h:32-40) at widths the tensor-core kernels
-    take: few rows (mma.sync) and many rows (tcgen05 for bf16); same bars as the reference's self-test."""
+    """The resident GEMMs either side of the block (c/backend_cuda_laguna.h:32-40): decode-size calls on the f32 kernels
+    (element-wise bar of the reference's self-test), batched calls on the tensor cores (mma.sync from 16 rows, tcgen05
+    for bf16 from 128)."""
     from sabrewing_b200 import synth
     l = _lag()
     rng = np.random.default_rng(77)
@@ -589,12 +589,14 @@ def test_lag_resident_matmuls_on_tensor_cores(orc):
     sc = (0.01 + rng.random(O, dtype=np.float32) * 0.05).astype(np.float32)
     Wb = synth.f32_to_bf16(rng.random((O, I), dtype=np.float32) * 2 - 1)
     dp, ds, dW = _up(l, p), _up(l, sc), _up(l, Wb)
-    for S in (1, 5, 200):
+    for S in (1, 5, 40, 200):
         x = (rng.random((S, I), dtype=np.float32) * 2 - 1)
         y = np.empty((S, O), np.float32)
         assert l.lag_cuda_matmul_q4(y.ctypes.data, x.ctypes.data, dp, ds, S, I, O) == 0
-        assert rel_l2(y, orc.matmul_q4(x, p, sc, 1)) < 1e-5
+        yc = orc.matmul_q4(x, p, sc, 1)
+        assert rel_l2(y, yc) < 1e-5
         assert l.lag_cuda_matmul_bf16(y.ctypes.data, x.ctypes.data, dW, S, I, O) == 0
-        assert rel_l2(y, orc.matmul_bf16(x, Wb, 1)) < 1e-5
+        yc = orc.matmul_bf16(x, Wb, 1)
+        assert rel_l2(y, yc) < 1e-5
     for d in (dp, ds, dW):
         l.lag_cuda_free(d)
