@@ -86,9 +86,17 @@ int    lag_cuda_moe_experts_fp4(float *out, const float *x,
  * reference has no router that uses it, so it is checked against the CPU
  * restatement only. */
 enum { SW_ROUTE_SIGMOID = 0, SW_ROUTE_SOFTMAX = 1, SW_ROUTE_SOFTPLUS = 2 };
-/* Shared-expert policy: the two modes the reference wires (c/moe_arch.h:25-30,
- * c/moe_block.h:44-51). */
-enum { SW_SHARED_NONE = 0, SW_SHARED_UNSCALED = 1 };
+/* Shared-expert policy.  0, 1 and 3 carry the values of the reference's MoeSharedMode
+ * (c/moe_arch.h:25-30); NONE and UNSCALED are the two that moe_block wires
+ * (c/moe_block.h:44-51).  GATED is the inkling engine's policy (c/inkling.c:1038-1043):
+ * the router has one more row, the shared expert's logit; the combine weights are the
+ * sigmoid scores of the K picks and of the shared expert, normalised to sum 1 over all
+ * K + 1 and multiplied by route_scale * route_global_scale, so the shared expert enters the
+ * sum like one more pick and nothing is scaled afterwards (sigmoid gate only, one shared
+ * expert).  SIGMOID_GATED is the qwen35 engine's (c/qwen35.c:684-699): out += routed *
+ * route_scale + sigmoid(x . sh_gate_w) * shared(x), a one-row gate per token.  SCALED (2)
+ * is not wired in the reference and is refused here. */
+enum { SW_SHARED_NONE = 0, SW_SHARED_UNSCALED = 1, SW_SHARED_GATED = 3, SW_SHARED_SIGMOID_GATED = 4 };
 enum { SW_DTYPE_F32 = 0, SW_DTYPE_BF16 = 1 };
 
 /* Same fields, order and types as MoeDesc (c/moe_arch.h:33-41). */
@@ -123,6 +131,8 @@ typedef struct {
     int gs;                    /* 0: one f32 scale per weight row (c/moe_quant.h:13-14).  >0 (multiple of 32):
                                   one scale per gs columns, gu_s [E*2I, ceil(D/gs)], dn_s [E*D, ceil(I/gs)]
                                   -- the reference's group-scaled int4, c/quant.h:167-202 */
+    const float *sh_gate_w;    /* SW_SHARED_SIGMOID_GATED: f32 [D], the shared expert's one-row gate; else NULL */
+    float route_global_scale;  /* SW_SHARED_GATED: the layer's gate.global_scale (0 is read as 1) */
 } SwMoeLayer;
 
 typedef struct SwMoeCtx SwMoeCtx;
@@ -218,6 +228,18 @@ void sw_ep_destroy(SwEp *ep);
 int  sw_ep_forward(SwEp *ep, const SwMoeDesc *desc, const SwMoeLayer *layer, const float *x, float *out, int T,
                    int scheme, int timed, void *stream);
 int  sw_ep_segments(SwEp *ep, float *ms, int scheme);
+
+/* Container loader: one MoE layer of a Laguna int4 snapshot from its safetensors file(s) (a file
+ * or a directory of them) straight into device memory, in the reference's container layout
+ * (docs/laguna.md:34-42; names as c/laguna.c:410-446 reads them through c/st.h): router
+ * `mlp.gate.weight` F32 or BF16, `mlp.experts.e_score_correction_bias`, fused packed int4
+ * `mlp.experts.gate_up_proj` / `down_proj` with `.qs` row scales, bf16 `mlp.shared_expert.*`.
+ * expert_cnt > 0 reads only the rows of experts [expert_lo, expert_lo + expert_cnt) (an
+ * expert-parallel shard).  *layer then points at device memory owned by *handle. */
+typedef struct SwLoadedLayer SwLoadedLayer;
+int  sw_layer_load(const char *path, int layer_index, int dev, int expert_lo, int expert_cnt,
+                   SwMoeLayer *layer, int *n_experts, SwLoadedLayer **handle);
+void sw_layer_free(SwLoadedLayer *handle);
 
 /* Routing without any allocation (no counterpart in the reference, which sizes its
  * scratch with cudaMalloc on demand, c/backend_cuda_laguna.cu:471-493): router

@@ -10,7 +10,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libsabrewing_b200.so")
 
 ROUTE_SIGMOID, ROUTE_SOFTMAX, ROUTE_SOFTPLUS = 0, 1, 2
-SHARED_NONE, SHARED_UNSCALED = 0, 1
+SHARED_NONE, SHARED_UNSCALED, SHARED_GATED, SHARED_SIGMOID_GATED = 0, 1, 3, 4
 DTYPE_F32, DTYPE_BF16 = 0, 1
 OPT_UMMA_TERMS, OPT_EXPERT_PATH = 1, 2
 EP_REPLICATE, EP_ALLTOALL = 0, 1
@@ -28,7 +28,8 @@ class SwMoeLayer(C.Structure):
                 ("router_w", C.c_void_p), ("corr_bias", C.c_void_p), ("logit_bias", C.c_void_p),
                 ("gu_q", C.c_void_p), ("gu_s", C.c_void_p), ("dn_q", C.c_void_p), ("dn_s", C.c_void_p),
                 ("sh_gate", C.c_void_p), ("sh_up", C.c_void_p), ("sh_down", C.c_void_p),
-                ("expert_lo", C.c_int), ("expert_cnt", C.c_int), ("gs", C.c_int)]
+                ("expert_lo", C.c_int), ("expert_cnt", C.c_int), ("gs", C.c_int),
+                ("sh_gate_w", C.c_void_p), ("route_global_scale", C.c_float)]
 
 
 # name -> (restype, argtypes); every symbol include/sabrewing_b200.h declares
@@ -70,6 +71,8 @@ SIGNATURES = {
     "sw_moe_capture_stream": (_vp, [_vp]),
     "sw_moe_capture_begin": (_i, [_vp]),
     "sw_moe_capture_end": (_i, [_vp, C.POINTER(_vp)]),
+    "sw_layer_load": (_i, [C.c_char_p, _i, _i, _i, _i, _pl, C.POINTER(_i), C.POINTER(_vp)]),
+    "sw_layer_free": (None, [_vp]),
     "sw_moe_route_static": (_i, [_pd, _pl, _vp, _i, _vp, _vp, _vp]),
     "sw_moe_get_routing": (_i, [_vp, _vp, _vp, _vp, C.POINTER(_i), _vp, _vp, _vp, _vp, _vp]),
     "sw_moe_status": (_i, [_vp]),

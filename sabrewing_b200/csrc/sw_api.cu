@@ -114,6 +114,7 @@ struct SwMoeCtx {
     cudaStream_t aux = nullptr;                 // the shared expert runs here, beside routing and the routed experts
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_pack = nullptr;
     SwRouting r{};
+    float *row_gate = nullptr;   // [T] weight of the shared expert per token (GATED / SIGMOID_GATED policies)
     float *glu = nullptr, *slots = nullptr, *sglu = nullptr, *so = nullptr, *routed = nullptr;
     float *dx = nullptr, *dout = nullptr, *hx = nullptr, *hout = nullptr;
     void *xp = nullptr;          // packed fp16 hi/lo copy of x for the tensor-core path
@@ -122,6 +123,7 @@ struct SwMoeCtx {
     void *spk = nullptr;         // packed bf16 hi/lo copy of x for the shared expert
     float *sums = nullptr;       // row sums of x and partial row sums of the SiLU*up rows
     int lastT = 0, lastK = 0, lastE = 0;
+    int lastES = 0;              // row stride of the scores of the last routing (experts + the shared-pool logit, if any)
     int last_path = -1;          // expert kernels of the last experts/forward call (sw_moe_last_path)
     int umma_terms = 1;
     int forced_path = -1;        // SW_OPT_EXPERT_PATH: -1 = choose by shape and group size          // fp16 terms per activation on the tcgen05 path: 1 = hi only, 2 = hi + lo
@@ -177,7 +179,7 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
 
     const size_t T = max_tokens, E = max_experts, K = max_topk, D = max_D, I = max_I, SI = max_SI, P = T * K;
     size_t sizes[] = {
-        T * E * 4,            // scores
+        T * (E + 1) * 4,      // scores (one more column for the shared expert's logit of the shared-pool policy)
         P * 4, P * 4,         // sel, w
         256,                  // G
         E * 4, E * 4, E * 4,  // gexp gbeg gcnt
@@ -185,6 +187,7 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
         256,                  // status
         P * I * 4,            // glu
         P * D * 4,            // slots
+        T * 4 + 256,          // row_gate: per-token weight of a gated shared expert
         T * (SI ? SI : 1) * 4,// sglu
         (((D + 255) / 256) * T * 2 * (SI ? SI : 1) + ((SI + 255) / 256 + 1) * T * D) * 4,   // so: slice partials of the shared expert
         T * D * 4,            // routed
@@ -194,7 +197,7 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
         T * D * 4,            // spk
         P * D * 4,            // um.xg: gathered fp16 hi + lo token rows
         (P / 128 + E + 64) * 8 + 256,   // um.chunks + nchunks
-        ((size_t)((D + 127) / 128) * (T < 128 ? T : 128) + ((size_t)c->num_sms * 32 * 256 + E - 1) / E + T + 64) * E * 8   // rpart
+        ((size_t)((D + 127) / 128) * (T < 128 ? T : 128) + ((size_t)c->num_sms * 32 * 256 + E - 1) / E + T + 64) * (E + 1) * 8   // rpart
     };
     size_t total = 0; for (size_t s : sizes) total += sw_align(s);
     if (sw_malloc(&c->block, total) != cudaSuccess) {
@@ -206,7 +209,7 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
     c->r.scores = (float *)take(); c->r.sel = (int *)take(); c->r.w = (float *)take(); c->r.G = (int *)take();
     c->r.gexp = (int *)take(); c->r.gbeg = (int *)take(); c->r.gcnt = (int *)take();
     c->r.grow = (int *)take(); c->r.rowof = (int *)take(); c->r.status = (int *)take();
-    c->glu = (float *)take(); c->slots = (float *)take(); c->sglu = (float *)take(); c->so = (float *)take();
+    c->glu = (float *)take(); c->slots = (float *)take(); c->row_gate = (float *)take(); c->sglu = (float *)take(); c->so = (float *)take();
     c->routed = (float *)take(); c->dx = (float *)take(); c->dout = (float *)take(); c->xp = take(); c->sums = (float *)take(); c->spk = take(); c->um.xg = take(); { char *q = (char *)take(); c->um.nchunks = (int *)q; c->um.chunks = q + 256; } c->rpart = (double *)take();
     cudaMemsetAsync(c->r.G, 0, 256, c->stream); cudaMemsetAsync(c->r.status, 0, 256, c->stream);
     if (sw_malloc_host((void **)&c->hx, T * D * 4) != cudaSuccess || sw_malloc_host((void **)&c->hout, T * D * 4) != cudaSuccess) {
@@ -245,8 +248,13 @@ static int sw_validate(const SwMoeDesc *d, const SwMoeLayer *L) {
     if (d->n_experts <= 0 || d->n_experts > SW_MAX_EXPERTS) return sw_fail("n_experts=%d outside (0,%d]", d->n_experts, SW_MAX_EXPERTS);
     if (d->topk <= 0 || d->topk > SW_MAX_TOPK || d->topk > d->n_experts) return sw_fail("topk=%d invalid", d->topk);
     if (d->route_act < 0 || d->route_act > 2) return sw_fail("route_act=%d unknown", d->route_act);
-    if (d->shared_mode != SW_SHARED_NONE && d->shared_mode != SW_SHARED_UNSCALED)
-        return sw_fail("shared_mode=%d is not wired (the reference wires NONE and UNSCALED only)", d->shared_mode);
+    if (d->shared_mode != SW_SHARED_NONE && d->shared_mode != SW_SHARED_UNSCALED && d->shared_mode != SW_SHARED_GATED &&
+        d->shared_mode != SW_SHARED_SIGMOID_GATED)
+        return sw_fail("shared_mode=%d is not wired (NONE, UNSCALED, GATED and SIGMOID_GATED are)", d->shared_mode);
+    if (d->shared_mode == SW_SHARED_GATED && (d->route_act != SW_ROUTE_SIGMOID || L->logit_bias || d->n_experts + 1 > SW_MAX_EXPERTS))
+        return sw_fail("shared_mode GATED needs the sigmoid gate, no logit bias and at most %d experts", SW_MAX_EXPERTS - 1);
+    if (d->shared_mode == SW_SHARED_SIGMOID_GATED && (!L->sh_gate_w || ((uintptr_t)L->sh_gate_w & 15)))
+        return sw_fail("shared_mode SIGMOID_GATED needs sh_gate_w (f32 [D], 16-byte aligned)");
     if (L->D <= 0 || L->D % 32) return sw_fail("D=%d must be a positive multiple of 32", L->D);
     if (L->I <= 0 || L->I % 32) return sw_fail("I=%d must be a positive multiple of 32", L->I);
     if (d->shared_mode != SW_SHARED_NONE) {
@@ -403,17 +411,21 @@ static int sw_logits_topk(SwMoeCtx *c, const SwLaunchCfg &cfg, const SwMoeDesc *
     const SwRouting *dr = fuse ? &c->r : nullptr;
     unsigned *ticket = fuse ? (unsigned *)(c->r.status + 16) : nullptr;
     const int force_simt = sw_tuning().force_simt;
+    // shared-pool policy: the router's last row is the shared expert's logit; its normalised weight lands in row_gate
+    const int ns = d->shared_mode == SW_SHARED_GATED ? 1 : 0;
+    const float pool_scale = d->route_scale * (L->route_global_scale != 0.f ? L->route_global_scale : 1.f);
+    float *rg = ns ? c->row_gate : nullptr;
     if (!force_simt && L->D % 32 == 0) {
-        const int KS = sw_router_slices(c->num_sms, T, L->D, E);
-        if (sw_launch_router_dmma(cfg, x, L->router_w, L->router_dtype, c->rpart, T, L->D, E, KS)) return sw_fail("router launch failed");
+        const int KS = sw_router_slices(c->num_sms, T, L->D, E + ns);
+        if (sw_launch_router_dmma(cfg, x, L->router_w, L->router_dtype, c->rpart, T, L->D, E + ns, KS)) return sw_fail("router launch failed");
         if (mark) sw_prof_mark(c, SW_ST_LOGITS, cfg.stream);
         if (sw_launch_route_topk(cfg, c->r.scores, c->rpart, KS, L->logit_bias, L->corr_bias, d->use_corr_bias, d->route_act,
-                                 d->norm_topk, T, E, K, c->r.sel, c->r.w, dr, ticket)) return sw_fail("route_topk launch failed");
+                                 d->norm_topk, T, E, K, c->r.sel, c->r.w, dr, ticket, ns, pool_scale, rg)) return sw_fail("route_topk launch failed");
     } else {
-        if (sw_launch_router_logits(cfg, x, L->router_w, L->router_dtype, L->logit_bias, c->r.scores, T, L->D, E)) return sw_fail("router_logits launch failed");
+        if (sw_launch_router_logits(cfg, x, L->router_w, L->router_dtype, L->logit_bias, c->r.scores, T, L->D, E + ns)) return sw_fail("router_logits launch failed");
         if (mark) sw_prof_mark(c, SW_ST_LOGITS, cfg.stream);
         if (sw_launch_route_topk(cfg, c->r.scores, nullptr, 0, nullptr, L->corr_bias, d->use_corr_bias, d->route_act,
-                                 d->norm_topk, T, E, K, c->r.sel, c->r.w, dr, ticket)) return sw_fail("route_topk launch failed");
+                                 d->norm_topk, T, E, K, c->r.sel, c->r.w, dr, ticket, ns, pool_scale, rg)) return sw_fail("route_topk launch failed");
     }
     if (mark) sw_prof_mark(c, SW_ST_TOPK, cfg.stream);
     if (!fuse && sw_launch_dispatch(cfg, c->r, T, K, E)) return sw_fail("dispatch launch failed");
@@ -424,7 +436,7 @@ static int sw_route_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, c
     SwLaunchCfg cfg{c->num_sms, st, c->dev};
     const int E = d->n_experts, K = d->topk;
     if (sw_logits_topk(c, cfg, d, L, x, T, false)) return -1;      // the top-k kernel's last CTA also runs the dispatch
-    c->last_stream = st; c->lastT = T; c->lastK = K; c->lastE = E;
+    c->last_stream = st; c->lastT = T; c->lastK = K; c->lastE = E; c->lastES = E + (d->shared_mode == SW_SHARED_GATED ? 1 : 0);
     return 0;
 }
 
@@ -486,6 +498,18 @@ static int sw_shared_stage(SwMoeCtx *c, const SwMoeLayer *L, const float *x, int
     if (sw_shared_run(cfg, L, x, T, c->spk, c->sglu, c->so, so, so_slices, nullptr, nullptr, c->r.status)) return sw_fail("shared expert launch failed");
     return 0;
 }
+// the per-token weight of the shared expert: none (plain add), the pool weight the router left in row_gate, or the
+// one-row sigmoid gate computed here
+static int sw_shared_gate(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, int T, cudaStream_t st, const float **gate) {
+    *gate = nullptr;
+    if (d->shared_mode == SW_SHARED_GATED) *gate = c->row_gate;
+    if (d->shared_mode == SW_SHARED_SIGMOID_GATED) {
+        SwLaunchCfg cfg{c->num_sms, st, c->dev};
+        if (sw_launch_row_gate(cfg, x, L->sh_gate_w, c->row_gate, T, L->D)) return sw_fail("shared gate launch failed");
+        *gate = c->row_gate;
+    }
+    return 0;
+}
 
 extern "C" int sw_moe_route(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L, const float *x, int T, void *stream) {
     SW_GATE();
@@ -535,7 +559,7 @@ extern "C" int sw_moe_experts_routed(SwMoeCtx *c, const SwMoeDesc *d, const SwMo
     if (w != c->r.w) SW_CUDA(cudaMemcpyAsync(c->r.w, w, nb, cudaMemcpyDeviceToDevice, st));
     SwLaunchCfg cfg{c->num_sms, st, c->dev};
     if (sw_launch_dispatch(cfg, c->r, T, K, E)) return sw_fail("dispatch launch failed");
-    c->last_stream = st; c->lastT = T; c->lastK = K; c->lastE = E;
+    c->last_stream = st; c->lastT = T; c->lastK = K; c->lastE = E; c->lastES = E;
     if (sw_expert_stage(c, d, L, x, T, st)) return -1;
     int lo, cnt; sw_resident(d, L, &lo, &cnt);
     if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, nullptr, 0, routed, T, K, L->D, 1.f, 0, lo, cnt)) return sw_fail("combine launch failed");
@@ -550,6 +574,7 @@ extern "C" int sw_moe_shared(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *
     if (sw_validate_rows(x, x, x, "shared")) return -1;
     float *so = nullptr; int so_slices = 1;
     if (sw_shared_stage(c, L, x, T, (cudaStream_t)stream, &so, &so_slices)) return -1;
+    if (d->shared_mode == SW_SHARED_SIGMOID_GATED) { const float *gt; if (sw_shared_gate(c, d, L, x, T, (cudaStream_t)stream, &gt)) return -1; }
     c->shared_T = T; c->shared_so = so; c->shared_slices = so_slices;
     return 0;
 }
@@ -563,9 +588,16 @@ extern "C" int sw_moe_finish(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *
     SwLaunchCfg cfg{c->num_sms, st, c->dev};
     const int has_shared = d->shared_mode != SW_SHARED_NONE;
     float *so = nullptr; int so_slices = 1;
-    if (has_shared && c->shared_T == T) { so = c->shared_so; so_slices = c->shared_slices; c->shared_T = -1; }   // left by sw_moe_shared
-    else if (has_shared && sw_shared_stage(c, L, x, T, st, &so, &so_slices)) return -1;
-    if (sw_launch_finish(cfg, routed, so, so_slices, out, T, L->D, d->route_scale, has_shared)) return sw_fail("finish launch failed");
+    const float *gate = nullptr;
+    if (has_shared && c->shared_T == T) {                                     // left by sw_moe_shared (with its gate)
+        so = c->shared_so; so_slices = c->shared_slices; c->shared_T = -1;
+        if (d->shared_mode == SW_SHARED_GATED || d->shared_mode == SW_SHARED_SIGMOID_GATED) gate = c->row_gate;
+    } else if (has_shared) {
+        if (sw_shared_stage(c, L, x, T, st, &so, &so_slices) || sw_shared_gate(c, d, L, x, T, st, &gate)) return -1;
+    }
+    // shared-pool policy: the weights already carry route_scale
+    const float scale = d->shared_mode == SW_SHARED_GATED ? 1.f : d->route_scale;
+    if (sw_launch_finish(cfg, routed, so, so_slices, out, T, L->D, scale, has_shared, gate)) return sw_fail("finish launch failed");
     return 0;
 }
 
@@ -614,6 +646,7 @@ static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
     struct MarkCtx { SwMoeCtx *c; cudaStream_t st; } mc{c, st};
     auto smark = [](void *p, int which) { MarkCtx *m = (MarkCtx *)p; sw_prof_mark(m->c, which == 0 ? SW_ST_SH_GATEUP : SW_ST_SH_DOWN, m->st); };
     float *so = nullptr; int so_slices = 1;
+    const float *gate = nullptr;                   // per-token weight of a gated shared expert
     // The shared expert depends only on x: outside stage profiling it runs on the
     // context's second stream, forked here and joined before the combine.
     const bool overlap = has_shared && !c->prof_on;
@@ -637,13 +670,14 @@ static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
     if (overlap) {
         SwLaunchCfg acfg{c->num_sms, c->aux, c->dev};
         if (sw_shared_run(acfg, L, x, T, c->spk, c->sglu, c->so, &so, &so_slices, nullptr, nullptr, c->r.status)) return sw_fail("shared expert launch failed");
+        if (d->shared_mode == SW_SHARED_SIGMOID_GATED && sw_shared_gate(c, d, L, x, T, c->aux, &gate)) return -1;
         SW_CUDA(cudaEventRecord(c->ev_join, c->aux));
     }
 
     sw_prof_mark(c, -1, st);
     if (sw_logits_topk(c, cfg, d, L, x, T, true)) return -1;       // the top-k kernel's last CTA also runs the dispatch
     sw_prof_mark(c, SW_ST_DISPATCH, st);
-    c->last_stream = st; c->lastT = T; c->lastK = K; c->lastE = E;
+    c->last_stream = st; c->lastT = T; c->lastK = K; c->lastE = E; c->lastES = E + (d->shared_mode == SW_SHARED_GATED ? 1 : 0);
 
     auto mark = [](void *p, int which) { MarkCtx *m = (MarkCtx *)p; sw_prof_mark(m->c, which == 0 ? SW_ST_GATEUP : SW_ST_DOWN, m->st); };
     if (prepack) SW_CUDA(cudaStreamWaitEvent(st, c->ev_pack, 0));
@@ -654,12 +688,15 @@ static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
         sw_prof_mark(c, SW_ST_SH_GATEUP, st); sw_prof_mark(c, SW_ST_SH_DOWN, st);
     } else if (has_shared) {
         if (sw_shared_run(cfg, L, x, T, c->spk, c->sglu, c->so, &so, &so_slices, smark, &mc, c->r.status)) return sw_fail("shared expert launch failed");
+        if (d->shared_mode == SW_SHARED_SIGMOID_GATED && sw_shared_gate(c, d, L, x, T, st, &gate)) return -1;
     } else {
         sw_prof_mark(c, SW_ST_SH_GATEUP, st); sw_prof_mark(c, SW_ST_SH_DOWN, st);
     }
     if (c->wait_res) SW_CUDA(cudaStreamWaitEvent(st, c->ev_res, 0));         // forward_host: the residual rows are on their way
+    if (d->shared_mode == SW_SHARED_GATED) gate = c->row_gate;              // written by the top-k kernel of this call
+    const int scale_bit = d->shared_mode == SW_SHARED_GATED ? 0 : 1;         // pool weights already carry route_scale
     if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, so, so_slices, out, T, K, L->D,
-                          d->route_scale, 1 | (has_shared ? 2 : 0) | (accumulate ? 4 : 0), lo, cnt)) return sw_fail("combine launch failed");
+                          d->route_scale, scale_bit | (has_shared ? 2 : 0) | (accumulate ? 4 : 0), lo, cnt, gate)) return sw_fail("combine launch failed");
     sw_prof_mark(c, SW_ST_COMBINE, st);
     if (c->prof_on && c->prof_calls < SW_PROF_MAX_CALLS) c->prof_calls++;
     return 0;
@@ -791,7 +828,7 @@ extern "C" int sw_moe_get_routing(SwMoeCtx *c, int *sel, float *w, float *scores
     const size_t P = (size_t)c->lastT * c->lastK, E = c->lastE;
     if (sel)    SW_CUDA(cudaMemcpy(sel, c->r.sel, P * 4, cudaMemcpyDeviceToHost));
     if (w)      SW_CUDA(cudaMemcpy(w, c->r.w, P * 4, cudaMemcpyDeviceToHost));
-    if (scores) SW_CUDA(cudaMemcpy(scores, c->r.scores, (size_t)c->lastT * E * 4, cudaMemcpyDeviceToHost));
+    if (scores) SW_CUDA(cudaMemcpy2D(scores, E * 4, c->r.scores, (size_t)(c->lastES > 0 ? c->lastES : (int)E) * 4, E * 4, (size_t)c->lastT, cudaMemcpyDeviceToHost));
     if (G)      SW_CUDA(cudaMemcpy(G, c->r.G, 4, cudaMemcpyDeviceToHost));
     if (gexp)   SW_CUDA(cudaMemcpy(gexp, c->r.gexp, E * 4, cudaMemcpyDeviceToHost));
     if (gbeg)   SW_CUDA(cudaMemcpy(gbeg, c->r.gbeg, E * 4, cudaMemcpyDeviceToHost));

@@ -88,7 +88,10 @@ int sw_launch_router_dmma(const SwLaunchCfg &c, const float *x, const void *W, i
 int sw_launch_route_topk(const SwLaunchCfg &c, float *scores, const double *part, int KS, const float *lbias,
                          const float *corr_bias, int use_bias,
                          int route_act, int norm_topk, int T, int E, int K, int *sel, float *w,
-                         const SwRouting *dr = nullptr, unsigned *ticket = nullptr);
+                         const SwRouting *dr = nullptr, unsigned *ticket = nullptr,
+                         int ns = 0, float pool_scale = 1.f, float *row_gate = nullptr);
+// row_gate[t] = sigmoid(x[t] . g) with the dot accumulated in fp64 (a one-row gate of the shared expert)
+int sw_launch_row_gate(const SwLaunchCfg &c, const float *x, const float *g, float *row_gate, int T, int D);
 int sw_launch_dispatch(const SwLaunchCfg &c, const SwRouting &r, int T, int K, int E);
 
 // sw_experts.cu
@@ -145,9 +148,9 @@ int sw_launch_q8_rows(const SwLaunchCfg &c, const float *x, const int8_t *W, con
 // `add` holds add_slices consecutive [T,D] arrays that are summed in order.
 int sw_launch_combine(const SwLaunchCfg &c, const float *slots, const int *rowof, const int *sel,
                       const float *w, const float *add, int add_slices, float *out, int T, int K, int D,
-                      float route_scale, int mode, int expert_lo, int expert_cnt);
+                      float route_scale, int mode, int expert_lo, int expert_cnt, const float *row_gate = nullptr);
 int sw_launch_finish(const SwLaunchCfg &c, const float *routed, const float *add, int add_slices, float *out,
-                     int T, int D, float route_scale, int has_add);
+                     int T, int D, float route_scale, int has_add, const float *row_gate = nullptr);
 int sw_launch_rmsnorm(const SwLaunchCfg &c, const float *x, const float *w, float *y, int T, int D, float eps);
 int sw_launch_sum_slices(const SwLaunchCfg &c, const float *part, int KS, size_t n, float *y);
 // fp4 (e2m1 + ue8m0 block-32) products of the lag_cuda_* tier (sw_fp4.cu)

@@ -329,7 +329,7 @@ int sw_launch_q8_rows(const SwLaunchCfg &c, const float *x, const int8_t *W, con
 __global__ void __launch_bounds__(256)
 k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const int *__restrict__ sel,
           const float *__restrict__ w, const float *__restrict__ add, int add_slices, float *__restrict__ out,
-          int T, int K, int D, float route_scale, int mode, int expert_lo, int expert_cnt) {
+          int T, int K, int D, float route_scale, int mode, int expert_lo, int expert_cnt, const float *__restrict__ row_gate) {
     const int D4 = D >> 2;
     const size_t n = (size_t)T * D4;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
@@ -366,6 +366,7 @@ k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const 
                 const float4 s2 = reinterpret_cast<const float4 *>(add)[(size_t)k * n + idx];
                 s.x += s2.x; s.y += s2.y; s.z += s2.z; s.w += s2.w;
             }
+            if (row_gate) { const float gt = row_gate[t]; s.x *= gt; s.y *= gt; s.z *= gt; s.w *= gt; }   // gated shared expert
             acc.x += s.x; acc.y += s.y; acc.z += s.z; acc.w += s.w;
         }
         float4 *o = reinterpret_cast<float4 *>(out) + idx;
@@ -376,13 +377,13 @@ k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const 
 
 int sw_launch_combine(const SwLaunchCfg &c, const float *slots, const int *rowof, const int *sel,
                       const float *w, const float *add, int add_slices, float *out, int T, int K, int D,
-                      float route_scale, int mode, int expert_lo, int expert_cnt) {
+                      float route_scale, int mode, int expert_lo, int expert_cnt, const float *row_gate) {
     if (T <= 0) return 0;
     if (D % 4) return -1;
     size_t n = (size_t)T * (D / 4);
     long long grid = (long long)((n + 255) / 256);
     if (grid > (long long)c.num_sms * 16) grid = (long long)c.num_sms * 16;
-    k_combine<<<(unsigned)grid, 256, 0, c.stream>>>(slots, rowof, sel, w, add, add_slices, out, T, K, D, route_scale, mode, expert_lo, expert_cnt);
+    k_combine<<<(unsigned)grid, 256, 0, c.stream>>>(slots, rowof, sel, w, add, add_slices, out, T, K, D, route_scale, mode, expert_lo, expert_cnt, row_gate);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
@@ -390,7 +391,7 @@ int sw_launch_combine(const SwLaunchCfg &c, const float *slots, const int *rowof
 // out += routed*route_scale (+ add)
 __global__ void __launch_bounds__(256)
 k_finish(const float *__restrict__ routed, const float *__restrict__ add, int add_slices, float *__restrict__ out,
-         size_t n4, float route_scale, int has_add) {
+         size_t n4, float route_scale, int has_add, const float *__restrict__ row_gate, int D4) {
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n4; idx += (size_t)gridDim.x * blockDim.x) {
         float4 a = reinterpret_cast<const float4 *>(routed)[idx];
         a.x *= route_scale; a.y *= route_scale; a.z *= route_scale; a.w *= route_scale;
@@ -400,6 +401,7 @@ k_finish(const float *__restrict__ routed, const float *__restrict__ add, int ad
                 const float4 s2 = reinterpret_cast<const float4 *>(add)[(size_t)k * n4 + idx];
                 s.x += s2.x; s.y += s2.y; s.z += s2.z; s.w += s2.w;
             }
+            if (row_gate) { const float gt = row_gate[idx / D4]; s.x *= gt; s.y *= gt; s.z *= gt; s.w *= gt; }
             a.x += s.x; a.y += s.y; a.z += s.z; a.w += s.w;
         }
         float4 h = reinterpret_cast<float4 *>(out)[idx];
@@ -408,13 +410,13 @@ k_finish(const float *__restrict__ routed, const float *__restrict__ add, int ad
     }
 }
 int sw_launch_finish(const SwLaunchCfg &c, const float *routed, const float *add, int add_slices, float *out,
-                     int T, int D, float route_scale, int has_add) {
+                     int T, int D, float route_scale, int has_add, const float *row_gate) {
     if (T <= 0) return 0;
     if (D % 4) return -1;
     size_t n4 = (size_t)T * (D / 4);
     long long grid = (long long)((n4 + 255) / 256);
     if (grid > (long long)c.num_sms * 16) grid = (long long)c.num_sms * 16;
-    k_finish<<<(unsigned)grid, 256, 0, c.stream>>>(routed, add, add_slices, out, n4, route_scale, has_add);
+    k_finish<<<(unsigned)grid, 256, 0, c.stream>>>(routed, add, add_slices, out, n4, route_scale, has_add, row_gate, D / 4);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
@@ -483,6 +485,33 @@ int sw_launch_sum_slices(const SwLaunchCfg &c, const float *part, int KS, size_t
     long long grid = (long long)((n4 + 255) / 256);
     if (grid > (long long)c.num_sms * 8) grid = (long long)c.num_sms * 8;
     k_sum_slices<<<(unsigned)grid, 256, 0, c.stream>>>(part, KS, n4, y);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// row_gate[t] = 1 / (1 + expf(-(float)(x[t] . g))): the one-row sigmoid gate of a shared expert (the reference's
+// qwen35 engine, c/qwen35.c:689-697: matmul_f32 in its exact mode, i.e. a double dot rounded to f32, then the gate).
+// One warp per row, fp64 partial sums reduced in a fixed tree.
+__global__ void __launch_bounds__(256)
+k_row_gate(const float *__restrict__ x, const float *__restrict__ g, float *__restrict__ row_gate, int T, int D) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 8 + warp;
+    if (t >= T) return;
+    const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)t * D), *gr = reinterpret_cast<const float4 *>(g);
+    double a = 0.0;
+    for (int i = lane; i < (D >> 2); i += 32) {
+        const float4 v = xr[i], w = gr[i];
+        a = fma((double)v.x, (double)w.x, a); a = fma((double)v.y, (double)w.y, a);
+        a = fma((double)v.z, (double)w.z, a); a = fma((double)v.w, (double)w.w, a);
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) a += __shfl_xor_sync(SW_FULL_MASK, a, off);
+    if (lane == 0) { const float gv = (float)a; row_gate[t] = 1.f / (1.f + (float)exp(-(double)gv)); }
+}
+int sw_launch_row_gate(const SwLaunchCfg &c, const float *x, const float *g, float *row_gate, int T, int D) {
+    if (T <= 0) return 0;
+    if (D % 4) return -1;
+    k_row_gate<<<(T + 7) / 8, 256, 0, c.stream>>>(x, g, row_gate, T, D);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -197,6 +197,7 @@ extern "C" int sw_moe_route_static(const SwMoeDesc *d, const SwMoeLayer *L, cons
     if (d->topk <= 0 || d->topk > SW_MAX_TOPK || d->topk > d->n_experts) return sw_noalloc_fail("route_static: bad topk");
     if (d->route_act < 0 || d->route_act > 2 || !L->router_w) return sw_noalloc_fail("route_static: bad route_act or missing router weights");
     if (L->router_dtype != SW_DTYPE_F32 && L->router_dtype != SW_DTYPE_BF16) return sw_noalloc_fail("route_static: unknown router_dtype");
+    if (d->shared_mode == SW_SHARED_GATED) return sw_noalloc_fail("route_static: the shared-pool policy (SW_SHARED_GATED) is not served here");
     // x and the router rows are read with 128-bit loads
     if (((uintptr_t)x | (uintptr_t)L->router_w) & 15) return sw_noalloc_fail("route_static: x and router_w must be 16-byte aligned");
     if (((uintptr_t)sel | (uintptr_t)w | (uintptr_t)L->corr_bias | (uintptr_t)L->logit_bias) & 3) return sw_noalloc_fail("route_static: sel, w and the bias arrays must be 4-byte aligned");

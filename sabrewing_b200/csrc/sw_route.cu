@@ -282,9 +282,13 @@ __device__ __forceinline__ float sw_expf_cr(float v) { return (float)exp((double
 // from -1e30f, ties to the lower id, an expert is taken once; if nothing compares greater (all NaN or <= -1e30f) the
 // lowest id not yet taken.  Lane l keeps the values of experts l, l+32, ... in registers; a round is a local scan, a
 // warp max over an order-preserving integer key and a warp min over the ids that hold that maximum.
+// pool (optional): the shared expert shares the routed weight pool (the reference's MOE_SHARED_GATED policy,
+// c/inkling.c:1038-1043): weights are the gate scores of the K picks and of the shared expert (s_sc[E]), normalised
+// to sum 1 over all K + 1 (float sum: the picks in rank order, then the shared one) and multiplied by pool_scale;
+// the shared expert's weight goes to *gate_t.
 template <int NJ>
 __device__ __forceinline__ void sw_topk_warp(const float *s_sb, const float *s_sc, int E, int K, int norm_topk,
-                                             int *sel_t, float *w_t) {
+                                             int *sel_t, float *w_t, bool pool = false, float pool_scale = 1.f, float *gate_t = nullptr) {
     const int lane = threadIdx.x & 31;
     float v[NJ];
 #pragma unroll
@@ -318,7 +322,15 @@ __device__ __forceinline__ void sw_topk_warp(const float *s_sb, const float *s_s
         if (lane == a) wsel = s_sc[best];
         if (lane == 0) sel_t[a] = (int)best;
     }
-    if (norm_topk) {                             // float sum in rank order, then divide
+    if (pool) {
+        float sm = 0.f;
+        for (int a = 0; a < K; a++) sm += __shfl_sync(SW_FULL_MASK, wsel, a);
+        const float ws = s_sc[E];
+        sm += ws;
+        const float f = pool_scale / sm;
+        wsel *= f;
+        if (lane == 0 && gate_t) *gate_t = ws * f;
+    } else if (norm_topk) {                      // float sum in rank order, then divide
         float sm = 0.f;
         for (int a = 0; a < K; a++) sm += __shfl_sync(SW_FULL_MASK, wsel, a);
         wsel = wsel / sm;
@@ -334,24 +346,27 @@ __global__ void __launch_bounds__(256)
 k_route_topk(float *__restrict__ scores, const double *__restrict__ part, int KS, const float *__restrict__ lbias,
              const float *__restrict__ corr_bias, int use_bias,
              int route_act, int norm_topk, int T, int E, int K,
-             int *__restrict__ sel, float *__restrict__ w, SwRouting dr, unsigned *ticket) {
+             int *__restrict__ sel, float *__restrict__ w, SwRouting dr, unsigned *ticket,
+             int ns, float pool_scale, float *__restrict__ row_gate) {
     extern __shared__ int sw_dyn_i[];
     __shared__ float s_sc[SW_MAX_EXPERTS], s_sb[SW_MAX_EXPERTS];
     __shared__ int s_last;
     __shared__ float s_redf[8];
     __shared__ double s_redd[8];
     const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    float *r = scores + (size_t)t * E;
+    // ns = 1: the router has one more row, the shared expert's logit (sigmoid gate only); it takes no part in the selection
+    const int ET = E + ns;
+    float *r = scores + (size_t)t * ET;
     const bool ub = use_bias && corr_bias != nullptr;
 
     // logits
-    for (int e = tid; e < E; e += 256) {
+    for (int e = tid; e < ET; e += 256) {
         float v;
         if (part) {
             // slice partials are loaded 32 or eight at a time (independent loads) and added in slice order
             double a = 0.0;
-            const double *pp = part + (size_t)t * E + e;
-            const size_t stride = (size_t)T * E;
+            const double *pp = part + (size_t)t * ET + e;
+            const size_t stride = (size_t)T * ET;
             int ks = 0;
             for (; ks + 32 <= KS; ks += 32) {
                 double p[32];
@@ -369,7 +384,7 @@ k_route_topk(float *__restrict__ scores, const double *__restrict__ part, int KS
             }
             for (; ks < KS; ks++) a += pp[(size_t)ks * stride];
             v = (float)a;
-            if (lbias) v += lbias[e];
+            if (lbias && e < E) v += lbias[e];
         } else v = r[e];
         s_sc[e] = v;
     }
@@ -399,7 +414,7 @@ k_route_topk(float *__restrict__ scores, const double *__restrict__ part, int KS
         const float inv = (float)(1.0 / sum);
         for (int e = tid; e < E; e += 256) s_sc[e] = s_sb[e] * inv;
     } else if (route_act == 0) {                 // sigmoid
-        for (int e = tid; e < E; e += 256) s_sc[e] = 1.f / (1.f + sw_expf_cr(-s_sc[e]));
+        for (int e = tid; e < ET; e += 256) s_sc[e] = 1.f / (1.f + sw_expf_cr(-s_sc[e]));
     } else {                                     // softplus
         for (int e = tid; e < E; e += 256) {
             const float v = s_sc[e];
@@ -407,17 +422,19 @@ k_route_topk(float *__restrict__ scores, const double *__restrict__ part, int KS
         }
     }
     __syncthreads();
-    for (int e = tid; e < E; e += 256) {
+    for (int e = tid; e < ET; e += 256) {
         const float sc = s_sc[e];
         r[e] = sc;                               // keep the scores for inspection
-        s_sb[e] = sc + (ub ? corr_bias[e] : 0.f);
+        if (e < E) s_sb[e] = sc + (ub ? corr_bias[e] : 0.f);
     }
     __syncthreads();
     if (warp == 0) {
         const int nj = (E + 31) >> 5;
-        if (nj <= 8) sw_topk_warp<8>(s_sb, s_sc, E, K, norm_topk, sel + (size_t)t * K, w + (size_t)t * K);
-        else if (nj <= 16) sw_topk_warp<16>(s_sb, s_sc, E, K, norm_topk, sel + (size_t)t * K, w + (size_t)t * K);
-        else sw_topk_warp<32>(s_sb, s_sc, E, K, norm_topk, sel + (size_t)t * K, w + (size_t)t * K);
+        const bool pool = ns > 0;
+        float *gt = row_gate ? row_gate + t : nullptr;
+        if (nj <= 8) sw_topk_warp<8>(s_sb, s_sc, E, K, norm_topk, sel + (size_t)t * K, w + (size_t)t * K, pool, pool_scale, gt);
+        else if (nj <= 16) sw_topk_warp<16>(s_sb, s_sc, E, K, norm_topk, sel + (size_t)t * K, w + (size_t)t * K, pool, pool_scale, gt);
+        else sw_topk_warp<32>(s_sb, s_sc, E, K, norm_topk, sel + (size_t)t * K, w + (size_t)t * K, pool, pool_scale, gt);
     }
     if (!ticket) return;
 
@@ -437,9 +454,9 @@ k_route_topk(float *__restrict__ scores, const double *__restrict__ part, int KS
 int sw_launch_route_topk(const SwLaunchCfg &c, float *scores, const double *part, int KS, const float *lbias,
                          const float *corr_bias, int use_bias,
                          int route_act, int norm_topk, int T, int E, int K, int *sel, float *w,
-                         const SwRouting *dr, unsigned *ticket) {
+                         const SwRouting *dr, unsigned *ticket, int ns, float pool_scale, float *row_gate) {
     if (T <= 0) return 0;
-    if (E > SW_MAX_EXPERTS || K > SW_MAX_TOPK || K > E || K <= 0) return -1;
+    if (E + ns > SW_MAX_EXPERTS || K > SW_MAX_TOPK || K > E || K <= 0 || ns < 0 || ns > 1 || (ns && route_act != 0)) return -1;
     static SwPerDevice attr_done;
     if (attr_done.get(c.dev, [] {
             if (cudaFuncSetAttribute(k_route_topk, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024) != cudaSuccess) { cudaGetLastError(); return -1; }
@@ -448,7 +465,7 @@ int sw_launch_route_topk(const SwLaunchCfg &c, float *scores, const double *part
     const bool fuse = dr && ticket;
     size_t smem = fuse ? (size_t)(256 / 32 + 2) * E * sizeof(int) : 0;
     k_route_topk<<<T, 256, smem, c.stream>>>(scores, part, KS, lbias, corr_bias, use_bias, route_act, norm_topk, T, E, K, sel, w,
-                                             fuse ? *dr : none, fuse ? ticket : nullptr);
+                                             fuse ? *dr : none, fuse ? ticket : nullptr, ns, pool_scale, row_gate);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -71,6 +71,8 @@ class MoeLayer:
         self.gu_q, self.gu_s = _dev(gu_q, device), _dev(gu_s, device)
         self.dn_q, self.dn_s = _dev(dn_q, device), _dev(dn_s, device)
         self.sh_gate, self.sh_up, self.sh_down = (_dev(a.get(k), device) for k in ("sh_gate", "sh_up", "sh_down"))
+        self.sh_gate_w = _dev(a.get("sh_gate_w"), device)                 # qwen35-style one-row gate of the shared expert
+        self.route_global_scale = float(a.get("route_global_scale", 0.0) or 0.0)
 
     @staticmethod
     def _p(t):
@@ -80,7 +82,8 @@ class MoeLayer:
         p = self._p
         return capi.SwMoeLayer(self.D, self.I, self.SI, self.router_dtype, p(self.router_w), p(self.corr_bias),
                                p(self.logit_bias), p(self.gu_q), p(self.gu_s), p(self.dn_q), p(self.dn_s),
-                               p(self.sh_gate), p(self.sh_up), p(self.sh_down), self.expert_lo, self.expert_cnt, self.gs)
+                               p(self.sh_gate), p(self.sh_up), p(self.sh_down), self.expert_lo, self.expert_cnt, self.gs,
+                               p(self.sh_gate_w), self.route_global_scale)
 
     def expert_bytes(self):
         return sum(t.numel() * t.element_size() for t in (self.gu_q, self.gu_s, self.dn_q, self.dn_s))

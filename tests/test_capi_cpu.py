@@ -50,7 +50,7 @@ def test_struct_layouts_match_reference_descriptor():
     assert [f[0] for f in capi.SwMoeDesc._fields_] == ["n_experts", "topk", "route_act", "use_corr_bias",
                                                      "norm_topk", "route_scale", "shared_mode"]
     assert C.sizeof(capi.SwMoeDesc) == 28
-    assert C.sizeof(capi.SwMoeLayer) == 16 + 10 * 8 + 16      # 4 ints, 10 pointers, 3 ints + padding
+    assert C.sizeof(capi.SwMoeLayer) == 16 + 10 * 8 + 16 + 16   # 4 ints, 10 pointers, 3 ints + padding, pointer, float + padding
 
 
 def test_calls_fail_cleanly_without_a_device():
@@ -86,7 +86,7 @@ def _layer(**kw):
     from sabrewing_b200 import capi
     base = dict(D=128, I=64, SI=0, router_dtype=capi.DTYPE_BF16, router_w=0x1000, corr_bias=None, logit_bias=None,
                 gu_q=0x2000, gu_s=0x3000, dn_q=0x4000, dn_s=0x5000, sh_gate=None, sh_up=None, sh_down=None,
-                expert_lo=0, expert_cnt=0, gs=0)
+                expert_lo=0, expert_cnt=0, gs=0, sh_gate_w=None, route_global_scale=0.0)
     base.update(kw)
     return capi.SwMoeLayer(*[base[f[0]] for f in capi.SwMoeLayer._fields_])
 

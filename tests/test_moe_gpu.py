@@ -600,3 +600,78 @@ def test_lag_resident_matmuls_on_tensor_cores(orc):
         assert rel_l2(y, yc) < 1e-5
     for d in (dp, ds, dW):
         l.lag_cuda_free(d)
+
+
+def _sigmoid_f32(v):
+    v = np.asarray(v, np.float32)
+    return (np.float32(1) / (np.float32(1) + np.exp(-v.astype(np.float64)).astype(np.float32))).astype(np.float32)
+
+
+def test_sigmoid_gated_shared_expert(orc):
+    """The qwen35 engine's policy (c/qwen35.c:684-699): out += routed * route_scale + sigmoid(x . g) * shared(x), with the
+    gate dot in the exact (double) contract."""
+    from sabrewing_b200 import capi
+    from sabrewing_b200.moe_block import MoeBlock, MoeLayer, MoeDesc
+    case = synth_case("c2", corr_bias_std=0.01, T=20, D=512, E=32, K=4, I=128, SI=128)
+    cfg = case.cfg
+    rng = np.random.default_rng(21)
+    case.a["sh_gate_w"] = (rng.standard_normal(cfg.D) * 0.05).astype(np.float32)
+    blk = MoeBlock("cuda:0", 20, cfg.E, cfg.K, cfg.D, cfg.I, cfg.SI)
+    layer = MoeLayer(cfg.D, cfg.I, cfg.SI, case.a, "cuda:0")
+    desc = MoeDesc(cfg.E, cfg.K, cfg.route_act, cfg.use_corr_bias, cfg.norm_topk, cfg.route_scale, capi.SHARED_SIGMOID_GATED)
+    x = torch.from_numpy(case.x).cuda(); out = torch.from_numpy(case.hin).cuda()
+    blk.forward(desc, layer, x, out)
+    torch.cuda.synchronize()
+    assert blk.status() == 0
+    sel, w = orc.route(case.host, case.x, exact=1)
+    assert np.array_equal(blk.routing()["sel"], sel)
+    routed = orc.experts_given_routing(case.host, case.x, sel, w, exact=1)
+    gv = orc.matmul_f32(case.x, case.a["sh_gate_w"].reshape(1, -1), exact=1)[:, 0]
+    want = routed * np.float32(cfg.route_scale) + _sigmoid_f32(gv)[:, None] * orc.shared_rows(case.host, case.x, exact=1)
+    assert rel_l2(out.cpu().numpy() - case.hin, want) < OUT_TOL
+    # the staged calls (shared ahead of finish) give the same rows
+    out2 = torch.from_numpy(case.hin).cuda(); r = torch.empty_like(x)
+    blk.shared(desc, layer, x); blk.route(desc, layer, x); blk.experts(desc, layer, x, r); blk.finish(desc, layer, x, r, out2)
+    torch.cuda.synchronize()
+    assert rel_l2(out2.cpu().numpy(), out.cpu().numpy()) < 1e-6
+    blk.close()
+
+
+def test_shared_expert_in_the_routed_weight_pool(orc):
+    """The inkling engine's policy (c/inkling.c:1029-1043): the router has one more row (the shared expert's logit); the
+    weights are the sigmoids of the K picks and of the shared expert, normalised over all K + 1 and multiplied by
+    route_scale * global scale; selection by sigmoid + bias as usual."""
+    from sabrewing_b200 import capi, synth
+    from sabrewing_b200.moe_block import MoeBlock, MoeLayer, MoeDesc
+    case = synth_case("c2", corr_bias_std=0.01, T=20, D=512, E=32, K=4, I=128, SI=128)
+    cfg = case.cfg
+    rng = np.random.default_rng(22)
+    extra = synth.f32_to_bf16((rng.standard_normal((1, cfg.D)) * 0.02).astype(np.float32))
+    rb = np.concatenate([case.a["router_bf16"], extra]); rw = synth.bf16_to_f32(rb)
+    a = dict(case.a); a["router_bf16"] = rb; a["router_w"] = rw; a["route_global_scale"] = 1.5
+    blk = MoeBlock("cuda:0", 20, cfg.E, cfg.K, cfg.D, cfg.I, cfg.SI)
+    layer = MoeLayer(cfg.D, cfg.I, cfg.SI, a, "cuda:0")
+    desc = MoeDesc(cfg.E, cfg.K, capi.ROUTE_SIGMOID, 1, 0, 2.5, capi.SHARED_GATED)
+    x = torch.from_numpy(case.x).cuda(); out = torch.from_numpy(case.hin).cuda()
+    blk.forward(desc, layer, x, out)
+    torch.cuda.synchronize()
+    assert blk.status() == 0
+    # restatement: exact logits of all E + 1 rows, sigmoid, top-K of score + bias over the E experts, pooled weights
+    sc = _sigmoid_f32(orc.matmul_f32(case.x, rw, exact=1))
+    sel = np.stack([orc.topk(sc[t, :cfg.E].copy(), case.a["corr_bias"], 1, cfg.K) for t in range(20)])
+    w = np.take_along_axis(sc[:, :cfg.E], sel, axis=1).astype(np.float32)
+    ws = sc[:, cfg.E]
+    sm = np.zeros(20, np.float32)
+    for k in range(cfg.K):
+        sm = (sm + w[:, k]).astype(np.float32)
+    sm = (sm + ws).astype(np.float32)
+    f = (np.float32(np.float32(2.5) * np.float32(1.5)) / sm).astype(np.float32)
+    wn = (w * f[:, None]).astype(np.float32); wsn = (ws * f).astype(np.float32)
+    got = blk.routing(want_scores=True)
+    assert np.array_equal(got["sel"], sel)
+    assert (np.abs(got["w"] - wn) / np.abs(wn)).max() < W_TOL
+    assert np.array_equal(got["scores"], sc[:, :cfg.E])
+    routed = orc.experts_given_routing(case.host, case.x, sel, wn, exact=1)
+    want = routed + wsn[:, None] * orc.shared_rows(case.host, case.x, exact=1)
+    assert rel_l2(out.cpu().numpy() - case.hin, want) < OUT_TOL
+    blk.close()
