@@ -6,27 +6,36 @@
 // the B operand, f32 accumulators in tensor memory.  A CTA work item is a chunk times
 // a PAIR of weight tiles that share the chunk's activation tiles (gate/up: the gate
 // rows of 128 outputs and their up rows, so SiLU(gate)*up is lane-local in the
-// epilogue; down: two neighbouring tiles).  K runs in slots of 64 columns through a
-// ring of shared-memory slots (six with one fp16 term, four with two).  Fifteen warps, four roles:
-//   warp 12      TMA producer: per slot the raw int4 rows of both tiles (2 x 128 rows
-//                x 32 B) and the fp16 activation tile(s) (R rows x 128 B, 128B swizzle =
-//                the K-major canonical layout the tensor core reads)
-//   warps 0-7    dequantise, two groups of four: group t turns the raw rows of tile t
-//                into exact fp16 integers (nibble - 8) stored as swizzled 128-byte rows
-//                of one of four A tiles in flight
-//   warps 13,14  MMA issuers, one thread each, one per tile of the pair:
-//                tcgen05.mma kind::f16 per 16-column step against the hi tile and, with
-//                two terms, against the lo tile (x = hi + lo) into the same accumulator
-//                columns; one tcgen05.commit per slot returns the slot and the A tiles
-//   warps 8-11   epilogue: tcgen05.ld the two accumulators of the item (two buffers
-//                alternate, so the next item's MMAs overlap this epilogue), apply the
-//                per-row scales and SiLU(gate)*up, or store the f32 slot rows
+// epilogue; down: two neighbouring tiles).  K runs in steps of 128 columns.  Fifteen
+// warps, four roles:
+//   warp 12      TMA producer: per step the raw int4 rows of both tiles (2 x 128 rows x
+//                64 B, 64-byte swizzle) and the fp16 activation tiles (two 64-column
+//                sub-tiles of R rows x 128 B per term, 128B swizzle = the K-major
+//                canonical layout the tensor core reads) into a ring of four 48-KB slots
+//                (two 80-KB slots with two terms)
+//   warps 0-7    dequantise, two groups of four: a thread owns one row of tile t, reads
+//                its 64 raw bytes of the step from the slot, expands them to 128 exact
+//                fp16 integers (nibble - 8) in registers and stores them with tcgen05.st
+//                into one of four A tiles in TENSOR MEMORY (64 columns each)
+//   warps 13,14  MMA issuers, one thread each, one per tile of the pair: eight
+//                tcgen05.mma kind::f16 per step with the A operand in tensor memory and B
+//                through its shared-memory descriptor (with two terms a second MMA
+//                against the lo tile into the same accumulator columns); one
+//                tcgen05.commit per step returns the slot and the step's A tiles
+//   warps 8-11   epilogue: tcgen05.ld the two accumulators of the item, apply the per-row
+//                scales and SiLU(gate)*up, or store the f32 slot rows.  The accumulators
+//                have ONE buffer (tensor memory: 256 columns of accumulators + 256 of A
+//                tiles), so the dequantising warps, idle at that point, take two thirds
+//                of every item's epilogue.
+// Why the A operand sits in tensor memory: with both operands in shared memory an
+// M = 128, N = 128, K = 16 MMA reads 8 KB in its 64 cycles, all the shared-memory
+// bandwidth of an SM, and the dequantised tiles crossed it once more on their way in.
 //
 // Activations are fp16 arrays [rows, K] whose columns are permuted inside every group
 // of eight to 0,4,1,5,2,6,3,7 -- the order in which the nibble masks deliver a weight
-// word -- so a dequantised word is one 16-byte chunk of the A tile.  `terms` = 1 feeds
-// the tensor core fp16(x) alone (relative rounding 2^-12 per element); `terms` = 2 adds
-// the residual lo = fp16(x - hi) as a second MMA per step (f32-level accuracy, twice the
+// word -- so the K order of a dequantised row matches.  `terms` = 1 feeds the tensor
+// core fp16(x) alone (relative rounding 2^-12 per element); `terms` = 2 adds the
+// residual lo = fp16(x - hi) as a second MMA per step (f32-level accuracy, twice the
 // tensor work).  The token rows of gate/up are gathered into packed-slot order by
 // k_umma_gather (the reference gathers too, c/laguna.c:742-743).
 //
@@ -37,18 +46,25 @@
 #include <cuda_fp16.h>
 #include <stdlib.h>
 
-#define UM_MAX_STAGES 6
-#define UM_RAW_A 4096                    // 128 rows x 32 B of int4
-#define UM_BT 16384                      // one activation tile: 128 rows x 128 B
-// A ring slot holds the raw rows of a pair of weight tiles and the activation tile(s) they share: 24 KB with one
-// fp16 term (six slots in flight), 40 KB with two (four slots).  The ring's depth is what hides the latency of the
-// weight stream: a slot is refilled only when its MMAs have retired.
-#define UM_STAGE_BYTES(terms) (2 * UM_RAW_A + (terms) * UM_BT)
-#define UM_STAGES_FOR(terms) ((terms) == 1 ? 6 : 4)
-#define UM_RING_BYTES (4 * UM_STAGE_BYTES(2))        // 160 KB: four slots of 40 KB, or six of 24 KB
-#define UM_A16 16384                     // dequantised A tile: 128 rows x 64 fp16
+#define UM_RAW_A 8192                    // raw int4 of one weight tile and step: 128 rows x 64 B (128 columns)
+#define UM_BT 16384                      // one activation sub-tile: 128 rows x 128 B (64 columns)
 #define UM_WAIT_LIMIT (1u << 24)
-#define UM_ABUF 4                        // dequantised A tiles in flight
+// K runs in steps of 128 columns.  A ring slot holds, for one step, the raw int4 rows of a pair of weight tiles
+// (2 x 8 KB, 64-byte rows under the 64-byte TMA swizzle so that a thread reads its row without bank conflicts) and
+// the fp16 activation tiles they share (two 64-column sub-tiles of 16 KB per term): 48 KB with one term (four
+// slots), 80 KB with two (two slots).  The dequantised weight tiles do NOT live in shared memory: they go from
+// registers into tensor memory (tcgen05.st) and the MMAs take their A operand from there.  With both operands in
+// shared memory an M = 128, N = 128, K = 16 MMA reads 8 KB in its 64 cycles, which is all the shared-memory
+// bandwidth an SM has (128 B/cycle), and the dequantised tiles crossed it a second time on their way in.
+#define UM_STAGE_BYTES(terms) (2 * UM_RAW_A + 2 * (terms) * UM_BT)
+#define UM_STAGES_FOR(terms) ((terms) == 1 ? 4 : 2)
+#define UM_MAX_STAGES 4
+#define UM_RING_BYTES (4 * UM_STAGE_BYTES(1))        // 192 KB: four slots of 48 KB, or two of 80 KB
+// Tensor memory (512 columns): the two accumulators of an item in columns [0, 256) (one buffer), and a ring of four
+// dequantised A tiles -- two steps of a tile pair, 64 columns each (128 rows x 128 fp16) -- in columns [256, 512).
+#define UM_A_SLOTS 2
+#define UM_ABUF (2 * UM_A_SLOTS)
+#define UM_TMEM_A 256
 #define UM_DQ_WARPS 8
 #define UM_THREADS ((UM_DQ_WARPS + 4 + 3) * 32)   // dequant, epilogue, TMA, two MMA issuers
 
@@ -83,6 +99,19 @@ __device__ __forceinline__ void um_mma(unsigned d_tmem, uint64_t adesc, uint64_t
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// A operand in tensor memory (128 lanes x 8 columns of two fp16 each per K = 16), B through its shared-memory descriptor
+__device__ __forceinline__ void um_mma_ta(unsigned d_tmem, unsigned a_tmem, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 :: "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 consecutive columns of this thread's lane (the caller waits with tcgen05.wait::st)
+__device__ __forceinline__ void um_st32_nowait(unsigned taddr, const uint32_t (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                 :: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                    "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                    "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                    "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
 __device__ __forceinline__ void um_commit(unsigned bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
 }
@@ -97,6 +126,16 @@ __device__ __forceinline__ void um_ld32(unsigned taddr, float (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void um_ld16(unsigned taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
 }
 // 8 nibbles -> 8 fp16 (nibble-8) in the order c0,c4,c1,c5,c2,c6,c3,c7
 __device__ __forceinline__ uint4 um_dq(uint32_t w) {
@@ -183,12 +222,11 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
           const __grid_constant__ CUtensorMap tmL64, const __grid_constant__ CUtensorMap tmL128,
           const UmArgs a) {
     extern __shared__ unsigned char um_dyn[];
-    __shared__ unsigned long long b_raw_full[UM_MAX_STAGES], b_raw_free[UM_MAX_STAGES], b_a_full[UM_ABUF], b_a_free[UM_ABUF], b_acc_full[4], b_acc_free[2];
+    __shared__ unsigned long long b_raw_full[UM_MAX_STAGES], b_raw_free[UM_MAX_STAGES], b_a_full[UM_ABUF], b_acc_full[2], b_acc_free;
     __shared__ unsigned s_tmem;
     __shared__ int s_abort;
     unsigned char *smem = (unsigned char *)(((uintptr_t)um_dyn + 1023) & ~(uintptr_t)1023);
     const unsigned STG = UM_STAGES_FOR(a.terms), SBYTES = UM_STAGE_BYTES(a.terms);   // ring depth and slot size
-    unsigned char *a16 = smem + UM_RING_BYTES;                          // UM_ABUF dequantised A tiles
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KD = a.KD, OUT = a.OUT;
     const int nrows_w = GATEUP ? 2 * OUT : OUT;
@@ -196,19 +234,19 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
     // gate/up: the gate rows of 128 outputs and their up rows; down: two neighbouring tiles (256 outputs).
     constexpr int OPP = GATEUP ? 128 : 256;                             // outputs per pair
     const int pairs = OUT / OPP;
-    const int NST = KD >> 6;                                            // 64-column stages per tile
+    const int NST = KD >> 7;                                            // 128-column steps per tile
     const int items = *a.nchunks * pairs;
     volatile int *abortp = &s_abort;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < UM_MAX_STAGES; i++) { um_bar_init(um_s32(&b_raw_full[i]), 1); um_bar_init(um_s32(&b_raw_free[i]), 2); }
-        for (int i = 0; i < UM_ABUF; i++) { um_bar_init(um_s32(&b_a_full[i]), UM_DQ_WARPS / 2); um_bar_init(um_s32(&b_a_free[i]), 1); }
-        for (int i = 0; i < 4; i++) um_bar_init(um_s32(&b_acc_full[i]), 1);
-        for (int i = 0; i < 2; i++) um_bar_init(um_s32(&b_acc_free[i]), 4);
+        for (int i = 0; i < UM_ABUF; i++) um_bar_init(um_s32(&b_a_full[i]), UM_DQ_WARPS / 2);
+        for (int i = 0; i < 2; i++) um_bar_init(um_s32(&b_acc_full[i]), 1);
+        um_bar_init(um_s32(&b_acc_free), 12);                           // four epilogue warps and the eight dequantising warps
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == UM_DQ_WARPS + 5) {                                      // tensor memory: two 256-column accumulators (hi | lo halves)
+    if (warp == UM_DQ_WARPS + 5) {                                      // all 512 columns of tensor memory
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(um_s32(&s_tmem)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -227,6 +265,66 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
     // Raw rows: the 128 rows of tile 0 (gate rows), then the 128 rows of tile 1 (up rows).
     auto tile_rows = [](int n) { return n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : 128; };
     const bool two_terms = a.terms == 2;
+
+    // The epilogue of an item, shared by three warps per tensor-memory lane quarter (the quarter's epilogue warp and its
+    // two dequantising warps, which have nothing to dequantise until the accumulators are free again): blocks of 16
+    // token columns are dealt round robin, share `part` of 3.  There is one accumulator buffer, so this time is not
+    // hidden under MMAs: it has to be short.
+    auto epilogue_share = [&](int item, unsigned nitem, int part, bool &clamped) -> bool {
+        const int q = warp & 3, trow = q * 32 + lane;                   // lane quarter of this warp, tile row of this thread
+        int gi, c0, pr; decode(item, gi, c0, pr);
+        const int e = a.gexp[gi] - a.expert_lo, n = min(128, a.gcnt[gi] - c0), row0 = a.gbeg[gi] + c0;
+        const float *ws = a.Ws + (size_t)e * nrows_w;
+        if (!um_bar_wait(um_s32(&b_acc_full[0]), nitem & 1, abortp) ||
+            !um_bar_wait(um_s32(&b_acc_full[1]), nitem & 1, abortp)) {
+            if (lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; }
+            return false;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned t0 = tmem + ((unsigned)(q * 32) << 16), t1 = t0 + 128;   // tile 0 / tile 1 of this lane
+        if (GATEUP) {
+            // lane r holds gate row r in tile 0 and up row r in tile 1: output o = pair*128 + r
+            const int o = pr * 128 + trow;
+            const float sg = o < OUT ? ws[o] : 0.f, su = o < OUT ? ws[OUT + o] : 0.f;
+            __half *Yh = reinterpret_cast<__half *>(a.Y0), *Yl = reinterpret_cast<__half *>(a.Y1);
+            const int pcol = um_perm8(o);
+            for (int cb = 16 * part; cb < n; cb += 48) {
+                float g[16], u[16];
+                um_ld16(t0 + cb, g);
+                um_ld16(t1 + cb, u);
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    if (cb + j < n && o < OUT) {
+                        const float gv = g[j] * sg;
+                        const float y = (gv / (1.f + expf(-gv))) * (u[j] * su);
+                        __half hi, lo; um_split(y, hi, lo);
+                        clamped |= fabsf(y) > 65504.f;
+                        const size_t pos = (size_t)(row0 + cb + j) * OUT + pcol;
+                        Yh[pos] = hi;
+                        if (two_terms) Yl[pos] = lo;
+                    }
+                }
+            }
+        } else {
+            float *Y = reinterpret_cast<float *>(a.Y0);
+#pragma unroll
+            for (int t = 0; t < 2; t++) {
+                const int o = pr * 256 + t * 128 + trow;
+                const float sc = o < OUT ? ws[o] : 0.f;
+                for (int cb = 16 * part; cb < n; cb += 48) {
+                    float v[16];
+                    um_ld16((t ? t1 : t0) + cb, v);
+#pragma unroll
+                    for (int j = 0; j < 16; j++)
+                        if (cb + j < n && o < OUT) Y[(size_t)(row0 + cb + j) * OUT + o] = v[j] * sc;
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) um_bar_arrive(um_s32(&b_acc_free));
+        return true;
+    };
 
     if (warp == UM_DQ_WARPS + 4) {
         // ------------------------------ TMA producer ------------------------------
@@ -247,32 +345,34 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
                     }
                     unsigned char *sp = smem + s * SBYTES;
                     const unsigned bar = um_s32(&b_raw_full[s]);
-                    um_bar_expect(bar, rawA + (two_terms ? 2u : 1u) * bt);
-                    um_tma_2d(um_s32(sp), &tmW, sl * 32, wrow, bar);                                  // 128 rows
-                    um_tma_2d(um_s32(sp + rawA / 2), &tmW, sl * 32, wrow + (GATEUP ? OUT : 128), bar);  // 128 rows
-                    um_tma_2d(um_s32(sp + rawA), th, sl * 64, row0, bar);
-                    if (two_terms) um_tma_2d(um_s32(sp + rawA + bt), tl, sl * 64, row0, bar);
+                    um_bar_expect(bar, rawA + (two_terms ? 4u : 2u) * bt);
+                    um_tma_2d(um_s32(sp), &tmW, sl * 64, wrow, bar);                                  // 128 rows x 64 B
+                    um_tma_2d(um_s32(sp + rawA / 2), &tmW, sl * 64, wrow + (GATEUP ? OUT : 128), bar);
+                    um_tma_2d(um_s32(sp + rawA), th, sl * 128, row0, bar);                             // columns [128 sl, +64)
+                    um_tma_2d(um_s32(sp + rawA + bt), th, sl * 128 + 64, row0, bar);                   // columns [128 sl + 64, +64)
+                    if (two_terms) {
+                        um_tma_2d(um_s32(sp + rawA + 2 * bt), tl, sl * 128, row0, bar);
+                        um_tma_2d(um_s32(sp + rawA + 3 * bt), tl, sl * 128 + 64, row0, bar);
+                    }
                 }
             }
         }
     } else if (warp >= UM_DQ_WARPS + 5) {
         // ------------------------------ MMA issuers ------------------------------
-        // Two warps, one thread each: issuer t multiplies tile t of the pair into its own accumulator columns.
-        // A lone thread pays the full latency of every instruction (a barrier test ~100 cycles, a tcgen05.commit ~250,
-        // an MMA issue ~55), so one thread cannot keep up with 8 MMAs per 1024 cycles; two can.
+        // Two warps, one thread each: issuer t multiplies tile t of the pair into its own accumulator columns
+        // [128 t, 128 t + R).  One MMA of N = R per 16 columns and term: A (the dequantised weights) from tensor
+        // memory, B (the fp16 activations) from the slot.
         if (lane == 0) {
             const int t = warp - (UM_DQ_WARPS + 5);
-            unsigned ks = 0, nitem = 0;                                  // ring-slot and item counters
+            unsigned ks = 0, nitem = 0;                                  // step and item counters
             for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, nitem++) {
                 int gi, c0, pr; decode(item, gi, c0, pr);
                 const int n = min(128, a.gcnt[gi] - c0);
-                // Two MMAs of N = R per 16 columns, A*hi then A*lo, accumulate into the SAME R accumulator columns, so a
-                // tile needs 128 columns at most and tensor memory holds two buffers of two tiles: the epilogue of one
-                // item runs under the MMAs of the next.
                 const int R = tile_rows(n);
                 const unsigned idesc = (1u << 4) | ((unsigned)(R >> 3) << 17) | ((128u >> 4) << 24);   // f32 accum, f16 x f16, K-major
-                const unsigned q = nitem & 1, d_tmem = tmem + (q * 2 + t) * 128;
-                if (nitem >= 2 && !um_bar_wait(um_s32(&b_acc_free[q]), ((nitem >> 1) - 1) & 1, abortp)) {
+                const unsigned d_tmem = tmem + (unsigned)t * 128;
+                // one accumulator buffer: the previous item's epilogue has to have read it
+                if (nitem >= 1 && !um_bar_wait(um_s32(&b_acc_free), (nitem - 1) & 1, abortp)) {
                     atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -280,132 +380,78 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
                 bool ok = true;
                 for (int st = 0; st < NST; st++, ks++) {
                     const unsigned s = ks % STG, kk = 2 * ks + t, b = kk % UM_ABUF;
+                    // the dequantising warps announce a tile only after they have seen the slot land (raw rows AND activations)
                     if (!um_bar_wait(um_s32(&b_a_full[b]), (kk / UM_ABUF) & 1, abortp)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t da = um_desc(um_s32(a16 + b * UM_A16));
-                    const uint64_t dh = um_desc(um_s32(smem + s * SBYTES + 2 * UM_RAW_A)), dl = um_desc(um_s32(smem + s * SBYTES + 2 * UM_RAW_A + bt));
+                    const unsigned ta = tmem + UM_TMEM_A + b * 64;
+                    const unsigned bb = um_s32(smem + s * SBYTES + 2 * UM_RAW_A);
 #pragma unroll
-                    for (int k = 0; k < 4; k++) {                       // 16 columns = 32 bytes per step
-                        um_mma(d_tmem, da + 2 * k, dh + 2 * k, idesc, (st | k) ? 1u : 0u);
-                        if (two_terms) um_mma(d_tmem, da + 2 * k, dl + 2 * k, idesc, 1u);
+                    for (int k = 0; k < 8; k++) {                       // 16 columns per MMA: 8 tensor-memory columns of A, 32 bytes of each B row
+                        const uint64_t dh = um_desc(bb + (k >> 2) * bt) + 2 * (k & 3);
+                        um_mma_ta(d_tmem, ta + 8 * k, dh, idesc, (st | k) ? 1u : 0u);
+                        if (two_terms) um_mma_ta(d_tmem, ta + 8 * k, um_desc(bb + (2 + (k >> 2)) * bt) + 2 * (k & 3), idesc, 1u);
                     }
-                    // one commit per slot and issuer: when both have arrived the slot returns to the TMA warp and the
-                    // pair's dequantised tiles to the dequantising warps
+                    // one commit per step and issuer: when both have arrived the slot returns to the TMA warp and the
+                    // step's two A tiles to the dequantising warps
                     um_commit(um_s32(&b_raw_free[s]));
                 }
                 if (!ok) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
-                um_commit(um_s32(&b_acc_full[q * 2 + t]));
+                um_commit(um_s32(&b_acc_full[t]));
             }
         }
     } else if (warp < UM_DQ_WARPS) {
         // ------------------------------ dequantise ------------------------------
-        // Two groups of four warps: group t dequantises tile t of every slot into A tile (2*slot + t) % 4.  Four warps
-        // per tile keep the chain wait -> load -> convert -> store -> fence -> arrive short (it sits on the loop
-        // "slot s-2 done -> tile of slot s ready -> MMAs of slot s").
-        // A thread converts two 16-byte pieces q = tg + 128*i of the tile's raw rows; consecutive lanes read consecutive
-        // pieces (no bank conflicts on the loads).  Piece q is half (q & 1) of the tile's raw row q/2.
-        const int tsel = warp >> 2, tg = threadIdx.x & 127;
-        unsigned slot_base = 0;
-        for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
-            int gi, c0, pr; decode(item, gi, c0, pr);
-            const int pitch = 32;                                       // bytes per raw row in the slot
-            int rawoff[2], dstoff[2];
-#pragma unroll
-            for (int i = 0; i < 2; i++) {
-                const int q = tg + 128 * i, rr = q >> 1, h = q & 1;     // the tile's row 0..127, half
-                const int trow = rr;
-                const int srow = tsel * 128 + rr;                       // row in the slot
-                rawoff[i] = srow * pitch + h * 16;
-                dstoff[i] = trow * 128 + (((h * 4) ^ (trow & 7)) << 4);  // chunk (4h + j) goes to (4h + j) ^ (trow & 7)
-            }
-            for (int st = 0; st < NST; st++) {
-                const unsigned ks = slot_base + st, kk = 2 * ks + tsel, b = kk % UM_ABUF;
-                const unsigned s = ks % STG;
+        // Two groups of four warps: group t dequantises tile t of every step.  A thread owns one tile row (tensor-memory
+        // lane 32 * (warp % 4) + lane): it reads the row's 32 raw bytes of the step from the slot, expands them to 64 exact
+        // fp16 integers (nibble - 8) in 32 registers and stores them to the 32 columns of A tile (2 * step + t) % 8.
+        const int tsel = warp >> 2, q = warp & 3;
+        const int trow = q * 32 + lane;
+        const unsigned lane_base = (unsigned)(q * 32) << 16;
+        unsigned ks = 0, nitem = 0;
+        bool clamped = false;
+        for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, nitem++) {
+            for (int st = 0; st < NST; st++, ks++) {
+                const unsigned kk = 2 * ks + tsel, b = kk % UM_ABUF, s = ks % STG;
                 bool ok = um_bar_wait(um_s32(&b_raw_full[s]), (ks / STG) & 1, abortp);
-                // A tile b was last read by the MMAs of the slot two back: wait until that slot is done
-                if (ok && ks >= 2) ok = um_bar_wait(um_s32(&b_raw_free[(ks - 2) % STG]), ((ks - 2) / STG) & 1, abortp);
+                // A tile b was last read by the MMAs of the step UM_A_SLOTS back: wait until that step has retired
+                if (ok && ks >= UM_A_SLOTS) ok = um_bar_wait(um_s32(&b_raw_free[(ks - UM_A_SLOTS) % STG]), ((ks - UM_A_SLOTS) / STG) & 1, abortp);
                 if (!ok) { if (lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; } break; }
-                const unsigned char *raw = smem + s * SBYTES;
-                unsigned char *dstb = a16 + b * UM_A16;
-                uint4 w[2];
+                // the row's 64 bytes; the TMA wrote them under the 64-byte swizzle: 16-byte chunk c sits at c ^ ((row >> 1) & 3)
+                const unsigned char *rrow = smem + s * SBYTES + (size_t)(tsel * 128 + trow) * 64;
+                const int sw = (trow >> 1) & 3;
+                uint4 wv[4];
 #pragma unroll
-                for (int i = 0; i < 2; i++) w[i] = *reinterpret_cast<const uint4 *>(raw + rawoff[i]);
+                for (int c = 0; c < 4; c++) wv[c] = *reinterpret_cast<const uint4 *>(rrow + ((c ^ sw) << 4));
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (int i = 0; i < 2; i++) {
-                    // (4h + j) ^ x7 == ((4h) ^ x7) ^ j for j < 4: the four chunks of a half are the base slot xor j
-                    unsigned char *d = dstb + (dstoff[i] & ~0x7F);
-                    const int base = (dstoff[i] >> 4) & 7;
-                    *reinterpret_cast<uint4 *>(d + ((base ^ 0) << 4)) = um_dq(w[i].x);
-                    *reinterpret_cast<uint4 *>(d + ((base ^ 1) << 4)) = um_dq(w[i].y);
-                    *reinterpret_cast<uint4 *>(d + ((base ^ 2) << 4)) = um_dq(w[i].z);
-                    *reinterpret_cast<uint4 *>(d + ((base ^ 3) << 4)) = um_dq(w[i].w);
+                for (int hf = 0; hf < 2; hf++) {                        // two independent halves of 64 columns
+                    uint32_t r[32];
+                    const uint32_t ww[8] = {wv[2 * hf].x, wv[2 * hf].y, wv[2 * hf].z, wv[2 * hf].w,
+                                            wv[2 * hf + 1].x, wv[2 * hf + 1].y, wv[2 * hf + 1].z, wv[2 * hf + 1].w};
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {                       // word i: columns 8i .. 8i+7 in the order 0,4,1,5,2,6,3,7
+                        const uint4 d = um_dq(ww[i]);
+                        r[4 * i] = d.x; r[4 * i + 1] = d.y; r[4 * i + 2] = d.z; r[4 * i + 3] = d.w;
+                    }
+                    um_st32_nowait(tmem + lane_base + UM_TMEM_A + b * 64 + hf * 32, r);
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic stores -> tensor-core reads
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) um_bar_arrive(um_s32(&b_a_full[b]));
             }
-            slot_base += NST;
+            if (*abortp) break;
+            // this item's tiles are all handed over: help with its epilogue (nothing can be dequantised into the A ring
+            // until the MMAs that read it have retired, and those are the ones the accumulators are waiting for)
+            if (!epilogue_share(item, nitem, 1 + tsel, clamped)) break;
         }
+        if (clamped) atomicOr(a.status, SW_ST_RANGE);
     } else {
-        // ------------------------------ epilogue (four warps, one TMEM lane quarter each) ------------------------------
-        const int q = warp & 3;                                         // TMEM lane quarter of this warp
-        const int trow = q * 32 + lane;                                 // tile row held by this thread
+        // ------------------------------ epilogue warps (one TMEM lane quarter each; share 0 of 3) ------------------------------
         unsigned nitem = 0;
         bool clamped = false;
-        for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, nitem++) {
-            int gi, c0, pr; decode(item, gi, c0, pr);
-            const int e = a.gexp[gi] - a.expert_lo, n = min(128, a.gcnt[gi] - c0), row0 = a.gbeg[gi] + c0;
-            const float *ws = a.Ws + (size_t)e * nrows_w;
-            const unsigned qb = nitem & 1;                              // accumulator buffer of this item
-            if (!um_bar_wait(um_s32(&b_acc_full[qb * 2]), (nitem >> 1) & 1, abortp) ||
-                !um_bar_wait(um_s32(&b_acc_full[qb * 2 + 1]), (nitem >> 1) & 1, abortp)) {
-                if (lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; }
-                break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const unsigned t0 = tmem + qb * 256 + ((unsigned)(q * 32) << 16), t1 = t0 + 128;   // tile 0 / tile 1 of this lane
-            if (GATEUP) {
-                // lane r holds gate row r in tile 0 and up row r in tile 1: output o = pair*128 + r
-                const int o = pr * 128 + trow;
-                const float sg = o < OUT ? ws[o] : 0.f, su = o < OUT ? ws[OUT + o] : 0.f;
-                __half *Yh = reinterpret_cast<__half *>(a.Y0), *Yl = reinterpret_cast<__half *>(a.Y1);
-                const int pcol = um_perm8(o);
-                for (int cb = 0; cb < n; cb += 32) {
-                    float g[32], u[32];
-                    um_ld32(t0 + cb, g);
-                    um_ld32(t1 + cb, u);
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        if (cb + j < n && o < OUT) {
-                            const float gv = g[j] * sg;
-                            const float y = (gv / (1.f + expf(-gv))) * (u[j] * su);
-                            __half hi, lo; um_split(y, hi, lo);
-                            clamped |= fabsf(y) > 65504.f;
-                            const size_t pos = (size_t)(row0 + cb + j) * OUT + pcol;
-                            Yh[pos] = hi;
-                            if (two_terms) Yl[pos] = lo;
-                        }
-                    }
-                }
-            } else {
-                float *Y = reinterpret_cast<float *>(a.Y0);
-#pragma unroll
-                for (int t = 0; t < 2; t++) {
-                    const int o = pr * 256 + t * 128 + trow;
-                    const float sc = o < OUT ? ws[o] : 0.f;
-                    for (int cb = 0; cb < n; cb += 32) {
-                        float v[32];
-                        um_ld32((t ? t1 : t0) + cb, v);
-#pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (cb + j < n && o < OUT) Y[(size_t)(row0 + cb + j) * OUT + o] = v[j] * sc;
-                    }
-                }
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) um_bar_arrive(um_s32(&b_acc_free[qb]));
-        }
+        for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, nitem++)
+            if (!epilogue_share(item, nitem, 0, clamped)) break;
         if (clamped) atomicOr(a.status, SW_ST_RANGE);
     }
 
@@ -472,17 +518,18 @@ int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_h
     if (a.max_rows <= 0) return 0;
     if (terms != 1 && terms != 2) return -1;
     if (terms == 1) act_lo = act_hi;                                    // never read; keeps the tensor maps valid
-    if (a.KD % 64 || a.OUT <= 0 || ((uintptr_t)a.q & 15)) return -1;
+    if (a.KD % 128 || a.OUT <= 0 || ((uintptr_t)a.q & 15)) return -1;
     if ((a.OUT % (gateup ? 128 : 256)) != 0) return -1;                  // whole tile pairs only
     CUtensorMap tw, th[4], tl[4];
-    if (um_make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.q, a.KD / 2, wrows_total, 32, 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
+    if (um_make_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.q, a.KD / 2, wrows_total, 64, 128, CU_TENSOR_MAP_SWIZZLE_64B)) return -1;
     const int R[4] = {16, 32, 64, 128};
     for (int i = 0; i < 4; i++) {
         if (um_make_map(&th[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act_hi, a.KD, a.max_rows, 64, R[i], CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
         if (um_make_map(&tl[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act_lo, a.KD, a.max_rows, 64, R[i], CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
     }
     static_assert(UM_STAGES_FOR(1) * UM_STAGE_BYTES(1) <= UM_RING_BYTES && UM_STAGES_FOR(2) * UM_STAGE_BYTES(2) <= UM_RING_BYTES, "ring sizes");
-    constexpr int SMEM = UM_RING_BYTES + UM_ABUF * UM_A16 + 1024;
+    static_assert(UM_A_SLOTS <= UM_STAGES_FOR(1) && UM_A_SLOTS <= UM_STAGES_FOR(2), "an A tile's release is read off the slot barrier of its step");
+    constexpr int SMEM = UM_RING_BYTES + 1024;
     static SwPerDevice attr;
     if (attr.get(c.dev, [] {
             if (cudaFuncSetAttribute(k_q4_umma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
