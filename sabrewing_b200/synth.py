@@ -44,6 +44,8 @@ CONFIGS = {
     "c3": MoeConfig("c3", 4096, 256, 10, 1024, 1024, ROUTE_SIGMOID, 1, 1, 2.5, SHARED_UNSCALED, 4096, 2, zipf=1.1),
     "c4": MoeConfig("c4", 5120, 384, 8, 1536, 0, ROUTE_SOFTMAX, 0, 0, 1.0, SHARED_NONE, 256, 3),
     "c5": MoeConfig("c5", 7168, 512, 8, 2048, 2048, ROUTE_SOFTMAX, 0, 0, 1.0, SHARED_UNSCALED, 1024, 4),
+    # the same layer with Zipf(1.1)-skewed routing (the benchmark runs the very large layer both ways)
+    "c5z": MoeConfig("c5z", 7168, 512, 8, 2048, 2048, ROUTE_SOFTMAX, 0, 0, 1.0, SHARED_UNSCALED, 1024, 4, zipf=1.1),
 }
 
 
