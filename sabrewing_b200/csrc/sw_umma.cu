@@ -104,6 +104,17 @@ __device__ __forceinline__ void um_mma_ta(unsigned d_tmem, unsigned a_tmem, uint
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
                  :: "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same, executed by a whole warp with warp-uniform operands: one elected lane issues.  Keeping the issuing code
+// warp-uniform lets the descriptors live in uniform registers, which is where the instruction takes them from; computed
+// per thread (inside an `if (lane == 0)`) every operand of every MMA is first moved across, and the moves, not the tensor
+// pipe, set the issue rate (measured: 190 against 64 clocks per M = 128, N = 128, K = 16 MMA).
+__device__ __forceinline__ void um_mma_ta_elect(unsigned d_tmem, unsigned a_tmem, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 :: "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void um_commit_elect(unsigned bar) {
+    asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" :: "r"(bar) : "memory");
+}
 // 32 consecutive columns of this thread's lane (the caller waits with tcgen05.wait::st)
 __device__ __forceinline__ void um_st32_nowait(unsigned taddr, const uint32_t (&r)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
@@ -362,18 +373,20 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
         // Two warps, one thread each: issuer t multiplies tile t of the pair into its own accumulator columns
         // [128 t, 128 t + R).  One MMA of N = R per 16 columns and term: A (the dequantised weights) from tensor
         // memory, B (the fp16 activations) from the slot.
-        if (lane == 0) {
-            const int t = warp - (UM_DQ_WARPS + 5);
+        // The whole warp runs this loop with warp-uniform values; an elected lane issues the MMAs and the commits.
+        {
+            const int t = __shfl_sync(0xffffffffu, warp, 0) - (UM_DQ_WARPS + 5);
             unsigned ks = 0, nitem = 0;                                  // step and item counters
             for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, nitem++) {
                 int gi, c0, pr; decode(item, gi, c0, pr);
-                const int n = min(128, a.gcnt[gi] - c0);
+                const int n = __shfl_sync(0xffffffffu, min(128, a.gcnt[gi] - c0), 0);
                 const int R = tile_rows(n);
                 const unsigned idesc = (1u << 4) | ((unsigned)(R >> 3) << 17) | ((128u >> 4) << 24);   // f32 accum, f16 x f16, K-major
                 const unsigned d_tmem = tmem + (unsigned)t * 128;
                 // one accumulator buffer: the previous item's epilogue has to have read it
                 if (nitem >= 1 && !um_bar_wait(um_s32(&b_acc_free), (nitem - 1) & 1, abortp)) {
-                    atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break;
+                    if (lane == 0) atomicOr(a.status, SW_ST_TIMEOUT);
+                    *abortp = 1; break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned bt = (unsigned)R * 128u;
@@ -388,15 +401,15 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
 #pragma unroll
                     for (int k = 0; k < 8; k++) {                       // 16 columns per MMA: 8 tensor-memory columns of A, 32 bytes of each B row
                         const uint64_t dh = um_desc(bb + (k >> 2) * bt) + 2 * (k & 3);
-                        um_mma_ta(d_tmem, ta + 8 * k, dh, idesc, (st | k) ? 1u : 0u);
-                        if (two_terms) um_mma_ta(d_tmem, ta + 8 * k, um_desc(bb + (2 + (k >> 2)) * bt) + 2 * (k & 3), idesc, 1u);
+                        um_mma_ta_elect(d_tmem, ta + 8 * k, dh, idesc, (st | k) ? 1u : 0u);
+                        if (two_terms) um_mma_ta_elect(d_tmem, ta + 8 * k, um_desc(bb + (2 + (k >> 2)) * bt) + 2 * (k & 3), idesc, 1u);
                     }
                     // one commit per step and issuer: when both have arrived the slot returns to the TMA warp and the
                     // step's two A tiles to the dequantising warps
-                    um_commit(um_s32(&b_raw_free[s]));
+                    um_commit_elect(um_s32(&b_raw_free[s]));
                 }
-                if (!ok) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
-                um_commit(um_s32(&b_acc_full[t]));
+                if (!ok) { if (lane == 0) atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
+                um_commit_elect(um_s32(&b_acc_full[t]));
             }
         }
     } else if (warp < UM_DQ_WARPS) {
