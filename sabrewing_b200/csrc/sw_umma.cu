@@ -95,36 +95,29 @@ __device__ __forceinline__ uint64_t um_desc(unsigned saddr) {
     d |= (uint64_t)2 << 61;                             // SWIZZLE_128B
     return d;
 }
-__device__ __forceinline__ void um_mma(unsigned d_tmem, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// A operand in tensor memory (128 lanes x 8 columns of two fp16 each per K = 16), B through its shared-memory descriptor
-__device__ __forceinline__ void um_mma_ta(unsigned d_tmem, unsigned a_tmem, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-                 :: "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// The same, executed by a whole warp with warp-uniform operands: one elected lane issues.  Keeping the issuing code
+// tcgen05.mma, executed by a whole warp with warp-uniform operands: one elected lane issues (and the same lane
+// issues the commits, which track the operations of the thread that executes them).  Keeping the issuing code
 // warp-uniform lets the descriptors live in uniform registers, which is where the instruction takes them from; computed
 // per thread (inside an `if (lane == 0)`) every operand of every MMA is first moved across, and the moves, not the tensor
 // pipe, set the issue rate (measured: 190 against 64 clocks per M = 128, N = 128, K = 16 MMA).
+// A operand in tensor memory (128 lanes x 8 columns of two fp16 each per K = 16), B through its shared-memory descriptor:
 __device__ __forceinline__ void um_mma_ta_elect(unsigned d_tmem, unsigned a_tmem, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
     asm volatile("{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
                  :: "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// both operands through shared-memory descriptors
+__device__ __forceinline__ void um_mma_elect(unsigned d_tmem, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void um_commit_elect(unsigned bar) {
     asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" :: "r"(bar) : "memory");
 }
-// 32 consecutive columns of this thread's lane (the caller waits with tcgen05.wait::st)
-__device__ __forceinline__ void um_st32_nowait(unsigned taddr, const uint32_t (&r)[32]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+// 16 consecutive columns of this thread's lane (the caller waits with tcgen05.wait::st)
+__device__ __forceinline__ void um_st16_nowait(unsigned taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
                  :: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-                    "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-                    "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-                    "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
-}
-__device__ __forceinline__ void um_commit(unsigned bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+                    "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
 __device__ __forceinline__ void um_ld32(unsigned taddr, float (&v)[32]) {
     uint32_t r[32];
@@ -437,16 +430,15 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
                 for (int c = 0; c < 4; c++) wv[c] = *reinterpret_cast<const uint4 *>(rrow + ((c ^ sw) << 4));
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (int hf = 0; hf < 2; hf++) {                        // two independent halves of 64 columns
-                    uint32_t r[32];
-                    const uint32_t ww[8] = {wv[2 * hf].x, wv[2 * hf].y, wv[2 * hf].z, wv[2 * hf].w,
-                                            wv[2 * hf + 1].x, wv[2 * hf + 1].y, wv[2 * hf + 1].z, wv[2 * hf + 1].w};
+                for (int qt = 0; qt < 4; qt++) {                        // four independent quarters of 32 columns: a quarter's store
+                    uint32_t r[16];                                     // drains while the next one is being converted
+                    const uint32_t ww[4] = {wv[qt].x, wv[qt].y, wv[qt].z, wv[qt].w};
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {                       // word i: columns 8i .. 8i+7 in the order 0,4,1,5,2,6,3,7
+                    for (int i = 0; i < 4; i++) {                       // word i: columns 8i .. 8i+7 in the order 0,4,1,5,2,6,3,7
                         const uint4 d = um_dq(ww[i]);
                         r[4 * i] = d.x; r[4 * i + 1] = d.y; r[4 * i + 2] = d.z; r[4 * i + 3] = d.w;
                     }
-                    um_st32_nowait(tmem + lane_base + UM_TMEM_A + b * 64 + hf * 32, r);
+                    um_st16_nowait(tmem + lane_base + UM_TMEM_A + b * 64 + qt * 16, r);
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -649,27 +641,27 @@ k_bf16_umma(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CU
             }
         }
     } else if (warp == 5) {
-        if (lane == 0) {                                                 // MMA issuer
+        {                                                                // MMA issuer: the whole warp, warp-uniform; an elected lane issues
             unsigned kk = 0, tile = 0;
             for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, tile++) {
                 const int ci = item / mtiles;
                 // hi and lo tiles are adjacent: one N=256 MMA per step, columns [0,128) = A*hi, [128,256) = A*lo
                 const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);  // f32 accum, bf16 x bf16
                 const unsigned acc = tile & 1, d_tmem = tmem + acc * 256;
-                if (tile >= 2 && !um_bar_wait(um_s32(&b_acc_free[acc]), ((tile >> 1) - 1) & 1, abortp)) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
+                if (tile >= 2 && !um_bar_wait(um_s32(&b_acc_free[acc]), ((tile >> 1) - 1) & 1, abortp)) { if (lane == 0) atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 for (int st = 0; st < NST; st++, kk++) {
                     const int s = kk % UB_STAGES;
-                    if (!um_bar_wait(um_s32(&b_full[s]), (kk / UB_STAGES) & 1, abortp)) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
+                    if (!um_bar_wait(um_s32(&b_full[s]), (kk / UB_STAGES) & 1, abortp)) { if (lane == 0) atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const unsigned char *sp = smem + s * UB_STAGE_BYTES;
                     const uint64_t da = um_desc(um_s32(sp)), db = um_desc(um_s32(sp + UM_BT));
 #pragma unroll
-                    for (int k = 0; k < 4; k++) um_mma(d_tmem, da + 2 * k, db + 2 * k, idesc, (st | k) ? 1u : 0u);
-                    um_commit(um_s32(&b_free[s]));
+                    for (int k = 0; k < 4; k++) um_mma_elect(d_tmem, da + 2 * k, db + 2 * k, idesc, (st | k) ? 1u : 0u);
+                    um_commit_elect(um_s32(&b_free[s]));
                 }
                 if (*abortp) break;
-                um_commit(um_s32(&b_acc_full[acc]));
+                um_commit_elect(um_s32(&b_acc_full[acc]));
             }
         }
     } else {
