@@ -17,11 +17,13 @@
 //                its 64 raw bytes of the step from the slot, expands them to 128 exact
 //                fp16 integers (nibble - 8) in registers and stores them with tcgen05.st
 //                into one of four A tiles in TENSOR MEMORY (64 columns each)
-//   warps 13,14  MMA issuers, one thread each, one per tile of the pair: eight
-//                tcgen05.mma kind::f16 per step with the A operand in tensor memory and B
-//                through its shared-memory descriptor (with two terms a second MMA
-//                against the lo tile into the same accumulator columns); one
-//                tcgen05.commit per step returns the slot and the step's A tiles
+//   warps 13,14  MMA issuers, one per tile of the pair: eight tcgen05.mma kind::f16 per
+//                step with the A operand in tensor memory and B through its
+//                shared-memory descriptor (with two terms a second MMA against the lo
+//                tile into the same accumulator columns); one tcgen05.commit per step
+//                returns the slot and the step's A tiles.  The WHOLE warp runs the loop
+//                with warp-uniform values and an elected lane issues (elect.sync), so
+//                that the descriptors are computed in uniform registers
 //   warps 8-11   epilogue: tcgen05.ld the two accumulators of the item, apply the per-row
 //                scales and SiLU(gate)*up, or store the f32 slot rows.  The accumulators
 //                have ONE buffer (tensor memory: 256 columns of accumulators + 256 of A
@@ -363,7 +365,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
         }
     } else if (warp >= UM_DQ_WARPS + 5) {
         // ------------------------------ MMA issuers ------------------------------
-        // Two warps, one thread each: issuer t multiplies tile t of the pair into its own accumulator columns
+        // Two warps: issuer t multiplies tile t of the pair into its own accumulator columns
         // [128 t, 128 t + R).  One MMA of N = R per 16 columns and term: A (the dequantised weights) from tensor
         // memory, B (the fp16 activations) from the slot.
         // The whole warp runs this loop with warp-uniform values; an elected lane issues the MMAs and the commits.
@@ -408,8 +410,8 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
     } else if (warp < UM_DQ_WARPS) {
         // ------------------------------ dequantise ------------------------------
         // Two groups of four warps: group t dequantises tile t of every step.  A thread owns one tile row (tensor-memory
-        // lane 32 * (warp % 4) + lane): it reads the row's 32 raw bytes of the step from the slot, expands them to 64 exact
-        // fp16 integers (nibble - 8) in 32 registers and stores them to the 32 columns of A tile (2 * step + t) % 8.
+        // lane 32 * (warp % 4) + lane): it reads the row's 64 raw bytes of the step from the slot, expands them to 128 exact
+        // fp16 integers (nibble - 8) and stores them to the 64 columns of A tile (2 * step + t) % 4 in four pieces.
         const int tsel = warp >> 2, q = warp & 3;
         const int trow = q * 32 + lane;
         const unsigned lane_base = (unsigned)(q * 32) << 16;
@@ -430,8 +432,8 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
                 for (int c = 0; c < 4; c++) wv[c] = *reinterpret_cast<const uint4 *>(rrow + ((c ^ sw) << 4));
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (int qt = 0; qt < 4; qt++) {                        // four independent quarters of 32 columns: a quarter's store
-                    uint32_t r[16];                                     // drains while the next one is being converted
+                for (int qt = 0; qt < 4; qt++) {                        // four independent quarters (32 fp16 = 16 columns each): a
+                    uint32_t r[16];                                     // quarter's store drains while the next one is converted
                     const uint32_t ww[4] = {wv[qt].x, wv[qt].y, wv[qt].z, wv[qt].w};
 #pragma unroll
                     for (int i = 0; i < 4; i++) {                       // word i: columns 8i .. 8i+7 in the order 0,4,1,5,2,6,3,7
