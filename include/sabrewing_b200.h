@@ -267,12 +267,17 @@ int  sw_moe_route_static(const SwMoeDesc *desc, const SwMoeLayer *layer, const f
 int  sw_moe_get_routing(SwMoeCtx *ctx, int *sel, float *w, float *scores, int *G,
                         int *gexp, int *gbeg, int *gcnt, int *grow, int *rowof);
 
-/* Device-side status word of the last launches (0 = clean); bit 0: an expert id
+/* Device-side status word: the bits raised by the launches since the previous call of this
+ * function, which clears them (0 = clean; synchronises the stream used last); bit 0: an expert id
  * outside [0,E) reached the dispatch, bit 1: a row index outside [0,T), bit 2: a
  * bounded device-side wait ran out (the kernel gave up and returned), bit 3: an
- * activation outside the fp16 range of the tensor-core expert kernels was clamped
- * to +-65504 (the result is then not the reference's; the reference is f32
- * throughout, c/moe_quant.h:45-217). */
+ * activation, or a SiLU(gate)*up value entering the down product, left the fp16
+ * range of the tensor-core expert kernels (every path but the CUDA-core one) and was
+ * clamped to +-65504: the result is then not the reference's (the reference is f32
+ * throughout, c/moe_quant.h:45-217).  The kernels divide every token row by a power
+ * of two on its way in and multiply back in f32 (the bar holds for inputs 1e-6 ...
+ * 1e6 times the usual size, tests/test_moe_gpu.py), so in practice the bit means an
+ * infinity or a NaN in the input. */
 int  sw_moe_status(SwMoeCtx *ctx);
 /* Context options.  SW_OPT_UMMA_TERMS: how the tcgen05 grouped GEMM (groups averaging >= 16
  * rows: prefill, large batches) feeds f32 activations to the fp16 tensor cores.

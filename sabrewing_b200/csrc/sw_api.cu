@@ -126,6 +126,7 @@ struct SwMoeCtx {
     int lastES = 0;              // row stride of the scores of the last routing (experts + the shared-pool logit, if any)
     int last_path = -1;          // expert kernels of the last experts/forward call (sw_moe_last_path)
     int umma_terms = 1;
+    const float *row_back = nullptr;   // set by the last expert stage: per-token powers of two the combine step squares and applies (or null)
     int forced_path = -1;        // SW_OPT_EXPERT_PATH: -1 = choose by shape and group size          // fp16 terms per activation on the tcgen05 path: 1 = hi only, 2 = hi + lo
     int cap_on = 0, cap_prof = 0; long long cap_l0 = 0;   // open stage capture (sw_moe_capture_begin)
     // a shared-expert result left by sw_moe_shared for the next sw_moe_finish of the same row count
@@ -135,6 +136,17 @@ struct SwMoeCtx {
     int prof_on = 0, prof_calls = 0;
     cudaEvent_t *prof_ev = nullptr;   // [SW_PROF_MAX_CALLS][SW_NSTAGES+1]
 };
+
+// Layout of the `sums` scratch of the tensor-core paths: row sums of x [rows_x], the token rows' powers of two
+// [rows_x], their copies per packed row [max_rows], then the partial row sums of the packed SiLU*up rows.
+struct SwSums { float *xsum, *rexp, *srex, *ypart; };
+static inline size_t sw_pad64(size_t n) { return (n + 63) & ~(size_t)63; }
+static inline SwSums sw_sums_layout(float *sums, int rows_x, int max_rows) {
+    SwSums l;
+    l.xsum = sums; l.rexp = l.xsum + sw_pad64(rows_x); l.srex = l.rexp + sw_pad64(rows_x); l.ypart = l.srex + sw_pad64(max_rows);
+    return l;
+}
+static inline size_t sw_sums_bytes(size_t T, size_t P, size_t I) { return (2 * sw_pad64(T) + sw_pad64(P) + P * (I / 8 + 1)) * 4; }
 
 enum { SW_ST_LOGITS = 0, SW_ST_TOPK, SW_ST_DISPATCH, SW_ST_GATEUP, SW_ST_DOWN, SW_ST_SH_GATEUP, SW_ST_SH_DOWN, SW_ST_COMBINE, SW_NSTAGES };
 #define SW_PROF_MAX_CALLS 512
@@ -193,7 +205,7 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
         T * D * 4,            // routed
         T * D * 4, T * D * 4, // dx, dout
         T * D * 4,            // xp
-        (T + 64) * 4 + P * (I / 8 + 1) * 4,  // sums
+        sw_sums_bytes(T, P, I),  // sums
         T * D * 4,            // spk
         P * D * 4,            // um.xg: gathered fp16 hi + lo token rows
         (P / 128 + E + 64) * 8 + 256,   // um.chunks + nchunks
@@ -335,53 +347,59 @@ static int sw_resolve_path(const SwQ4Args &a, int D, int I, const SwUmmaScratch 
     return path;
 }
 
-// x_packed: the packed copy of x (xp) and its row sums are already in flight or done (the caller ordered them
-// before this call's stream position).
+// x_packed: the packed copy of x (xp), its row sums and its rows' powers of two are already in flight or done (the
+// caller ordered them before this call's stream position).
 static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, const float *gu_s,
                           const void *dn_q, const float *dn_s, const float *x, int rows_x, void *xp,
                           float *glu, float *slots, float *sums, int *status, int D, int I,
                           void (*mark)(void *, int), void *mark_ctx, const SwUmmaScratch *um = nullptr, bool x_packed = false,
-                          int *path_out = nullptr, int umma_terms = 2, int forced_path = -1) {
+                          int *path_out = nullptr, int umma_terms = 2, int forced_path = -1, const float **row_back = nullptr) {
     const int path = sw_resolve_path(a, D, I, um, forced_path);
     if (path_out) *path_out = path;
+    // *row_back: null, or per row of x the power of two whose square the caller's combine step still has to apply
+    if (row_back) *row_back = nullptr;
     if (path == 3) {
         // tcgen05 path: gather + split the token rows in packed-slot order, build the chunk list, two grouped GEMMs
         const long long nexp = a.expert_cnt > 4096 ? 4096 : a.expert_cnt;
         const int P = a.max_rows, max_chunks = P / 128 + a.max_groups;
         __half *xh = (__half *)um->xg, *xl = xh + (size_t)P * D;
         __half *gh = (__half *)glu, *gl = gh + (size_t)P * I;
-        if (sw_launch_umma_gather(cfg, x, a.grow, a.G + 1, P, D, xh, umma_terms == 2 ? xl : nullptr, status)) return -1;
+        const SwSums sl = sw_sums_layout(sums, rows_x, a.max_rows);
+        if (sw_launch_row_exp(cfg, x, rows_x, D, sl.rexp)) return -1;
+        if (sw_launch_umma_gather(cfg, x, a.grow, a.G + 1, P, D, xh, umma_terms == 2 ? xl : nullptr, status, sl.rexp, sl.srex)) return -1;
         if (sw_launch_umma_chunks(cfg, a, um->nchunks, um->chunks)) return -1;
         a.q = (const uint8_t *)gu_q; a.s = gu_s; a.KD = D; a.OUT = I;
-        if (sw_launch_q4_umma(cfg, a, xh, xl, gh, gl, um->nchunks, um->chunks, max_chunks, status, nexp * 2 * I, true, umma_terms)) return -1;
+        if (sw_launch_q4_umma(cfg, a, xh, xl, gh, gl, um->nchunks, um->chunks, max_chunks, status, nexp * 2 * I, true, umma_terms, sl.srex)) return -1;
         if (mark) mark(mark_ctx, 0);
         a.q = (const uint8_t *)dn_q; a.s = dn_s; a.KD = I; a.OUT = D;
-        if (sw_launch_q4_umma(cfg, a, gh, gl, slots, nullptr, um->nchunks, um->chunks, max_chunks, status, nexp * D, false, umma_terms)) return -1;
+        if (sw_launch_q4_umma(cfg, a, gh, gl, slots, nullptr, um->nchunks, um->chunks, max_chunks, status, nexp * D, false, umma_terms, nullptr)) return -1;
+        if (!row_back) return -1;                                      // every caller of this path has a combine step
+        *row_back = sl.rexp;
         if (mark) mark(mark_ctx, 1);
         return 0;
     }
     if (path > 0) {
-        // sums: [rows_x] row sums of x, then [max_rows, parts] partial row sums of the packed SiLU*up rows
-        float *xsum = sums, *ypart = sums + ((rows_x + 63) & ~63);
-        if (!x_packed && sw_launch_pack_act(cfg, x, xp, xsum, rows_x, D)) return -1;
+        const SwSums sl = sw_sums_layout(sums, rows_x, a.max_rows);
+        float *xsum = sl.xsum, *ypart = sl.ypart;
+        if (!x_packed && sw_launch_pack_act(cfg, x, xp, xsum, rows_x, D, sl.rexp, status)) return -1;
         const long long nexp = a.expert_cnt > 4096 ? 4096 : a.expert_cnt;   // bounds the tensor map when the caller gave no count
         a.q = (const uint8_t *)gu_q; a.s = gu_s; a.KD = D; a.OUT = I;
         int parts;
         if (path == 2) {
             int mt = (long long)a.max_groups * ((I + 63) / 64) >= (long long)cfg.num_sms * 4 ? 2 : 1;
             if (sw_tuning().tma_mt) mt = sw_tuning().tma_mt;
-            SwMmaIO io{xp, xsum, 1, glu, ypart};
+            SwMmaIO io{xp, xsum, 1, glu, ypart, status, sl.rexp, sl.srex};
             if (sw_launch_q4_tma(cfg, a, io, status, nexp * 2 * I, true, mt)) return -1;
             parts = sw_q4_tma_parts(I, mt);
         } else {
             const int mt = sw_q4_mma_mt(cfg, a, true);
-            SwMmaIO io{xp, xsum, 1, glu, ypart};
+            SwMmaIO io{xp, xsum, 1, glu, ypart, status, sl.rexp, sl.srex};
             if (sw_launch_q4_mma(cfg, a, io, true, mt)) return -1;
             parts = I / (8 * mt);
         }
         if (mark) mark(mark_ctx, 0);
         a.q = (const uint8_t *)dn_q; a.s = dn_s; a.KD = I; a.OUT = D;
-        SwMmaIO io2{glu, ypart, parts, slots, nullptr};
+        SwMmaIO io2{glu, ypart, parts, slots, nullptr, status, sl.srex, nullptr};
         if (path == 2) {
             int mt = (long long)a.max_groups * ((D + 127) / 128) >= (long long)cfg.num_sms * 4 ? 2 : 1;
             if (sw_tuning().tma_mt) mt = sw_tuning().tma_mt;
@@ -448,7 +466,7 @@ static int sw_expert_stage(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
     a.gexp = c->r.gexp; a.gbeg = c->r.gbeg; a.gcnt = c->r.gcnt; a.G = c->r.G; a.grow = c->r.grow;
     a.expert_lo = lo; a.expert_cnt = cnt;
     a.max_rows = T * K; a.max_groups = E < T * K ? E : T * K; a.gs = L->gs;
-    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, nullptr, nullptr, &c->um, false, &c->last_path, c->umma_terms, c->forced_path))
+    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, nullptr, nullptr, &c->um, false, &c->last_path, c->umma_terms, c->forced_path, &c->row_back))
         return sw_fail("expert launch failed");
     return 0;
 }
@@ -530,7 +548,7 @@ extern "C" int sw_moe_experts(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer 
     if (sw_expert_stage(c, d, L, x, T, st)) return -1;
     SwLaunchCfg cfg{c->num_sms, st, c->dev};
     int lo, cnt; sw_resident(d, L, &lo, &cnt);
-    if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, nullptr, 0, routed, T, d->topk, L->D, 1.f, 0, lo, cnt)) return sw_fail("combine launch failed");
+    if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, nullptr, 0, routed, T, d->topk, L->D, 1.f, 0, lo, cnt, nullptr, c->row_back)) return sw_fail("combine launch failed");
     return 0;
 }
 
@@ -562,7 +580,7 @@ extern "C" int sw_moe_experts_routed(SwMoeCtx *c, const SwMoeDesc *d, const SwMo
     c->last_stream = st; c->lastT = T; c->lastK = K; c->lastE = E; c->lastES = E;
     if (sw_expert_stage(c, d, L, x, T, st)) return -1;
     int lo, cnt; sw_resident(d, L, &lo, &cnt);
-    if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, nullptr, 0, routed, T, K, L->D, 1.f, 0, lo, cnt)) return sw_fail("combine launch failed");
+    if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, nullptr, 0, routed, T, K, L->D, 1.f, 0, lo, cnt, nullptr, c->row_back)) return sw_fail("combine launch failed");
     return 0;
 }
 
@@ -663,7 +681,7 @@ static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
         SW_CUDA(cudaEventRecord(c->ev_fork, st));
         SW_CUDA(cudaStreamWaitEvent(c->aux, c->ev_fork, 0));
         if (prepack) {
-            if (sw_launch_pack_act(acfg, x, c->xp, c->sums, T, L->D)) return sw_fail("pack launch failed");
+            if (sw_launch_pack_act(acfg, x, c->xp, c->sums, T, L->D, sw_sums_layout(c->sums, T, T * d->topk).rexp, c->r.status)) return sw_fail("pack launch failed");
             SW_CUDA(cudaEventRecord(c->ev_pack, c->aux));
         }
     }
@@ -681,7 +699,7 @@ static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
 
     auto mark = [](void *p, int which) { MarkCtx *m = (MarkCtx *)p; sw_prof_mark(m->c, which == 0 ? SW_ST_GATEUP : SW_ST_DOWN, m->st); };
     if (prepack) SW_CUDA(cudaStreamWaitEvent(st, c->ev_pack, 0));
-    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, mark, &mc, &c->um, prepack, &c->last_path, c->umma_terms, c->forced_path))
+    if (sw_run_experts(cfg, a, L->gu_q, L->gu_s, L->dn_q, L->dn_s, x, T, c->xp, c->glu, c->slots, c->sums, c->r.status, L->D, L->I, mark, &mc, &c->um, prepack, &c->last_path, c->umma_terms, c->forced_path, &c->row_back))
         return sw_fail("expert launch failed");
     if (overlap) {
         SW_CUDA(cudaStreamWaitEvent(st, c->ev_join, 0));
@@ -696,7 +714,7 @@ static int sw_forward_impl(SwMoeCtx *c, const SwMoeDesc *d, const SwMoeLayer *L,
     if (d->shared_mode == SW_SHARED_GATED) gate = c->row_gate;              // written by the top-k kernel of this call
     const int scale_bit = d->shared_mode == SW_SHARED_GATED ? 0 : 1;         // pool weights already carry route_scale
     if (sw_launch_combine(cfg, c->slots, c->r.rowof, c->r.sel, c->r.w, so, so_slices, out, T, K, L->D,
-                          d->route_scale, scale_bit | (has_shared ? 2 : 0) | (accumulate ? 4 : 0), lo, cnt, gate)) return sw_fail("combine launch failed");
+                          d->route_scale, scale_bit | (has_shared ? 2 : 0) | (accumulate ? 4 : 0), lo, cnt, gate, c->row_back)) return sw_fail("combine launch failed");
     sw_prof_mark(c, SW_ST_COMBINE, st);
     if (c->prof_on && c->prof_calls < SW_PROF_MAX_CALLS) c->prof_calls++;
     return 0;
@@ -843,6 +861,7 @@ extern "C" int sw_moe_status(SwMoeCtx *c) {
     int s = 0;
     if (c->last_stream) cudaStreamSynchronize(c->last_stream);
     if (cudaMemcpy(&s, c->r.status, 4, cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (s && cudaMemset(c->r.status, 0, 4) != cudaSuccess) { cudaGetLastError(); return -1; }     // read and clear, like cudaGetLastError
     return s;
 }
 
@@ -1063,7 +1082,7 @@ static int lag_group_core(float *acc, const float *x, const void *gu_q, const fl
     if (((uintptr_t)gu_q | (uintptr_t)gu_s | (uintptr_t)dn_q | (uintptr_t)dn_s) & 15) return -1;   // 128-bit loads, TMA tensor maps
     const int P = S * K;
     if (g_lag.dglu.ensure((size_t)P * I * 4) || g_lag.dslot.ensure((size_t)P * D * 4) || g_lag.dxp.ensure((size_t)S * D * 4) ||
-        g_lag.dsums.ensure(((size_t)S + 64 + (size_t)P * (I / 8 + 1)) * 4)) return -1;
+        g_lag.dsums.ensure(sw_sums_bytes(S, P, I))) return -1;
     LagIdx ix;
     if (lag_stage_idx(&ix, gexp, gbeg, gcnt, G, grow, rowof, w, P)) return -1;
     SwLaunchCfg cfg{g_lag.num_sms, g_lag.st, g_lag.dev};
@@ -1071,10 +1090,12 @@ static int lag_group_core(float *acc, const float *x, const void *gu_q, const fl
         SwQ4Args a{};
         a.gexp = ix.gexp; a.gbeg = ix.gbeg; a.gcnt = ix.gcnt; a.G = ix.G; a.grow = ix.grow;
         a.expert_lo = 0; a.expert_cnt = 0x7fffffff; a.max_groups = G; a.max_rows = P;
+        const float *row_back = nullptr;
         if (sw_run_experts(cfg, a, gu_q, gu_s, dn_q, dn_s, (const float *)g_lag.dx.p, S, g_lag.dxp.p,
-                           (float *)g_lag.dglu.p, (float *)g_lag.dslot.p, (float *)g_lag.dsums.p, ix.G + 32, D, I, nullptr, nullptr)) return -1;
+                           (float *)g_lag.dglu.p, (float *)g_lag.dslot.p, (float *)g_lag.dsums.p, ix.G + 32, D, I, nullptr, nullptr,
+                           nullptr, false, nullptr, 2, -1, &row_back)) return -1;
         return sw_launch_combine(cfg, (const float *)g_lag.dslot.p, ix.rowof, ix.sel, ix.w, nullptr, 0, (float *)g_lag.dy.p,
-                                 S, K, D, 1.f, 0, 0, 1);
+                                 S, K, D, 1.f, 0, 0, 1, nullptr, row_back);
     });
 }
 
@@ -1161,8 +1182,8 @@ extern "C" int lag_cuda_matmul_q4(float *y, const float *x, const void *packed, 
         a.q = (const uint8_t *)packed; a.s = (const float *)scale; a.X = (const float *)g_lag.dx.p; a.Y = (float *)g_lag.dy.p;
         a.KD = I; a.OUT = O;
         if (tc) {
-            if (sw_launch_pack_act(cfg, (const float *)g_lag.dx.p, g_lag.dxp.p, (float *)g_lag.dsums.p, S, I)) return -1;
-            SwMmaIO io{g_lag.dxp.p, (const float *)g_lag.dsums.p, 1, g_lag.dy.p, nullptr};
+            if (sw_launch_pack_act(cfg, (const float *)g_lag.dx.p, g_lag.dxp.p, (float *)g_lag.dsums.p, S, I, nullptr, nullptr)) return -1;
+            SwMmaIO io{g_lag.dxp.p, (const float *)g_lag.dsums.p, 1, g_lag.dy.p, nullptr, nullptr, nullptr, nullptr};
             const int mt = (O + 127) / 128 >= cfg.num_sms * 4 ? 2 : 1;
             return sw_launch_q4_tma(cfg, a, io, dm + 128, O, false, mt);
         }

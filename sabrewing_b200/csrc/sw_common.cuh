@@ -115,8 +115,14 @@ struct SwMmaIO {
     int xsum_parts;
     void *Y;               // gate/up: packed rows; down: f32 rows
     float *ypart;          // gate/up only: [rows, OUT/(8*mt)] sums of what each item wrote
+    int *status;           // device status word (may be null): SW_ST_RANGE when a value had to be clamped to the fp16 range
+    // Per-row powers of two (both may be null = 1).  gate/up: rex[token row] = 2^e the packed row was divided by; the
+    // kernel also copies it to srex_out[packed row].  down: rex[packed row]; the outputs are multiplied by its square.
+    const float *rex;
+    float *srex_out;
 };
-int sw_launch_pack_act(const SwLaunchCfg &c, const float *x, void *xp, float *rowsum, int rows, int KD);
+// rexp (may be null): normalise every row by a power of two and store it there (see k_pack_act)
+int sw_launch_pack_act(const SwLaunchCfg &c, const float *x, void *xp, float *rowsum, int rows, int KD, float *rexp, int *status);
 int sw_q4_mma_mt(const SwLaunchCfg &c, const SwQ4Args &a, bool gateup);
 int sw_launch_q4_mma(const SwLaunchCfg &c, const SwQ4Args &a, const SwMmaIO &io, bool gateup, int mt);
 // sw_tma.cu: TMA-staged variant of the int4 products
@@ -126,10 +132,13 @@ int sw_launch_q4_tma(const SwLaunchCfg &c, const SwQ4Args &a, const SwMmaIO &io,
 int sw_launch_wait_runs_out(const SwLaunchCfg &c, int *status, unsigned limit);
 // sw_umma.cu: tcgen05/TMEM grouped GEMM for groups with many rows
 bool sw_umma_available();
-int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow, const int *npairs, int P, int KD, void *hi, void *lo, int *status);
+int sw_launch_row_exp(const SwLaunchCfg &c, const float *x, int rows, int KD, float *rexp);
+int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow, const int *npairs, int P, int KD, void *hi, void *lo, int *status,
+                          const float *rexp, float *srex);
 int sw_launch_umma_chunks(const SwLaunchCfg &c, const SwQ4Args &a, int *nchunks, void *chunks);
 int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_hi, const void *act_lo, void *Y0, void *Y1,
-                      const int *nchunks, const void *chunks, int max_chunks, int *status, long long wrows_total, bool gateup, int terms);
+                      const int *nchunks, const void *chunks, int max_chunks, int *status, long long wrows_total, bool gateup, int terms,
+                      const float *srex);
 int sw_launch_pack_bf16_planar(const SwLaunchCfg &c, const float *x, void *hi, void *lo, int rows, int KD);
 int sw_launch_bf16_umma(const SwLaunchCfg &c, const void *W0, const void *W1, const void *act_hi, const void *act_lo,
                         void *Y0, void *Y1, int T, int KD, int O, int *status, bool gateup);
@@ -148,7 +157,8 @@ int sw_launch_q8_rows(const SwLaunchCfg &c, const float *x, const int8_t *W, con
 // `add` holds add_slices consecutive [T,D] arrays that are summed in order.
 int sw_launch_combine(const SwLaunchCfg &c, const float *slots, const int *rowof, const int *sel,
                       const float *w, const float *add, int add_slices, float *out, int T, int K, int D,
-                      float route_scale, int mode, int expert_lo, int expert_cnt, const float *row_gate = nullptr);
+                      float route_scale, int mode, int expert_lo, int expert_cnt, const float *row_gate = nullptr,
+                      const float *row_back = nullptr);   // row_back[t]: power of two whose square multiplies row t's routed sum
 int sw_launch_finish(const SwLaunchCfg &c, const float *routed, const float *add, int add_slices, float *out,
                      int T, int D, float route_scale, int has_add, const float *row_gate = nullptr);
 int sw_launch_rmsnorm(const SwLaunchCfg &c, const float *x, const float *w, float *y, int T, int D, float eps);

@@ -329,7 +329,8 @@ int sw_launch_q8_rows(const SwLaunchCfg &c, const float *x, const int8_t *W, con
 __global__ void __launch_bounds__(256)
 k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const int *__restrict__ sel,
           const float *__restrict__ w, const float *__restrict__ add, int add_slices, float *__restrict__ out,
-          int T, int K, int D, float route_scale, int mode, int expert_lo, int expert_cnt, const float *__restrict__ row_gate) {
+          int T, int K, int D, float route_scale, int mode, int expert_lo, int expert_cnt, const float *__restrict__ row_gate,
+          const float *__restrict__ row_back) {
     const int D4 = D >> 2;
     const size_t n = (size_t)T * D4;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
@@ -358,6 +359,12 @@ k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const 
                     acc.z = fmaf(wa[j], v[j].z, acc.z); acc.w = fmaf(wa[j], v[j].w, acc.w);
                 }
         }
+        if (row_back) {
+            // the tcgen05 expert kernels worked on the token row divided by the power of two row_back[t] and left the
+            // slot rows divided by its square: multiplying the sum back is exact
+            const float b = row_back[t], b2 = b * b;
+            acc.x *= b2; acc.y *= b2; acc.z *= b2; acc.w *= b2;
+        }
         if (mode & 1) { acc.x *= route_scale; acc.y *= route_scale; acc.z *= route_scale; acc.w *= route_scale; }
         if (mode & 2) {
             float4 s = reinterpret_cast<const float4 *>(add)[idx];
@@ -377,13 +384,13 @@ k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const 
 
 int sw_launch_combine(const SwLaunchCfg &c, const float *slots, const int *rowof, const int *sel,
                       const float *w, const float *add, int add_slices, float *out, int T, int K, int D,
-                      float route_scale, int mode, int expert_lo, int expert_cnt, const float *row_gate) {
+                      float route_scale, int mode, int expert_lo, int expert_cnt, const float *row_gate, const float *row_back) {
     if (T <= 0) return 0;
     if (D % 4) return -1;
     size_t n = (size_t)T * (D / 4);
     long long grid = (long long)((n + 255) / 256);
     if (grid > (long long)c.num_sms * 16) grid = (long long)c.num_sms * 16;
-    k_combine<<<(unsigned)grid, 256, 0, c.stream>>>(slots, rowof, sel, w, add, add_slices, out, T, K, D, route_scale, mode, expert_lo, expert_cnt, row_gate);
+    k_combine<<<(unsigned)grid, 256, 0, c.stream>>>(slots, rowof, sel, w, add, add_slices, out, T, K, D, route_scale, mode, expert_lo, expert_cnt, row_gate, row_back);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

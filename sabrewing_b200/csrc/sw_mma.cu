@@ -83,22 +83,59 @@ __device__ __forceinline__ float sw_split_f16(float v, __half &hi, __half &lo) {
 // ---------------------------------------------------------------------------
 // x[rows, KD] f32 -> packed rows + row sums of the represented values.
 // One CTA per row; the sum is reduced in double in a fixed order.
+// With `rexp` the row is first divided by a power of two 2^e chosen so that its
+// largest magnitude lands in [1, 2), and rexp[row] = 2^e: the fp16 pairs then
+// carry every row at the same relative precision whatever the caller's scale,
+// the gate/up epilogue multiplies the gate back, and SiLU(gate)*up is stored
+// divided by 2^2e (the down product multiplies it back), so that no value of
+// the pipeline depends on the input's magnitude for its range.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-k_pack_act(const float *__restrict__ x, uint4 *__restrict__ xp, float *__restrict__ rowsum, int rows, int KD) {
+k_pack_act(const float *__restrict__ x, uint4 *__restrict__ xp, float *__restrict__ rowsum, int rows, int KD,
+           float *__restrict__ rexp, int *__restrict__ status) {
     __shared__ double s_part[8];
+    __shared__ float s_max[8];
+    bool clamped = false;
     const int cpr = KD >> 3;                                  // chunks per row
     for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        float inv = 1.f;
+        if (rexp) {
+            float m = 0.f;
+            for (int c8 = threadIdx.x; c8 < cpr; c8 += 256) {
+                const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)r * KD + c8 * 8);
+                const float4 a = src[0], b = src[1];
+                m = fmaxf(m, fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))),
+                                   fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w)))));
+            }
+#pragma unroll
+            for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(SW_FULL_MASK, m, off));
+            __syncthreads();                                  // s_max of the previous row has been read
+            if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = m;
+            __syncthreads();
+            m = s_max[0];
+#pragma unroll
+            for (int i = 1; i < 8; i++) m = fmaxf(m, s_max[i]);
+            float rex = 1.f;
+            if (m > 0.f && m <= 3.0e38f) {                    // zero rows, infinities and NaNs keep scale one
+                int ex;
+                frexpf(m, &ex);                               // m = f * 2^ex, f in [0.5, 1)
+                ex = max(-120, min(120, ex - 1));
+                rex = ldexpf(1.f, ex); inv = ldexpf(1.f, -ex);
+            }
+            if (threadIdx.x == 0) rexp[r] = rex;
+        }
         double sum = 0.0;
         for (int c8 = threadIdx.x; c8 < cpr; c8 += 256) {
             const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)r * KD + c8 * 8);
-            const float4 a = src[0], b = src[1];
+            float4 a = src[0], b = src[1];
+            a.x *= inv; a.y *= inv; a.z *= inv; a.w *= inv; b.x *= inv; b.y *= inv; b.z *= inv; b.w *= inv;
             // order 0,4,1,5,2,6,3,7; odd columns carry 1/16
             const float v[8] = {a.x, b.x, a.y * 0.0625f, b.y * 0.0625f, a.z, b.z, a.w * 0.0625f, b.w * 0.0625f};
             __half hi[8], lo[8];
             float even = 0.f, odd = 0.f;
 #pragma unroll
             for (int i = 0; i < 8; i++) {
+                clamped |= !(fabsf(v[i]) <= 65504.f);          // also true for NaN
                 const float rep = sw_split_f16(v[i], hi[i], lo[i]);
                 if ((i >> 1) & 1) odd += rep; else even += rep;
             }
@@ -120,13 +157,14 @@ k_pack_act(const float *__restrict__ x, uint4 *__restrict__ xp, float *__restric
             rowsum[r] = (float)t;
         }
     }
+    if (clamped && status) atomicOr(status, SW_ST_RANGE);
 }
 
-int sw_launch_pack_act(const SwLaunchCfg &c, const float *x, void *xp, float *rowsum, int rows, int KD) {
+int sw_launch_pack_act(const SwLaunchCfg &c, const float *x, void *xp, float *rowsum, int rows, int KD, float *rexp, int *status) {
     if (rows <= 0) return 0;
     if (KD % 128) return -1;
     int grid = rows < c.num_sms * 8 ? rows : c.num_sms * 8;
-    k_pack_act<<<grid, 256, 0, c.stream>>>(x, (uint4 *)xp, rowsum, rows, KD);
+    k_pack_act<<<grid, 256, 0, c.stream>>>(x, (uint4 *)xp, rowsum, rows, KD, rexp, status);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
@@ -231,8 +269,10 @@ k_q4_mma(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
          void *__restrict__ Yout, float *__restrict__ ypart,
          const int *__restrict__ gexp, const int *__restrict__ gbeg, const int *__restrict__ gcnt,
          const int *__restrict__ Gp, const int *__restrict__ grow,
-         int KD, int OUT, int expert_lo, int expert_cnt) {
+         int KD, int OUT, int expert_lo, int expert_cnt, int *__restrict__ status,
+         const float *__restrict__ rex_in, float *__restrict__ srex_out) {
     extern __shared__ uint4 sw_ring[];                        // [P][2*MT][128]
+    bool clamped = false;
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int warps_total = gridDim.x * 4, wid = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int G = *Gp;
@@ -287,7 +327,7 @@ k_q4_mma(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
             }
             // token rows of this thread's two columns, and the "-8 * sum x" correction
             const bool own = m8 || t < 2;
-            float corr[2]; int tok[2];
+            float corr[2], rex[2]; int tok[2];
 #pragma unroll
             for (int j = 0; j < 2; j++) {
                 tok[j] = c0 + 2 * t + j;
@@ -295,10 +335,14 @@ k_q4_mma(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
                 // row sum of the token's activations: the 8 lanes that share t split the partial
                 // sums between them (k = g, g+8, ...) and add up in a fixed tree
                 float sx = 0.f;
+                rex[j] = 1.f;
                 if (ok) {
                     const int rid = GATEUP ? grow[beg + tok[j]] : beg + tok[j];
                     const float *ps = xsum + (size_t)rid * xsum_parts;
                     for (int k = g; k < xsum_parts; k += 8) sx += ps[k];
+                    // the power of two the row was divided by (gate/up: the token's; down: the packed row's)
+                    if (rex_in) rex[j] = rex_in[rid];
+                    if (GATEUP && srex_out && mb == 0 && g == 0) srex_out[beg + tok[j]] = rex[j];
                 }
                 sx += __shfl_xor_sync(SW_FULL_MASK, sx, 4);
                 sx += __shfl_xor_sync(SW_FULL_MASK, sx, 8);
@@ -321,10 +365,12 @@ k_q4_mma(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
 #pragma unroll
                     for (int j = 0; j < 2; j++) {
                         if (tok[j] < 0 || !ov) continue;
-                        const float gv = (acc[mt][j] * SW_ACC_SCALE - corr[j]) * sg;
+                        // gate at its true size; the up value stays divided by 2^e and the product is divided once more
+                        const float gv = (acc[mt][j] * SW_ACC_SCALE - corr[j]) * sg * rex[j];
                         const float uv = (acc[mt][2 + j] * SW_ACC_SCALE - corr[j]) * su;
-                        const float y = (gv / (1.f + expf(-gv))) * uv;
+                        const float y = ((gv / (1.f + expf(-gv))) * __frcp_rn(rex[j])) * uv;
                         __half hi, lo;
+                        clamped |= fabsf(y * pre) > 65504.f;
                         const float rep = sw_split_f16(y * pre, hi, lo);
                         ysum[j] += (o & 1) ? rep * 16.f : rep;
                         __half *row = Y + (size_t)(beg + tok[j]) * (2 * (size_t)OUT);
@@ -350,14 +396,16 @@ k_q4_mma(const uint8_t *__restrict__ Wq, const float *__restrict__ Ws,
                     for (int j = 0; j < 2; j++) {
                         if (tok[j] < 0) continue;
                         float *row = Y + (size_t)(beg + tok[j]) * OUT;
-                        if (oa < OUT) row[oa] = (acc[mt][j] * SW_ACC_SCALE - corr[j]) * sa;
-                        if (ob < OUT) row[ob] = (acc[mt][2 + j] * SW_ACC_SCALE - corr[j]) * sb;
+                        const float back = rex[j] * rex[j];             // SiLU(gate)*up came in divided by 2^2e
+                        if (oa < OUT) row[oa] = (acc[mt][j] * SW_ACC_SCALE - corr[j]) * sa * back;
+                        if (ob < OUT) row[ob] = (acc[mt][2 + j] * SW_ACC_SCALE - corr[j]) * sb * back;
                     }
                 }
             }
             c0 += ntok;
         }
     }
+    if (GATEUP && clamped && status) atomicOr(status, SW_ST_RANGE);
 }
 
 template <bool GATEUP, int MT, int P>
@@ -378,7 +426,7 @@ static int sw_launch_q4_mma_t(const SwLaunchCfg &c, const SwQ4Args &a, const SwM
     if (grid > need) grid = need;
     if (grid < 1) grid = 1;
     kern<<<(unsigned)grid, 128, SMEM, c.stream>>>(a.q, a.s, (const uint4 *)io.XP, io.xsum, io.xsum_parts, io.Y, io.ypart,
-                                                  a.gexp, a.gbeg, a.gcnt, a.G, a.grow, a.KD, a.OUT, a.expert_lo, a.expert_cnt);
+                                                  a.gexp, a.gbeg, a.gcnt, a.G, a.grow, a.KD, a.OUT, a.expert_lo, a.expert_cnt, io.status, io.rex, io.srex_out);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

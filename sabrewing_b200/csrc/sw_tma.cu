@@ -89,6 +89,8 @@ struct SwTmaArgs {
     const int *gexp, *gbeg, *gcnt, *Gp, *grow;
     int *status;
     int KD, OUT, expert_lo, expert_cnt;
+    const float *rex;              // per-row powers of two (null = 1): gate/up by token row, down by packed row
+    float *srex_out;               // gate/up: the token's power of two, copied per packed row for the down product
 };
 
 // fragments of one stage (two 128-column steps) from shared memory -> MT m-tiles of accumulators
@@ -156,6 +158,7 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
     // 8 * (row sum of the token's activations) for the up to 8 token rows of a pass, written by the producer warp
     // (ring of 8 passes: the producer is at most P <= 6 passes ahead of the consumers' epilogue)
     __shared__ float s_corr[8][8];
+    __shared__ float s_rex[8][8];                  // the rows' powers of two, same ring
     unsigned char *smem = (unsigned char *)(((uintptr_t)sw_dyn + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KD = a.KD, OUT = a.OUT;
@@ -200,6 +203,11 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
                 float v[8];
 #pragma unroll
                 for (int r = 0; r < 8; r++) v[r] = 0.f;
+                float my_rex = 1.f;                                                // lane r: the power of two of row r
+                if (lane < ntok && a.rex) {
+                    my_rex = a.rex[GATEUP ? a.grow[beg + c0 + lane] : beg + c0 + lane];
+                    if (GATEUP && a.srex_out && rb == 0) a.srex_out[beg + c0 + lane] = my_rex;
+                }
                 for (int k = lane; k < a.xsum_parts; k += 32) {
                     float ld[8];
 #pragma unroll
@@ -224,6 +232,7 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
                             for (int off = 16; off; off >>= 1) sx += __shfl_xor_sync(SW_FULL_MASK, sx, off);
                             if (lane == 0) s_corr[pass & 7][r] = 8.f * sx;
                         }
+                        if (lane < 8) s_rex[pass & 7][lane] = my_rex;
                         __syncwarp();
                     }
                     if (lane == 0) {
@@ -263,6 +272,7 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
         const int g = lane >> 2, t = lane & 3;
         const int rho = (g >> 1) | ((g & 1) << 2);
         unsigned it = 0, pass = 0;
+        bool clamped = false;                                             // a SiLU*up value left the fp16 range
         // group of the next item, fetched one item ahead (its L2 round trip then passes under the current item)
         int nx_e = 0, nx_n = 0, nx_beg = 0;
         if ((int)blockIdx.x < items) { const int g0 = blockIdx.x / rb_per_group; nx_e = a.gexp[g0]; nx_n = a.gcnt[g0]; nx_beg = a.gbeg[g0]; }
@@ -322,12 +332,14 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
                         for (int i = 0; i < 4; i++) acc[mt][i] += __shfl_down_sync(SW_FULL_MASK, acc[mt][i], 2);
                 }
                 const bool own = m8 || t < 2;
-                float corr[2]; int tok[2];
+                float corr[2], rex[2], rex2[2]; int tok[2];
 #pragma unroll
                 for (int j = 0; j < 2; j++) {
                     tok[j] = c0 + 2 * t + j;
                     const bool ok = own && tok[j] < c0 + ntok;
                     corr[j] = ok ? s_corr[pass & 7][2 * t + j] : 0.f;     // left there by the producer warp
+                    rex[j] = ok ? s_rex[pass & 7][2 * t + j] : 1.f;
+                    rex2[j] = GATEUP ? __frcp_rn(rex[j]) : rex[j] * rex[j];   // gate/up: 2^-e; down: 2^2e (SiLU(gate)*up came in divided by it)
                     if (!ok) tok[j] = -1;
                 }
                 if (GATEUP) {
@@ -343,10 +355,12 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
 #pragma unroll
                         for (int j = 0; j < 2; j++) {
                             if (tok[j] < 0 || !ov) continue;
-                            const float gv = (acc[mt][j] * SW_ACC_SCALE_T - corr[j]) * sg;
+                            // gate at its true size; the up value stays divided by 2^e and the product is divided once more
+                            const float gv = (acc[mt][j] * SW_ACC_SCALE_T - corr[j]) * sg * rex[j];
                             const float uv = (acc[mt][2 + j] * SW_ACC_SCALE_T - corr[j]) * su;
-                            const float y = (gv / (1.f + expf(-gv))) * uv;
+                            const float y = ((gv / (1.f + expf(-gv))) * rex2[j]) * uv;
                             __half hi, lo;
+                            clamped |= fabsf(y * pre) > 65504.f;
                             const float rep = sw_split_f16_t(y * pre, hi, lo);
                             ysum[j] += (o & 1) ? rep * 16.f : rep;
                             __half *row = Y + (size_t)(beg + tok[j]) * (2 * (size_t)OUT);
@@ -372,14 +386,15 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
                         for (int j = 0; j < 2; j++) {
                             if (tok[j] < 0) continue;
                             float *row = Y + (size_t)(beg + tok[j]) * OUT;
-                            if (oa < OUT) row[oa] = (acc[mt][j] * SW_ACC_SCALE_T - corr[j]) * sa;
-                            if (ob < OUT) row[ob] = (acc[mt][2 + j] * SW_ACC_SCALE_T - corr[j]) * sb;
+                            if (oa < OUT) row[oa] = (acc[mt][j] * SW_ACC_SCALE_T - corr[j]) * sa * rex2[j];
+                            if (ob < OUT) row[ob] = (acc[mt][2 + j] * SW_ACC_SCALE_T - corr[j]) * sb * rex2[j];
                         }
                     }
                 }
                 c0 += ntok;
             }
         }
+        if (GATEUP && clamped) atomicOr(a.status, SW_ST_RANGE);
     }
 }
 
@@ -503,6 +518,7 @@ static int sw_launch_q4_tma_t(const SwLaunchCfg &c, const SwQ4Args &a, const SwM
     ka.Ws = a.s; ka.XP = (const unsigned char *)io.XP; ka.xsum = io.xsum; ka.xsum_parts = io.xsum_parts;
     ka.Yout = io.Y; ka.ypart = io.ypart; ka.gexp = a.gexp; ka.gbeg = a.gbeg; ka.gcnt = a.gcnt; ka.Gp = a.G; ka.grow = a.grow;
     ka.status = status; ka.KD = a.KD; ka.OUT = a.OUT; ka.expert_lo = a.expert_lo; ka.expert_cnt = a.expert_cnt;
+    ka.rex = io.rex; ka.srex_out = io.srex_out;
     long long items = (long long)a.max_groups * ((a.OUT + OPI - 1) / OPI);
     long long grid = (long long)c.num_sms * ctas_per_sm;
     if (grid > items) grid = items;

@@ -67,8 +67,11 @@
 #define UM_A_SLOTS 2
 #define UM_ABUF (2 * UM_A_SLOTS)
 #define UM_TMEM_A 256
-#define UM_DQ_WARPS 8
-#define UM_THREADS ((UM_DQ_WARPS + 4 + 3) * 32)   // dequant, epilogue, TMA, two MMA issuers
+#define UM_DQ_WARPS 8                              // dequantise (and two thirds of the epilogue): two per tensor-memory lane quarter
+#define UM_EPI_WARPS 4                             // epilogue only: one per lane quarter
+#define UM_WARP_TMA (UM_DQ_WARPS + UM_EPI_WARPS)
+#define UM_WARP_MMA (UM_WARP_TMA + 1)              // and UM_WARP_MMA + 1
+#define UM_THREADS ((UM_WARP_MMA + 2) * 32)
 
 __device__ __forceinline__ unsigned um_s32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void um_bar_init(unsigned bar, unsigned count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory"); }
@@ -167,21 +170,54 @@ __device__ __forceinline__ void um_split(float v, __half &hi, __half &lo) {
 // xg_hi/xg_lo[slot, :] = fp16 hi/lo of x[grow[slot], :] with the columns of each
 // group of eight in the order 0,4,1,5,2,6,3,7
 // ---------------------------------------------------------------------------
+// rexp[row] = the power of two 2^e with max|x[row, :]| / 2^e in [1, 2) (1 for rows of zeros, infinities, NaNs).
+// One warp per row.  The gather divides every token row by it, so that the fp16 planes carry all rows at the same relative
+// precision whatever the caller's scale; the epilogues multiply back (see k_pack_act, which does the same for the decode kernels).
+__global__ void __launch_bounds__(256)
+k_row_exp(const float *__restrict__ x, int rows, int KD, float *__restrict__ rexp) {
+    const int lane = threadIdx.x & 31;
+    for (int r = blockIdx.x * 8 + (threadIdx.x >> 5); r < rows; r += gridDim.x * 8) {
+        const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)r * KD);
+        float m = 0.f;
+        for (int i = lane; i < (KD >> 2); i += 32) {
+            const float4 a = src[i];
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
+        }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+        float rex = 1.f;
+        if (m > 0.f && m <= 3.0e38f) {
+            int ex;
+            frexpf(m, &ex);
+            rex = ldexpf(1.f, max(-120, min(120, ex - 1)));
+        }
+        if (lane == 0) rexp[r] = rex;
+    }
+}
+
 __global__ void __launch_bounds__(256)
 k_umma_gather(const float *__restrict__ x, const int *__restrict__ grow, const int *__restrict__ npairs, int P, int KD,
-              __half *__restrict__ hi, __half *__restrict__ lo, int *__restrict__ status) {
+              __half *__restrict__ hi, __half *__restrict__ lo, int *__restrict__ status,
+              const float *__restrict__ rexp, float *__restrict__ srex) {
     const int cpr = KD >> 3;
     P = min(P, *npairs);                         // packed rows the dispatch filled (pairs that selected no expert leave none)
     const size_t n = (size_t)P * cpr;
     bool clamped = false;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
         const int slot = (int)(idx / cpr), c8 = (int)(idx - (size_t)slot * cpr);
-        const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)grow[slot] * KD + c8 * 8);
+        const int tokrow = grow[slot];
+        const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)tokrow * KD + c8 * 8);
         const float4 a = src[0], b = src[1];
-        const float v[8] = {a.x, b.x, a.y, b.y, a.z, b.z, a.w, b.w};
+        float inv = 1.f;
+        if (rexp) {
+            const float rex = rexp[tokrow];
+            inv = __frcp_rn(rex);                                  // a power of two: exact
+            if (c8 == 0) srex[slot] = rex;                         // the packed row's copy, for the epilogues
+        }
+        const float v[8] = {a.x * inv, b.x * inv, a.y * inv, b.y * inv, a.z * inv, b.z * inv, a.w * inv, b.w * inv};
         __half h[8], l[8];
 #pragma unroll
-        for (int i = 0; i < 8; i++) { clamped |= fabsf(v[i]) > 65504.f; um_split(v[i], h[i], l[i]); }
+        for (int i = 0; i < 8; i++) { clamped |= !(fabsf(v[i]) <= 65504.f); um_split(v[i], h[i], l[i]); }
         reinterpret_cast<uint4 *>(hi)[idx] = *reinterpret_cast<uint4 *>(h);
         if (lo) reinterpret_cast<uint4 *>(lo)[idx] = *reinterpret_cast<uint4 *>(l);
     }
@@ -217,6 +253,7 @@ struct UmArgs {
     int *status;
     int KD, OUT, expert_lo;
     int terms;                     // fp16 terms per activation: 1 = hi only, 2 = hi + lo
+    const float *srex;             // per packed row: the power of two its token row was divided by (null = 1)
 };
 
 template <bool GATEUP>
@@ -231,6 +268,11 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
     __shared__ unsigned long long b_raw_full[UM_MAX_STAGES], b_raw_free[UM_MAX_STAGES], b_a_full[UM_ABUF], b_acc_full[2], b_acc_free;
     __shared__ unsigned s_tmem;
     __shared__ int s_abort;
+    // the powers of two of the item's (<= 128) packed rows, left here by the epilogue warps while the item's MMAs run
+    // (two buffers: the dequantising warps may still be reading one item's when the next item's are fetched)
+    // [0]: 2^e of each row; [1]: 2^-e (gate/up only: the down product leaves its rows divided by 2^2e for the combine step)
+    __shared__ __align__(16) float s_srex[2][2][128];
+    __shared__ unsigned long long b_srex[2];
     unsigned char *smem = (unsigned char *)(((uintptr_t)um_dyn + 1023) & ~(uintptr_t)1023);
     const unsigned STG = UM_STAGES_FOR(a.terms), SBYTES = UM_STAGE_BYTES(a.terms);   // ring depth and slot size
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -248,11 +290,12 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
         for (int i = 0; i < UM_MAX_STAGES; i++) { um_bar_init(um_s32(&b_raw_full[i]), 1); um_bar_init(um_s32(&b_raw_free[i]), 2); }
         for (int i = 0; i < UM_ABUF; i++) um_bar_init(um_s32(&b_a_full[i]), UM_DQ_WARPS / 2);
         for (int i = 0; i < 2; i++) um_bar_init(um_s32(&b_acc_full[i]), 1);
-        um_bar_init(um_s32(&b_acc_free), 12);                           // four epilogue warps and the eight dequantising warps
+        for (int i = 0; i < 2; i++) um_bar_init(um_s32(&b_srex[i]), UM_EPI_WARPS);
+        um_bar_init(um_s32(&b_acc_free), UM_DQ_WARPS + UM_EPI_WARPS);   // the epilogue warps and the dequantising warps, which take shares of it
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == UM_DQ_WARPS + 5) {                                      // all 512 columns of tensor memory
+    if (warp == UM_WARP_MMA) {                                          // all 512 columns of tensor memory
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(um_s32(&s_tmem)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -286,6 +329,12 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
             if (lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; }
             return false;
         }
+        if (GATEUP && !um_bar_wait(um_s32(&b_srex[nitem & 1]), (nitem >> 1) & 1, abortp)) {
+            if (lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; }
+            return false;
+        }
+        const float4 *srex4 = reinterpret_cast<const float4 *>(s_srex[nitem & 1][0]);
+        const float4 *saux4 = reinterpret_cast<const float4 *>(s_srex[nitem & 1][1]);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned t0 = tmem + ((unsigned)(q * 32) << 16), t1 = t0 + 128;   // tile 0 / tile 1 of this lane
         if (GATEUP) {
@@ -295,14 +344,21 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
             __half *Yh = reinterpret_cast<__half *>(a.Y0), *Yl = reinterpret_cast<__half *>(a.Y1);
             const int pcol = um_perm8(o);
             for (int cb = 16 * part; cb < n; cb += 48) {
-                float g[16], u[16];
+                float g[16], u[16], rex[16], rinv[16];
+#pragma unroll
+                for (int j4 = 0; j4 < 4; j4++) {
+                    const float4 r = srex4[(cb >> 2) + j4], ri = saux4[(cb >> 2) + j4];
+                    rex[4 * j4] = r.x; rex[4 * j4 + 1] = r.y; rex[4 * j4 + 2] = r.z; rex[4 * j4 + 3] = r.w;
+                    rinv[4 * j4] = ri.x; rinv[4 * j4 + 1] = ri.y; rinv[4 * j4 + 2] = ri.z; rinv[4 * j4 + 3] = ri.w;
+                }
                 um_ld16(t0 + cb, g);
                 um_ld16(t1 + cb, u);
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     if (cb + j < n && o < OUT) {
-                        const float gv = g[j] * sg;
-                        const float y = (gv / (1.f + expf(-gv))) * (u[j] * su);
+                        // gate at its true size; the up value stays divided by 2^e and the product is divided once more
+                        const float gv = g[j] * sg * rex[j];
+                        const float y = ((gv / (1.f + expf(-gv))) * rinv[j]) * (u[j] * su);
                         __half hi, lo; um_split(y, hi, lo);
                         clamped |= fabsf(y) > 65504.f;
                         const size_t pos = (size_t)(row0 + cb + j) * OUT + pcol;
@@ -317,6 +373,8 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
             for (int t = 0; t < 2; t++) {
                 const int o = pr * 256 + t * 128 + trow;
                 const float sc = o < OUT ? ws[o] : 0.f;
+                // (SiLU(gate)*up came in divided by the square of the row's power of two: the slot rows stay divided by it,
+                // and the combine step multiplies the token's sum back)
                 for (int cb = 16 * part; cb < n; cb += 48) {
                     float v[16];
                     um_ld16((t ? t1 : t0) + cb, v);
@@ -332,7 +390,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
         return true;
     };
 
-    if (warp == UM_DQ_WARPS + 4) {
+    if (warp == UM_WARP_TMA) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             unsigned kk = 0;
@@ -363,14 +421,14 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
                 }
             }
         }
-    } else if (warp >= UM_DQ_WARPS + 5) {
+    } else if (warp >= UM_WARP_MMA) {
         // ------------------------------ MMA issuers ------------------------------
         // Two warps: issuer t multiplies tile t of the pair into its own accumulator columns
         // [128 t, 128 t + R).  One MMA of N = R per 16 columns and term: A (the dequantised weights) from tensor
         // memory, B (the fp16 activations) from the slot.
         // The whole warp runs this loop with warp-uniform values; an elected lane issues the MMAs and the commits.
         {
-            const int t = __shfl_sync(0xffffffffu, warp, 0) - (UM_DQ_WARPS + 5);
+            const int t = __shfl_sync(0xffffffffu, warp, 0) - UM_WARP_MMA;
             unsigned ks = 0, nitem = 0;                                  // step and item counters
             for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, nitem++) {
                 int gi, c0, pr; decode(item, gi, c0, pr);
@@ -412,6 +470,8 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
         // Two groups of four warps: group t dequantises tile t of every step.  A thread owns one tile row (tensor-memory
         // lane 32 * (warp % 4) + lane): it reads the row's 64 raw bytes of the step from the slot, expands them to 128 exact
         // fp16 integers (nibble - 8) and stores them to the 64 columns of A tile (2 * step + t) % 4 in four pieces.
+        // (Sixteen warps with half a row each were slower: 1.02 against 0.96 ms on the 4096-token prefill.  Eight warps
+        // stream 146 bytes per clock into tensor memory next to the MMAs, sixteen 186.)
         const int tsel = warp >> 2, q = warp & 3;
         const int trow = q * 32 + lane;
         const unsigned lane_base = (unsigned)(q * 32) << 16;
@@ -457,14 +517,24 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
         // ------------------------------ epilogue warps (one TMEM lane quarter each; share 0 of 3) ------------------------------
         unsigned nitem = 0;
         bool clamped = false;
-        for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, nitem++)
+        for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, nitem++) {
+            if (GATEUP) {   // this item's per-row powers of two -> shared memory (128 entries, ones past the chunk's end)
+                int gi, c0, pr; decode(item, gi, c0, pr);
+                const int n = min(128, a.gcnt[gi] - c0), row0 = a.gbeg[gi] + c0, i = (warp - UM_DQ_WARPS) * 32 + lane;
+                const float r = (a.srex && i < n) ? a.srex[row0 + i] : 1.f;
+                s_srex[nitem & 1][0][i] = r;
+                s_srex[nitem & 1][1][i] = __frcp_rn(r);
+                __syncwarp();
+                if (lane == 0) um_bar_arrive(um_s32(&b_srex[nitem & 1]));
+            }
             if (!epilogue_share(item, nitem, 0, clamped)) break;
+        }
         if (clamped) atomicOr(a.status, SW_ST_RANGE);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == UM_DQ_WARPS + 5) {
+    if (warp == UM_WARP_MMA) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(512) : "memory");
     }
@@ -502,12 +572,25 @@ static int um_make_map(CUtensorMap *m, CUtensorMapDataType dt, int esize, const 
 
 bool sw_umma_available() { return um_get_encode() != nullptr; }
 
-int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow, const int *npairs, int P, int KD, void *hi, void *lo, int *status) {
+int sw_launch_row_exp(const SwLaunchCfg &c, const float *x, int rows, int KD, float *rexp) {
+    if (rows <= 0) return 0;
+    if (KD % 4) return -1;
+    int grid = (rows + 7) / 8;
+    if (grid > c.num_sms * 8) grid = c.num_sms * 8;
+    k_row_exp<<<grid, 256, 0, c.stream>>>(x, rows, KD, rexp);
+    sw_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// rexp / srex (both or neither): rexp[token row] = the power of two to divide the row by, srex[packed row] receives a copy
+int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow, const int *npairs, int P, int KD, void *hi, void *lo, int *status,
+                          const float *rexp, float *srex) {
     if (P <= 0) return 0;
+    if ((rexp == nullptr) != (srex == nullptr)) return -1;
     size_t n = (size_t)P * (KD / 8);
     long long grid = (long long)((n + 255) / 256);
     if (grid > (long long)c.num_sms * 16) grid = (long long)c.num_sms * 16;
-    k_umma_gather<<<(unsigned)grid, 256, 0, c.stream>>>(x, grow, npairs, P, KD, (__half *)hi, (__half *)lo, status);
+    k_umma_gather<<<(unsigned)grid, 256, 0, c.stream>>>(x, grow, npairs, P, KD, (__half *)hi, (__half *)lo, status, rexp, srex);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
@@ -521,7 +604,8 @@ int sw_launch_umma_chunks(const SwLaunchCfg &c, const SwQ4Args &a, int *nchunks,
 // act_hi/act_lo: fp16 [max_rows, KD] in packed-slot order (permuted columns).
 // gate/up: Y0/Y1 = fp16 hi/lo [max_rows, OUT]; down: Y0 = f32 [max_rows, OUT].
 int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_hi, const void *act_lo, void *Y0, void *Y1,
-                      const int *nchunks, const void *chunks, int max_chunks, int *status, long long wrows_total, bool gateup, int terms) {
+                      const int *nchunks, const void *chunks, int max_chunks, int *status, long long wrows_total, bool gateup, int terms,
+                      const float *srex) {
     if (a.max_rows <= 0) return 0;
     if (terms != 1 && terms != 2) return -1;
     if (terms == 1) act_lo = act_hi;                                    // never read; keeps the tensor maps valid
@@ -544,7 +628,7 @@ int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_h
             return 1; }) <= 0) return -1;
     UmArgs ka;
     ka.Ws = a.s; ka.Y0 = Y0; ka.Y1 = Y1; ka.gexp = a.gexp; ka.gbeg = a.gbeg; ka.gcnt = a.gcnt; ka.nchunks = nchunks;
-    ka.chunks = (const int2 *)chunks; ka.status = status; ka.KD = a.KD; ka.OUT = a.OUT; ka.expert_lo = a.expert_lo; ka.terms = terms;
+    ka.chunks = (const int2 *)chunks; ka.status = status; ka.KD = a.KD; ka.OUT = a.OUT; ka.expert_lo = a.expert_lo; ka.terms = terms; ka.srex = srex;
     const int pairs = a.OUT / (gateup ? 128 : 256);
     long long items = (long long)max_chunks * pairs;
     long long grid = c.num_sms;                        // one CTA per SM (shared memory and tensor memory are sized for that)
