@@ -110,6 +110,19 @@ __device__ __forceinline__ void um_mma_ta_elect(unsigned d_tmem, unsigned a_tmem
     asm volatile("{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
                  :: "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the same with the election done once by the caller (um_elect): `leader` is 1 in the elected lane, 0 elsewhere
+__device__ __forceinline__ unsigned um_elect() {
+    unsigned l;
+    asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\tselp.u32 %0, 1, 0, e;\n\t}" : "=r"(l));
+    return l;
+}
+__device__ __forceinline__ void um_mma_ta_lead(unsigned leader, unsigned d_tmem, unsigned a_tmem, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p, e;\n\tsetp.ne.b32 e, %5, 0;\n\tsetp.ne.b32 p, %4, 0;\n\t@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 :: "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(leader) : "memory");
+}
+__device__ __forceinline__ void um_commit_lead(unsigned leader, unsigned bar) {
+    asm volatile("{\n\t.reg .pred e;\n\tsetp.ne.b32 e, %1, 0;\n\t@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" :: "r"(bar), "r"(leader) : "memory");
+}
 // both operands through shared-memory descriptors
 __device__ __forceinline__ void um_mma_elect(unsigned d_tmem, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
     asm volatile("{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
@@ -343,27 +356,34 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
             const float sg = o < OUT ? ws[o] : 0.f, su = o < OUT ? ws[OUT + o] : 0.f;
             __half *Yh = reinterpret_cast<__half *>(a.Y0), *Yl = reinterpret_cast<__half *>(a.Y1);
             const int pcol = um_perm8(o);
+            // This loop is not hidden under MMAs (one accumulator buffer) and it is instruction-bound, so it is kept short:
+            // fast exp and reciprocal (SiLU to ~3e-7 relative, far inside what the fp16 operands leave of the bar),
+            // running pointers, the lo term only when it is stored.
             for (int cb = 16 * part; cb < n; cb += 48) {
                 float g[16], u[16], rex[16], rinv[16];
 #pragma unroll
                 for (int j4 = 0; j4 < 4; j4++) {
                     const float4 r = srex4[(cb >> 2) + j4], ri = saux4[(cb >> 2) + j4];
-                    rex[4 * j4] = r.x; rex[4 * j4 + 1] = r.y; rex[4 * j4 + 2] = r.z; rex[4 * j4 + 3] = r.w;
-                    rinv[4 * j4] = ri.x; rinv[4 * j4 + 1] = ri.y; rinv[4 * j4 + 2] = ri.z; rinv[4 * j4 + 3] = ri.w;
+                    rex[4 * j4] = r.x * sg; rex[4 * j4 + 1] = r.y * sg; rex[4 * j4 + 2] = r.z * sg; rex[4 * j4 + 3] = r.w * sg;
+                    rinv[4 * j4] = ri.x * su; rinv[4 * j4 + 1] = ri.y * su; rinv[4 * j4 + 2] = ri.z * su; rinv[4 * j4 + 3] = ri.w * su;
                 }
                 um_ld16(t0 + cb, g);
                 um_ld16(t1 + cb, u);
+                if (o < OUT) {
+                    __half *ph = Yh + (size_t)(row0 + cb) * OUT + pcol, *pl = Yl + (size_t)(row0 + cb) * OUT + pcol;
+                    const int m = min(16, n - cb);
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    if (cb + j < n && o < OUT) {
-                        // gate at its true size; the up value stays divided by 2^e and the product is divided once more
-                        const float gv = g[j] * sg * rex[j];
-                        const float y = ((gv / (1.f + expf(-gv))) * rinv[j]) * (u[j] * su);
-                        __half hi, lo; um_split(y, hi, lo);
-                        clamped |= fabsf(y) > 65504.f;
-                        const size_t pos = (size_t)(row0 + cb + j) * OUT + pcol;
-                        Yh[pos] = hi;
-                        if (two_terms) Yl[pos] = lo;
+                    for (int j = 0; j < 16; j++) {
+                        if (j < m) {
+                            // gate at its true size (x 2^e); the up value stays divided by 2^e and the product is divided once more
+                            const float gv = g[j] * rex[j];
+                            float y = __fdividef(gv, 1.f + __expf(-gv)) * (u[j] * rinv[j]);
+                            clamped |= !(fabsf(y) <= 65504.f);
+                            y = fminf(fmaxf(y, -65504.f), 65504.f);
+                            const __half hi = __float2half_rn(y);
+                            ph[(size_t)j * OUT] = hi;
+                            if (two_terms) pl[(size_t)j * OUT] = __float2half_rn(y - __half2float(hi));
+                        }
                     }
                 }
             }
@@ -429,6 +449,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
         // The whole warp runs this loop with warp-uniform values; an elected lane issues the MMAs and the commits.
         {
             const int t = __shfl_sync(0xffffffffu, warp, 0) - UM_WARP_MMA;
+            const unsigned leader = um_elect();                         // the same lane issues every MMA and every commit
             unsigned ks = 0, nitem = 0;                                  // step and item counters
             for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, nitem++) {
                 int gi, c0, pr; decode(item, gi, c0, pr);
@@ -454,15 +475,15 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
 #pragma unroll
                     for (int k = 0; k < 8; k++) {                       // 16 columns per MMA: 8 tensor-memory columns of A, 32 bytes of each B row
                         const uint64_t dh = um_desc(bb + (k >> 2) * bt) + 2 * (k & 3);
-                        um_mma_ta_elect(d_tmem, ta + 8 * k, dh, idesc, (st | k) ? 1u : 0u);
-                        if (two_terms) um_mma_ta_elect(d_tmem, ta + 8 * k, um_desc(bb + (2 + (k >> 2)) * bt) + 2 * (k & 3), idesc, 1u);
+                        um_mma_ta_lead(leader, d_tmem, ta + 8 * k, dh, idesc, (st | k) ? 1u : 0u);
+                        if (two_terms) um_mma_ta_lead(leader, d_tmem, ta + 8 * k, um_desc(bb + (2 + (k >> 2)) * bt) + 2 * (k & 3), idesc, 1u);
                     }
                     // one commit per step and issuer: when both have arrived the slot returns to the TMA warp and the
                     // step's two A tiles to the dequantising warps
-                    um_commit_elect(um_s32(&b_raw_free[s]));
+                    um_commit_lead(leader, um_s32(&b_raw_free[s]));
                 }
                 if (!ok) { if (lane == 0) atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
-                um_commit_elect(um_s32(&b_acc_full[t]));
+                um_commit_lead(leader, um_s32(&b_acc_full[t]));
             }
         }
     } else if (warp < UM_DQ_WARPS) {
