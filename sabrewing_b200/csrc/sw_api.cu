@@ -30,6 +30,7 @@ const SwTuning &sw_tuning() {
         const char *f = getenv("SW_FORCE_SIMT");
         v.force_simt = (f && *f && *f != '0') ? 1 : 0;
         if (v.force_simt) v.expert_pref = 0;
+        v.row_scale = sw_env_int("SW_ROW_SCALE", 1);
         v.umma_min_rows = sw_env_int("SW_UMMA_MIN_ROWS", 16);    // mean rows per group from which the tcgen05 kernels win (measured)
         v.tma_mt = sw_env_int("SW_TMA_MT", 0);
         if (v.tma_mt != 1 && v.tma_mt != 2) v.tma_mt = 0;
@@ -144,6 +145,7 @@ static inline size_t sw_pad64(size_t n) { return (n + 63) & ~(size_t)63; }
 static inline SwSums sw_sums_layout(float *sums, int rows_x, int max_rows) {
     SwSums l;
     l.xsum = sums; l.rexp = l.xsum + sw_pad64(rows_x); l.srex = l.rexp + sw_pad64(rows_x); l.ypart = l.srex + sw_pad64(max_rows);
+    if (!sw_tuning().row_scale) l.rexp = l.srex = nullptr;             // every consumer takes null as "all ones"
     return l;
 }
 static inline size_t sw_sums_bytes(size_t T, size_t P, size_t I) { return (2 * sw_pad64(T) + sw_pad64(P) + P * (I / 8 + 1)) * 4; }
@@ -365,7 +367,7 @@ static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, 
         __half *xh = (__half *)um->xg, *xl = xh + (size_t)P * D;
         __half *gh = (__half *)glu, *gl = gh + (size_t)P * I;
         const SwSums sl = sw_sums_layout(sums, rows_x, a.max_rows);
-        if (sw_launch_row_exp(cfg, x, rows_x, D, sl.rexp)) return -1;
+        if (sl.rexp && sw_launch_row_exp(cfg, x, rows_x, D, sl.rexp)) return -1;
         if (sw_launch_umma_gather(cfg, x, a.grow, a.G + 1, P, D, xh, umma_terms == 2 ? xl : nullptr, status, sl.rexp, sl.srex)) return -1;
         if (sw_launch_umma_chunks(cfg, a, um->nchunks, um->chunks)) return -1;
         a.q = (const uint8_t *)gu_q; a.s = gu_s; a.KD = D; a.OUT = I;

@@ -62,6 +62,7 @@ struct SwPerDevice {
 struct SwTuning {
     int expert_pref;     // SW_EXPERT_PATH: 2 default, 3 umma, 4 tma always, 1 mma, 0 simt
     int umma_min_rows;   // SW_UMMA_MIN_ROWS: mean rows per group from which the tcgen05 kernels are used
+    int row_scale;       // SW_ROW_SCALE (default 1): 0 switches the per-token power-of-two normalisation of the tensor-core paths off (measurements)
     int force_simt;      // SW_FORCE_SIMT
     int tma_mt;          // SW_TMA_MT: 0 = choose, 1 or 2
     int tma_p;           // SW_TMA_P: ring depth of the TMA decode kernels (0 = default)

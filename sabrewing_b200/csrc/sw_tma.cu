@@ -204,10 +204,7 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
 #pragma unroll
                 for (int r = 0; r < 8; r++) v[r] = 0.f;
                 float my_rex = 1.f;                                                // lane r: the power of two of row r
-                if (lane < ntok && a.rex) {
-                    my_rex = a.rex[GATEUP ? a.grow[beg + c0 + lane] : beg + c0 + lane];
-                    if (GATEUP && a.srex_out && rb == 0) a.srex_out[beg + c0 + lane] = my_rex;
-                }
+                if (lane < ntok && a.rex) my_rex = a.rex[GATEUP ? a.grow[beg + c0 + lane] : beg + c0 + lane];   // used at the join below
                 for (int k = lane; k < a.xsum_parts; k += 32) {
                     float ld[8];
 #pragma unroll
@@ -233,6 +230,7 @@ k_q4_tma(const __grid_constant__ CUtensorMap tmW, const SwTmaArgs a) {
                             if (lane == 0) s_corr[pass & 7][r] = 8.f * sx;
                         }
                         if (lane < 8) s_rex[pass & 7][lane] = my_rex;
+                        if (GATEUP && a.srex_out && rb == 0 && lane < ntok) a.srex_out[beg + c0 + lane] = my_rex;
                         __syncwarp();
                     }
                     if (lane == 0) {
