@@ -326,6 +326,7 @@ int sw_launch_q8_rows(const SwLaunchCfg &c, const float *x, const int8_t *W, con
 // (the reference's multiply-add, contracted by its build), then optionally
 // *route_scale, + add rows, and store or accumulate.
 // ---------------------------------------------------------------------------
+template <int KB>          // ranks whose slot rows are in flight at once: top-k of 8, 10-12 and up to 16 take one round
 __global__ void __launch_bounds__(256)
 k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const int *__restrict__ sel,
           const float *__restrict__ w, const float *__restrict__ add, int add_slices, float *__restrict__ out,
@@ -336,11 +337,11 @@ k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const 
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
         const int t = (int)(idx / D4), i4 = (int)(idx - (size_t)t * D4);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        // eight ranks at a time: indices first, then all slot rows (independent loads), then the FMAs in rank order
-        for (int a0 = 0; a0 < K; a0 += 8) {
-            float wa[8]; int slot[8];
+        // KB ranks at a time: indices first, then all slot rows (independent loads), then the FMAs in rank order
+        for (int a0 = 0; a0 < K; a0 += KB) {
+            float wa[KB]; int slot[KB];
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
+            for (int j = 0; j < KB; j++) {
                 const int a = a0 + j;
                 slot[j] = -1; wa[j] = 0.f;
                 if (a < K) {
@@ -348,12 +349,12 @@ k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const 
                     if (e >= 0 && e < expert_cnt) { slot[j] = rowof[t * K + a]; wa[j] = w[t * K + a]; }
                 }
             }
-            float4 v[8];
+            float4 v[KB];
 #pragma unroll
-            for (int j = 0; j < 8; j++)
+            for (int j = 0; j < KB; j++)
                 if (slot[j] >= 0) v[j] = reinterpret_cast<const float4 *>(slots + (size_t)slot[j] * D)[i4];
 #pragma unroll
-            for (int j = 0; j < 8; j++)
+            for (int j = 0; j < KB; j++)
                 if (slot[j] >= 0) {
                     acc.x = fmaf(wa[j], v[j].x, acc.x); acc.y = fmaf(wa[j], v[j].y, acc.y);
                     acc.z = fmaf(wa[j], v[j].z, acc.z); acc.w = fmaf(wa[j], v[j].w, acc.w);
@@ -390,7 +391,13 @@ int sw_launch_combine(const SwLaunchCfg &c, const float *slots, const int *rowof
     size_t n = (size_t)T * (D / 4);
     long long grid = (long long)((n + 255) / 256);
     if (grid > (long long)c.num_sms * 16) grid = (long long)c.num_sms * 16;
-    k_combine<<<(unsigned)grid, 256, 0, c.stream>>>(slots, rowof, sel, w, add, add_slices, out, T, K, D, route_scale, mode, expert_lo, expert_cnt, row_gate, row_back);
+    // wide rounds pay when the step is latency-bound (few rows); with many rows their registers cost more than the second round
+    if (K <= 8 || K > 16 || T > 256)
+        k_combine<8><<<(unsigned)grid, 256, 0, c.stream>>>(slots, rowof, sel, w, add, add_slices, out, T, K, D, route_scale, mode, expert_lo, expert_cnt, row_gate, row_back);
+    else if (K <= 12)
+        k_combine<12><<<(unsigned)grid, 256, 0, c.stream>>>(slots, rowof, sel, w, add, add_slices, out, T, K, D, route_scale, mode, expert_lo, expert_cnt, row_gate, row_back);
+    else
+        k_combine<16><<<(unsigned)grid, 256, 0, c.stream>>>(slots, rowof, sel, w, add, add_slices, out, T, K, D, route_scale, mode, expert_lo, expert_cnt, row_gate, row_back);
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -278,7 +278,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
           const __grid_constant__ CUtensorMap tmL64, const __grid_constant__ CUtensorMap tmL128,
           const UmArgs a) {
     extern __shared__ unsigned char um_dyn[];
-    __shared__ unsigned long long b_raw_full[UM_MAX_STAGES], b_raw_free[UM_MAX_STAGES], b_a_full[UM_ABUF], b_acc_full[2], b_acc_free;
+    __shared__ unsigned long long b_raw_full[UM_MAX_STAGES], b_raw_free[UM_MAX_STAGES], b_a_full[UM_ABUF], b_a_free[UM_ABUF], b_acc_full[2], b_acc_free;
     __shared__ unsigned s_tmem;
     __shared__ int s_abort;
     // the powers of two of the item's (<= 128) packed rows, left here by the epilogue warps while the item's MMAs run
@@ -301,7 +301,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < UM_MAX_STAGES; i++) { um_bar_init(um_s32(&b_raw_full[i]), 1); um_bar_init(um_s32(&b_raw_free[i]), 2); }
-        for (int i = 0; i < UM_ABUF; i++) um_bar_init(um_s32(&b_a_full[i]), UM_DQ_WARPS / 2);
+        for (int i = 0; i < UM_ABUF; i++) { um_bar_init(um_s32(&b_a_full[i]), UM_DQ_WARPS / 2); um_bar_init(um_s32(&b_a_free[i]), 1); }
         for (int i = 0; i < 2; i++) um_bar_init(um_s32(&b_acc_full[i]), 1);
         for (int i = 0; i < 2; i++) um_bar_init(um_s32(&b_srex[i]), UM_EPI_WARPS);
         um_bar_init(um_s32(&b_acc_free), UM_DQ_WARPS + UM_EPI_WARPS);   // the epilogue warps and the dequantising warps, which take shares of it
@@ -478,8 +478,9 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
                         um_mma_ta_lead(leader, d_tmem, ta + 8 * k, dh, idesc, (st | k) ? 1u : 0u);
                         if (two_terms) um_mma_ta_lead(leader, d_tmem, ta + 8 * k, um_desc(bb + (2 + (k >> 2)) * bt) + 2 * (k & 3), idesc, 1u);
                     }
-                    // one commit per step and issuer: when both have arrived the slot returns to the TMA warp and the
-                    // step's two A tiles to the dequantising warps
+                    // two commits per step and issuer: the A tile goes back to this tile's dequantising warps (who then do
+                    // not wait for the other tile's MMAs), and when both issuers have arrived the slot returns to the TMA warp
+                    um_commit_lead(leader, um_s32(&b_a_free[b]));
                     um_commit_lead(leader, um_s32(&b_raw_free[s]));
                 }
                 if (!ok) { if (lane == 0) atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; break; }
@@ -502,8 +503,8 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
             for (int st = 0; st < NST; st++, ks++) {
                 const unsigned kk = 2 * ks + tsel, b = kk % UM_ABUF, s = ks % STG;
                 bool ok = um_bar_wait(um_s32(&b_raw_full[s]), (ks / STG) & 1, abortp);
-                // A tile b was last read by the MMAs of the step UM_A_SLOTS back: wait until that step has retired
-                if (ok && ks >= UM_A_SLOTS) ok = um_bar_wait(um_s32(&b_raw_free[(ks - UM_A_SLOTS) % STG]), ((ks - UM_A_SLOTS) / STG) & 1, abortp);
+                // A tile b was last read by this tile's MMAs of the step UM_A_SLOTS back: wait until they have retired
+                if (ok && ks >= UM_A_SLOTS) ok = um_bar_wait(um_s32(&b_a_free[b]), ((kk / UM_ABUF) - 1) & 1, abortp);
                 if (!ok) { if (lane == 0) { atomicOr(a.status, SW_ST_TIMEOUT); *abortp = 1; } break; }
                 // the row's 64 bytes; the TMA wrote them under the 64-byte swizzle: 16-byte chunk c sits at c ^ ((row >> 1) & 3)
                 const unsigned char *rrow = smem + s * SBYTES + (size_t)(tsel * 128 + trow) * 64;
