@@ -337,6 +337,10 @@ k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const 
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
         const int t = (int)(idx / D4), i4 = (int)(idx - (size_t)t * D4);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        // The tcgen05 expert kernels worked on the token row divided by the power of two row_back[t] and left the slot rows
+        // divided by its square: the weights carry it back (a power of two: every product and sum scales exactly).
+        float b2 = 1.f;
+        if (row_back) { const float b = row_back[t]; b2 = b * b; }
         // KB ranks at a time: indices first, then all slot rows (independent loads), then the FMAs in rank order
         for (int a0 = 0; a0 < K; a0 += KB) {
             float wa[KB]; int slot[KB];
@@ -346,7 +350,7 @@ k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const 
                 slot[j] = -1; wa[j] = 0.f;
                 if (a < K) {
                     const int e = sel[t * K + a] - expert_lo;
-                    if (e >= 0 && e < expert_cnt) { slot[j] = rowof[t * K + a]; wa[j] = w[t * K + a]; }
+                    if (e >= 0 && e < expert_cnt) { slot[j] = rowof[t * K + a]; wa[j] = w[t * K + a] * b2; }
                 }
             }
             float4 v[KB];
@@ -359,12 +363,6 @@ k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const 
                     acc.x = fmaf(wa[j], v[j].x, acc.x); acc.y = fmaf(wa[j], v[j].y, acc.y);
                     acc.z = fmaf(wa[j], v[j].z, acc.z); acc.w = fmaf(wa[j], v[j].w, acc.w);
                 }
-        }
-        if (row_back) {
-            // the tcgen05 expert kernels worked on the token row divided by the power of two row_back[t] and left the
-            // slot rows divided by its square: multiplying the sum back is exact
-            const float b = row_back[t], b2 = b * b;
-            acc.x *= b2; acc.y *= b2; acc.z *= b2; acc.w *= b2;
         }
         if (mode & 1) { acc.x *= route_scale; acc.y *= route_scale; acc.z *= route_scale; acc.w *= route_scale; }
         if (mode & 2) {
