@@ -199,6 +199,7 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
         E * 4, E * 4, E * 4,  // gexp gbeg gcnt
         P * 4, P * 4,         // grow rowof
         256,                  // status
+        sw_dispatch_scratch_ints(P, E) * 4,   // scratch of the many-CTA dispatch
         P * I * 4,            // glu
         P * D * 4,            // slots
         T * 4 + 256,          // row_gate: per-token weight of a gated shared expert
@@ -223,9 +224,11 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
     c->r.scores = (float *)take(); c->r.sel = (int *)take(); c->r.w = (float *)take(); c->r.G = (int *)take();
     c->r.gexp = (int *)take(); c->r.gbeg = (int *)take(); c->r.gcnt = (int *)take();
     c->r.grow = (int *)take(); c->r.rowof = (int *)take(); c->r.status = (int *)take();
+    c->r.dpar = (int *)take(); c->r.dpar_ints = sw_dispatch_scratch_ints(P, E);
     c->glu = (float *)take(); c->slots = (float *)take(); c->row_gate = (float *)take(); c->sglu = (float *)take(); c->so = (float *)take();
     c->routed = (float *)take(); c->dx = (float *)take(); c->dout = (float *)take(); c->xp = take(); c->sums = (float *)take(); c->spk = take(); c->um.xg = take(); { char *q = (char *)take(); c->um.nchunks = (int *)q; c->um.chunks = q + 256; } c->rpart = (double *)take();
     cudaMemsetAsync(c->r.G, 0, 256, c->stream); cudaMemsetAsync(c->r.status, 0, 256, c->stream);
+    cudaMemsetAsync(c->r.dpar, 0, 128, c->stream);              // the ticket of the many-CTA dispatch
     if (sw_malloc_host((void **)&c->hx, T * D * 4) != cudaSuccess || sw_malloc_host((void **)&c->hout, T * D * 4) != cudaSuccess) {
         cudaGetLastError(); sw_moe_ctx_destroy(c);
         return sw_fail("ctx_create: pinned staging allocation failed");

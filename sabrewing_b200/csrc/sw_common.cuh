@@ -28,7 +28,11 @@ struct SwRouting {
     int   *grow;     // [T*K] packed row -> token row
     int   *rowof;    // [T*K] (token, rank) -> packed row
     int   *status;   // [1]
+    int   *dpar;     // scratch of the many-CTA dispatch (null: one CTA does it), dpar_ints ints
+    size_t dpar_ints;
 };
+// ints of scratch the many-CTA dispatch needs for P pairs over E experts
+size_t sw_dispatch_scratch_ints(size_t P, size_t E);
 
 struct SwLaunchCfg {
     int num_sms;

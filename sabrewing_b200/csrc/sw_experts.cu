@@ -390,7 +390,7 @@ int sw_launch_combine(const SwLaunchCfg &c, const float *slots, const int *rowof
     long long grid = (long long)((n + 255) / 256);
     if (grid > (long long)c.num_sms * 16) grid = (long long)c.num_sms * 16;
     // wide rounds pay when the step is latency-bound (few rows); with many rows their registers cost more than the second round
-    if (K <= 8 || K > 16 || T > 256)
+    if (K <= 8 || K > 16 || T > 64)
         k_combine<8><<<(unsigned)grid, 256, 0, c.stream>>>(slots, rowof, sel, w, add, add_slices, out, T, K, D, route_scale, mode, expert_lo, expert_cnt, row_gate, row_back);
     else if (K <= 12)
         k_combine<12><<<(unsigned)grid, 256, 0, c.stream>>>(slots, rowof, sel, w, add, add_slices, out, T, K, D, route_scale, mode, expert_lo, expert_cnt, row_gate, row_back);

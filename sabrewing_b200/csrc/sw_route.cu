@@ -144,8 +144,92 @@ k_router_dmma(const float *__restrict__ x, const WT *__restrict__ W, double *__r
     }
 }
 
+// The same product for many token rows (prefill, large batches): a CTA computes a tile of 64 experts x 64 token rows
+// from operands staged in shared memory AS DOUBLES, 32 columns per stage, two stages.  The kernel above streams its
+// operands from L2 into registers for every 8 x 32 tile (3.6 flop per byte: at 4096 tokens it moves 5.8 TB/s out of L2
+// and runs at half the fp64 tensor rate) and converts every value once per use; here a value is loaded and converted
+// once per 64 x 64 tile.  Eight warps, each 16 experts x 32 tokens = 2 x 4 MMA tiles.  Rows are padded to 36 doubles:
+// the 16 lanes of a half-warp (4 rows x 4 k-slots) then read 32 different banks.
+#define RT_TILE 64
+#define RT_LD 36
+#define RT_SMEM (2 * 2 * RT_TILE * RT_LD * 8)
+template <typename WT>
+__global__ void __launch_bounds__(256)
+k_router_dmma_tiled(const float *__restrict__ x, const WT *__restrict__ W, double *__restrict__ part,
+                    int T, int D, int E, int KS, int slice) {
+    extern __shared__ __align__(16) unsigned char rt_dyn[];
+    double (*sm)[2][RT_TILE][RT_LD] = reinterpret_cast<double (*)[2][RT_TILE][RT_LD]>(rt_dyn);   // [buffer][A|B][row][col]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, c = lane & 3;
+    const int etiles = (E + RT_TILE - 1) / RT_TILE, ttiles = (T + RT_TILE - 1) / RT_TILE;
+    const int items = etiles * ttiles * KS;
+    const int frow = tid >> 2, fcol = (tid & 3) * 8;          // this thread's row and first column when filling a stage
+    const int m0 = (warp & 3) * 16, n0 = (warp >> 2) * 32;    // this warp's experts and tokens inside the tile
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        // the expert tiles of one (token tile, slice) are neighbours: the token rows stay in L2
+        const int et = item % etiles, rest = item / etiles, ks = rest % KS, tt = rest / KS;
+        const int k0 = ks * slice, k1 = min(D, k0 + slice);
+        const int e0 = et * RT_TILE, t0 = tt * RT_TILE;
+        const WT *wr = W + (size_t)min(e0 + frow, E - 1) * D + fcol;
+        const float *xr = x + (size_t)min(t0 + frow, T - 1) * D + fcol;
+        double acc[2][4][2];
+#pragma unroll
+        for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+            for (int ni = 0; ni < 4; ni++) { acc[mi][ni][0] = 0.0; acc[mi][ni][1] = 0.0; }
+        float wv[8], xv[8];
+        if (k0 < k1) { sw_load8(wr + k0, wv); sw_load8(xr + k0, xv); }
+        __syncthreads();                                       // the previous item's last stage has been read
+        for (int k = k0, st = 0; k < k1; k += 32, st++) {
+            double (*A)[RT_LD] = sm[st & 1][0], (*B)[RT_LD] = sm[st & 1][1];
+#pragma unroll
+            for (int i = 0; i < 8; i += 2) {
+                *reinterpret_cast<double2 *>(&A[frow][fcol + i]) = make_double2((double)wv[i], (double)wv[i + 1]);
+                *reinterpret_cast<double2 *>(&B[frow][fcol + i]) = make_double2((double)xv[i], (double)xv[i + 1]);
+            }
+            __syncthreads();
+            if (k + 32 < k1) { sw_load8(wr + k + 32, wv); sw_load8(xr + k + 32, xv); }   // in flight under the MMAs
+#pragma unroll
+            for (int kk = 0; kk < 8; kk++) {
+                double a[2], b[4];
+#pragma unroll
+                for (int mi = 0; mi < 2; mi++) a[mi] = A[m0 + mi * 8 + r][4 * kk + c];
+#pragma unroll
+                for (int ni = 0; ni < 4; ni++) b[ni] = B[n0 + ni * 8 + r][4 * kk + c];
+#pragma unroll
+                for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+                    for (int ni = 0; ni < 4; ni++) sw_dmma(acc[mi][ni], a[mi], b[ni]);
+            }
+            // the stage after next overwrites this buffer; every warp passes the barrier above (of the next stage) first
+        }
+        // C[row = expert r][col = token 2c, 2c+1] of every MMA tile
+#pragma unroll
+        for (int mi = 0; mi < 2; mi++) {
+            const int eo = e0 + m0 + mi * 8 + r;
+            if (eo >= E) continue;
+#pragma unroll
+            for (int ni = 0; ni < 4; ni++)
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const int t = t0 + n0 + ni * 8 + 2 * c + j;
+                    if (t < T) part[((size_t)ks * T + t) * E + eo] = acc[mi][ni][j];
+                }
+        }
+    }
+}
+
+// Token rows from which the tiled kernel is used
+#define SW_ROUTER_TILED_MIN_T 128
+
 // Number of column slices the DMMA router uses for (T, E, D); the top-k kernel sums this many partials.
 int sw_router_slices(int num_sms, int T, int D, int E) {
+    if (T >= SW_ROUTER_TILED_MIN_T) {
+        // two CTA items per SM; never finer than 256 columns.  KS * T stays below num_sms * 8192 / E + T, the same bound
+        // as for the streaming kernel below, which is what the partial-sum buffer is sized for.
+        const int tiles = ((E + RT_TILE - 1) / RT_TILE) * ((T + RT_TILE - 1) / RT_TILE);
+        const int want = (num_sms * 2 + tiles - 1) / tiles, maxs = (D + 255) / 256;
+        return want < 1 ? 1 : want > maxs ? maxs : want;
+    }
     const int nt = T <= 64 ? 1 : 4;
     const int etiles = (E + 7) / 8, passes = (T + 8 * nt - 1) / (8 * nt);
     int want = (num_sms * 32 + etiles * passes - 1) / (etiles * passes);
@@ -158,9 +242,23 @@ int sw_launch_router_dmma(const SwLaunchCfg &c, const float *x, const void *W, i
                           int T, int D, int E, int KS) {
     if (T <= 0) return 0;
     if (D % 32) return -1;
+    int slice = ((D + KS - 1) / KS + 31) & ~31;
+    if (T >= SW_ROUTER_TILED_MIN_T) {
+        static SwPerDevice attr;
+        if (attr.get(c.dev, [] {
+                if (cudaFuncSetAttribute(k_router_dmma_tiled<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM) != cudaSuccess ||
+                    cudaFuncSetAttribute(k_router_dmma_tiled<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
+                return 1; }) <= 0) return -1;
+        const long long items = (long long)((E + RT_TILE - 1) / RT_TILE) * ((T + RT_TILE - 1) / RT_TILE) * KS;
+        long long grid = (long long)c.num_sms * 2;
+        if (grid > items) grid = items;
+        if (w_dtype == 1) k_router_dmma_tiled<__nv_bfloat16><<<(unsigned)grid, 256, RT_SMEM, c.stream>>>(x, (const __nv_bfloat16 *)W, part, T, D, E, KS, slice);
+        else k_router_dmma_tiled<float><<<(unsigned)grid, 256, RT_SMEM, c.stream>>>(x, (const float *)W, part, T, D, E, KS, slice);
+        sw_count_launch();
+        return cudaGetLastError() == cudaSuccess ? 0 : -1;
+    }
     const int nt = T <= 64 ? 1 : 4;
     const int etiles = (E + 7) / 8, passes = (T + 8 * nt - 1) / (8 * nt);
-    int slice = ((D + KS - 1) / KS + 31) & ~31;
     long long items = (long long)etiles * passes * KS, need = (items + 3) / 4;
     long long grid = (long long)c.num_sms * 8;
     if (grid > need) grid = need;
@@ -480,9 +578,139 @@ k_dispatch(const int *__restrict__ sel, int npairs, int K, int E, int T,
     sw_dispatch_block<SW_DISPATCH_THREADS>(sm, sel, npairs, K, E, T, Gout, gexp, gbeg, gcnt, grow, rowof, status);
 }
 
+// ---------------------------------------------------------------------------
+// The same grouping for many pairs (prefill), by many CTAs in three launches.
+// A segment is DP_SEG consecutive pairs, walked by one warp; a CTA has eight.
+//   k_dpar_hist     per-segment histograms            hist[e][s]
+//   k_dpar_scan     a warp per expert: exclusive scan over the segments (the first slot, inside the expert's group, of
+//                   each segment's pairs) and the expert's total; the last CTA to finish (ticket) scans the totals
+//                   over the experts and writes the group arrays, exactly as the one-CTA version does
+//   k_dpar_scatter  per segment, in pair order, with __match_any ranks: slot = pos[e] + hist[e][s] + rank
+// Pairs of one expert therefore keep ascending flat index: the reference's order (c/laguna.c:709-723), bit for bit.
+// Scratch: [ticket, 31 unused][cnt E][pos E][hist E x NSP].
+// ---------------------------------------------------------------------------
+#define DP_SEG 256
+#define DP_WARPS 8
+#define DP_MIN_PAIRS 16384         // below this one CTA is as fast (and is fused into the top-k kernel below 4096)
+
+size_t sw_dispatch_scratch_ints(size_t P, size_t E) {
+    const size_t nb = (P + DP_SEG * DP_WARPS - 1) / (DP_SEG * DP_WARPS);
+    return 32 + 2 * E + E * nb * DP_WARPS;
+}
+
+__global__ void __launch_bounds__(DP_WARPS * 32)
+k_dpar_hist(const int *__restrict__ sel, int npairs, int E, int NSP, int *__restrict__ hist, int *__restrict__ status) {
+    extern __shared__ int dp_sm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int *wh = dp_sm + warp * E;
+    for (int e = lane; e < E; e += 32) wh[e] = 0;
+    __syncwarp();
+    const int s = blockIdx.x * DP_WARPS + warp;
+    const int s0 = min(s * DP_SEG, npairs), s1 = min(s0 + DP_SEG, npairs);
+    for (int i = s0 + lane; i < s1; i += 32) {
+        const int e = __ldcg(sel + i);
+        if (e == SW_NO_EXPERT) continue;
+        if (e < 0 || e >= E) { atomicOr(status, SW_ST_BAD_EXPERT); continue; }
+        atomicAdd(&wh[e], 1);
+    }
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) hist[(size_t)e * NSP + s] = wh[e];
+}
+
+__global__ void __launch_bounds__(256)
+k_dpar_scan(int E, int NSP, int *__restrict__ hist, int *__restrict__ cnt, int *__restrict__ pos, unsigned *__restrict__ ticket,
+            int *__restrict__ Gout, int *__restrict__ gexp, int *__restrict__ gbeg, int *__restrict__ gcnt) {
+    __shared__ int s_last, s_wsum[8], s_gsum[8];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int e = blockIdx.x * 8 + warp;
+    if (e < E) {
+        int carry = 0;
+        int *row = hist + (size_t)e * NSP;
+        for (int base = 0; base < NSP; base += 32) {
+            const int i = base + lane;
+            const int v = i < NSP ? row[i] : 0;
+            int inc = v;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) { const int a = __shfl_up_sync(SW_FULL_MASK, inc, off); if (lane >= off) inc += a; }
+            if (i < NSP) row[i] = carry + inc - v;
+            carry += __shfl_sync(SW_FULL_MASK, inc, 31);
+        }
+        if (lane == 0) cnt[e] = carry;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(ticket, 1u) == gridDim.x - 1) ? 1 : 0;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (tid == 0) *ticket = 0;
+    // exclusive scan over the experts of cnt (slots) and of cnt > 0 (group index): every thread owns a run of CH experts
+    const int CH = (E + 255) / 256;
+    const int e0 = min(E, tid * CH), e1 = min(E, e0 + CH);
+    int c = 0, nz = 0;
+    for (int x = e0; x < e1; x++) { const int v = __ldcg(cnt + x); c += v; nz += v > 0 ? 1 : 0; }
+    int sc = c, sg = nz;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int a = __shfl_up_sync(SW_FULL_MASK, sc, off), b = __shfl_up_sync(SW_FULL_MASK, sg, off);
+        if (lane >= off) { sc += a; sg += b; }
+    }
+    if (lane == 31) { s_wsum[warp] = sc; s_gsum[warp] = sg; }
+    __syncthreads();
+    int wbase = 0, gbase = 0;
+    for (int wv = 0; wv < warp; wv++) { wbase += s_wsum[wv]; gbase += s_gsum[wv]; }
+    int excl = wbase + sc - c, gidx = gbase + sg - nz;
+    for (int x = e0; x < e1; x++) {
+        const int ce = __ldcg(cnt + x);
+        pos[x] = excl;
+        if (ce > 0) { gexp[gidx] = x; gbeg[gidx] = excl; gcnt[gidx] = ce; gidx++; }
+        excl += ce;
+    }
+    if (tid == 255) { Gout[0] = gidx; Gout[1] = excl; }          // groups, and pairs that selected an expert
+}
+
+__global__ void __launch_bounds__(DP_WARPS * 32)
+k_dpar_scatter(const int *__restrict__ sel, int npairs, int K, int E, int T, int NSP, const int *__restrict__ hist,
+               const int *__restrict__ pos, int *__restrict__ grow, int *__restrict__ rowof, int *__restrict__ status) {
+    extern __shared__ int dp_sm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int *wh = dp_sm + warp * E;                                  // next slot of each expert for this segment
+    const int s = blockIdx.x * DP_WARPS + warp;
+    for (int e = lane; e < E; e += 32) wh[e] = pos[e] + hist[(size_t)e * NSP + s];
+    __syncwarp();
+    const int s0 = min(s * DP_SEG, npairs), s1 = min(s0 + DP_SEG, npairs);
+    for (int base = s0; base < s1; base += 32) {
+        const int i = base + lane;
+        const int e = i < s1 ? __ldcg(sel + i) : -1;
+        const bool ok = e >= 0 && e < E;
+        const unsigned peers = __match_any_sync(SW_FULL_MASK, ok ? e : -1 - lane);
+        const int first = ok ? wh[e] : 0;
+        __syncwarp();
+        if (ok) {
+            const int rank = __popc(peers & ((1u << lane) - 1));
+            const int slot = first + rank, row = i / K;
+            if (row >= T) atomicOr(status, SW_ST_BAD_ROW);
+            else { grow[slot] = row; rowof[i] = slot; }
+            if (rank == 0) wh[e] = first + __popc(peers);
+        }
+        __syncwarp();
+    }
+}
+
 int sw_launch_dispatch(const SwLaunchCfg &c, const SwRouting &r, int T, int K, int E) {
     if (T <= 0) return 0;
     if (E > SW_MAX_EXPERTS) return -1;
+    const long long npairs = (long long)T * K;
+    if (r.dpar && npairs >= DP_MIN_PAIRS && sw_dispatch_scratch_ints((size_t)npairs, (size_t)E) <= r.dpar_ints) {
+        const int NB = (int)((npairs + DP_SEG * DP_WARPS - 1) / (DP_SEG * DP_WARPS)), NSP = NB * DP_WARPS;
+        int *cnt = r.dpar + 32, *pos = cnt + E, *hist = pos + E;
+        const size_t smem = (size_t)DP_WARPS * E * sizeof(int);
+        k_dpar_hist<<<NB, DP_WARPS * 32, smem, c.stream>>>(r.sel, (int)npairs, E, NSP, hist, r.status);
+        k_dpar_scan<<<(E + 7) / 8, 256, 0, c.stream>>>(E, NSP, hist, cnt, pos, (unsigned *)r.dpar, r.G, r.gexp, r.gbeg, r.gcnt);
+        k_dpar_scatter<<<NB, DP_WARPS * 32, smem, c.stream>>>(r.sel, (int)npairs, K, E, T, NSP, hist, pos, r.grow, r.rowof, r.status);
+        sw_count_launch(); sw_count_launch(); sw_count_launch();
+        return cudaGetLastError() == cudaSuccess ? 0 : -1;
+    }
     size_t smem = (size_t)(SW_DISPATCH_THREADS / 32 + 2) * E * sizeof(int);
     static SwPerDevice attr_done;
     if (attr_done.get(c.dev, [] {

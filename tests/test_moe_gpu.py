@@ -684,7 +684,7 @@ def test_activation_scales_far_from_one(orc):
     where plain fp16 pairs would flush to zero or overflow."""
     from sabrewing_b200 import capi
     base = synth_case("c3", corr_bias_std=0.01, T=160, D=512, I=256, SI=128, E=16, K=4)
-    for scale in (1e-6, 1e-3, 1e3, 1e6):
+    for scale in (1e-6, 1e-4, 1e4, 1e6):
         case = synth_case("c3", corr_bias_std=0.01, T=160, D=512, I=256, SI=128, E=16, K=4)
         case.x[:] = base.x * np.float32(scale)
         case.x[7] *= np.float32(1e-3)                          # rows of one batch at different scales
