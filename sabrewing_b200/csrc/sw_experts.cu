@@ -326,7 +326,33 @@ int sw_launch_q8_rows(const SwLaunchCfg &c, const float *x, const int8_t *W, con
 // (the reference's multiply-add, contracted by its build), then optionally
 // *route_scale, + add rows, and store or accumulate.
 // ---------------------------------------------------------------------------
-template <int KB>          // ranks whose slot rows are in flight at once: top-k of 8, 10-12 and up to 16 take one round
+// NB ranks of one token, starting at flat pair index `base`: indices and weights first, then all slot rows (independent,
+// unconditional loads: a rank whose expert lives elsewhere reads row 0 and is not added), then the FMAs in rank order.
+template <int NB>
+__device__ __forceinline__ void sw_combine_round(float4 &acc, const float *__restrict__ slots, const int *__restrict__ rowof,
+                                                 const int *__restrict__ sel, const float *__restrict__ w, size_t base,
+                                                 int D, int i4, int expert_lo, int expert_cnt, float b2) {
+    float wa[NB]; int slot[NB];
+#pragma unroll
+    for (int j = 0; j < NB; j++) {
+        const int e = sel[base + j] - expert_lo;
+        const bool ok = e >= 0 && e < expert_cnt;
+        const int ro = rowof[base + j];
+        const float wj = w[base + j];
+        slot[j] = ok ? ro : -1; wa[j] = wj * b2;
+    }
+    float4 v[NB];
+#pragma unroll
+    for (int j = 0; j < NB; j++) v[j] = reinterpret_cast<const float4 *>(slots + (size_t)max(slot[j], 0) * D)[i4];
+#pragma unroll
+    for (int j = 0; j < NB; j++)
+        if (slot[j] >= 0) {
+            acc.x = fmaf(wa[j], v[j].x, acc.x); acc.y = fmaf(wa[j], v[j].y, acc.y);
+            acc.z = fmaf(wa[j], v[j].z, acc.z); acc.w = fmaf(wa[j], v[j].w, acc.w);
+        }
+}
+
+template <int KB>          // ranks whose slot rows are in flight at once: 8, or 16 at decode sizes (top-k up to 16 in one round)
 __global__ void __launch_bounds__(256)
 k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const int *__restrict__ sel,
           const float *__restrict__ w, const float *__restrict__ add, int add_slices, float *__restrict__ out,
@@ -341,29 +367,17 @@ k_combine(const float *__restrict__ slots, const int *__restrict__ rowof, const 
         // divided by its square: the weights carry it back (a power of two: every product and sum scales exactly).
         float b2 = 1.f;
         if (row_back) { const float b = row_back[t]; b2 = b * b; }
-        // KB ranks at a time: indices first, then all slot rows (independent loads), then the FMAs in rank order
-        for (int a0 = 0; a0 < K; a0 += KB) {
-            float wa[KB]; int slot[KB];
-#pragma unroll
-            for (int j = 0; j < KB; j++) {
-                const int a = a0 + j;
-                slot[j] = -1; wa[j] = 0.f;
-                if (a < K) {
-                    const int e = sel[t * K + a] - expert_lo;
-                    if (e >= 0 && e < expert_cnt) { slot[j] = rowof[t * K + a]; wa[j] = w[t * K + a] * b2; }
-                }
-            }
-            float4 v[KB];
-#pragma unroll
-            for (int j = 0; j < KB; j++)
-                if (slot[j] >= 0) v[j] = reinterpret_cast<const float4 *>(slots + (size_t)slot[j] * D)[i4];
-#pragma unroll
-            for (int j = 0; j < KB; j++)
-                if (slot[j] >= 0) {
-                    acc.x = fmaf(wa[j], v[j].x, acc.x); acc.y = fmaf(wa[j], v[j].y, acc.y);
-                    acc.z = fmaf(wa[j], v[j].z, acc.z); acc.w = fmaf(wa[j], v[j].w, acc.w);
-                }
+        const size_t base = (size_t)t * K;
+        int a0 = 0;
+        for (; a0 + KB <= K; a0 += KB) sw_combine_round<KB>(acc, slots, rowof, sel, w, base + a0, D, i4, expert_lo, expert_cnt, b2);
+#define SW_CR(N) case N: sw_combine_round<N>(acc, slots, rowof, sel, w, base + a0, D, i4, expert_lo, expert_cnt, b2); break;
+        switch (K - a0) {                        // the remaining ranks in one round of exactly that width
+            SW_CR(1) SW_CR(2) SW_CR(3) SW_CR(4) SW_CR(5) SW_CR(6) SW_CR(7)
+            default:
+                if (KB > 8) switch (K - a0) { SW_CR(8) SW_CR(9) SW_CR(10) SW_CR(11) SW_CR(12) SW_CR(13) SW_CR(14) SW_CR(15) default: break; }
+                break;
         }
+#undef SW_CR
         if (mode & 1) { acc.x *= route_scale; acc.y *= route_scale; acc.z *= route_scale; acc.w *= route_scale; }
         if (mode & 2) {
             float4 s = reinterpret_cast<const float4 *>(add)[idx];
@@ -389,11 +403,10 @@ int sw_launch_combine(const SwLaunchCfg &c, const float *slots, const int *rowof
     size_t n = (size_t)T * (D / 4);
     long long grid = (long long)((n + 255) / 256);
     if (grid > (long long)c.num_sms * 16) grid = (long long)c.num_sms * 16;
-    // wide rounds pay when the step is latency-bound (few rows); with many rows their registers cost more than the second round
-    if (K <= 8 || K > 16 || T > 64)
+    // one round for top-k up to 16 when the step is latency-bound (few rows); with many rows the registers of a wide
+    // round cost more than a second round does
+    if (T > 64)
         k_combine<8><<<(unsigned)grid, 256, 0, c.stream>>>(slots, rowof, sel, w, add, add_slices, out, T, K, D, route_scale, mode, expert_lo, expert_cnt, row_gate, row_back);
-    else if (K <= 12)
-        k_combine<12><<<(unsigned)grid, 256, 0, c.stream>>>(slots, rowof, sel, w, add, add_slices, out, T, K, D, route_scale, mode, expert_lo, expert_cnt, row_gate, row_back);
     else
         k_combine<16><<<(unsigned)grid, 256, 0, c.stream>>>(slots, rowof, sel, w, add, add_slices, out, T, K, D, route_scale, mode, expert_lo, expert_cnt, row_gate, row_back);
     sw_count_launch();
