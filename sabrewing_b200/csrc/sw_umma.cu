@@ -214,25 +214,40 @@ k_umma_gather(const float *__restrict__ x, const int *__restrict__ grow, const i
               const float *__restrict__ rexp, float *__restrict__ srex) {
     const int cpr = KD >> 3;
     P = min(P, *npairs);                         // packed rows the dispatch filled (pairs that selected no expert leave none)
-    const size_t n = (size_t)P * cpr;
     bool clamped = false;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
-        const int slot = (int)(idx / cpr), c8 = (int)(idx - (size_t)slot * cpr);
+    // a warp per packed row: the row's token and power of two are fetched once, then the lanes walk the row's 8-column
+    // chunks four at a time (eight independent 16-byte loads in flight per lane)
+    const int lane = threadIdx.x & 31;
+    for (int slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); slot < P; slot += gridDim.x * (blockDim.x >> 5)) {
         const int tokrow = grow[slot];
-        const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)tokrow * KD + c8 * 8);
-        const float4 a = src[0], b = src[1];
         float inv = 1.f;
         if (rexp) {
             const float rex = rexp[tokrow];
             inv = __frcp_rn(rex);                                  // a power of two: exact
-            if (c8 == 0) srex[slot] = rex;                         // the packed row's copy, for the epilogues
+            if (lane == 0) srex[slot] = rex;                       // the packed row's copy, for the epilogues
         }
-        const float v[8] = {a.x * inv, b.x * inv, a.y * inv, b.y * inv, a.z * inv, b.z * inv, a.w * inv, b.w * inv};
-        __half h[8], l[8];
+        const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)tokrow * KD);
+        uint4 *dh = reinterpret_cast<uint4 *>(hi) + (size_t)slot * cpr;
+        uint4 *dl = lo ? reinterpret_cast<uint4 *>(lo) + (size_t)slot * cpr : nullptr;
+        for (int c0 = lane; c0 < cpr; c0 += 128) {
+            float4 a[4], b[4];
 #pragma unroll
-        for (int i = 0; i < 8; i++) { clamped |= !(fabsf(v[i]) <= 65504.f); um_split(v[i], h[i], l[i]); }
-        reinterpret_cast<uint4 *>(hi)[idx] = *reinterpret_cast<uint4 *>(h);
-        if (lo) reinterpret_cast<uint4 *>(lo)[idx] = *reinterpret_cast<uint4 *>(l);
+            for (int u = 0; u < 4; u++) {
+                const int c8 = c0 + 32 * u;
+                if (c8 < cpr) { a[u] = src[2 * c8]; b[u] = src[2 * c8 + 1]; }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int c8 = c0 + 32 * u;
+                if (c8 >= cpr) continue;
+                const float v[8] = {a[u].x * inv, b[u].x * inv, a[u].y * inv, b[u].y * inv, a[u].z * inv, b[u].z * inv, a[u].w * inv, b[u].w * inv};
+                __half h[8], l[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) { clamped |= !(fabsf(v[i]) <= 65504.f); um_split(v[i], h[i], l[i]); }
+                dh[c8] = *reinterpret_cast<uint4 *>(h);
+                if (dl) dl[c8] = *reinterpret_cast<uint4 *>(l);
+            }
+        }
     }
     if (clamped && status) atomicOr(status, SW_ST_RANGE);
 }
@@ -493,7 +508,9 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
         // lane 32 * (warp % 4) + lane): it reads the row's 64 raw bytes of the step from the slot, expands them to 128 exact
         // fp16 integers (nibble - 8) and stores them to the 64 columns of A tile (2 * step + t) % 4 in four pieces.
         // (Sixteen warps with half a row each were slower: 1.02 against 0.96 ms on the 4096-token prefill.  Eight warps
-        // stream 146 bytes per clock into tensor memory next to the MMAs, sixteen 186.)
+        // stream 146 bytes per clock into tensor memory next to the MMAs, sixteen 186.  A third ring position for chunks
+        // of at most 64 rows -- in the accumulators' unused halves, or with the accumulators packed into 128 columns --
+        // was slower too, three times out of three: 2.51 against 2.33 ms on the 1024-token very large layer.)
         const int tsel = warp >> 2, q = warp & 3;
         const int trow = q * 32 + lane;
         const unsigned lane_base = (unsigned)(q * 32) << 16;
@@ -609,8 +626,7 @@ int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow,
                           const float *rexp, float *srex) {
     if (P <= 0) return 0;
     if ((rexp == nullptr) != (srex == nullptr)) return -1;
-    size_t n = (size_t)P * (KD / 8);
-    long long grid = (long long)((n + 255) / 256);
+    long long grid = ((long long)P + 7) / 8;                            // a warp per packed row, eight warps per CTA
     if (grid > (long long)c.num_sms * 16) grid = (long long)c.num_sms * 16;
     k_umma_gather<<<(unsigned)grid, 256, 0, c.stream>>>(x, grow, npairs, P, KD, (__half *)hi, (__half *)lo, status, rexp, srex);
     sw_count_launch();
