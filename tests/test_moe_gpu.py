@@ -707,3 +707,29 @@ def test_activation_scales_far_from_one(orc):
                 nr = np.linalg.norm(ref[r])
                 assert np.linalg.norm(got[r] - ref[r]) <= OUT_TOL * max(nr, 1e-30) + 0.0, (scale, path, r)
             blk.close()
+
+
+def test_shapes_around_the_kernels_tile_sizes(orc):
+    """Shapes chosen to land on the edges of today's kernels: top-k of every width the combine step treats differently
+    (1 ... 16: full rounds of 8 or 16 plus a last round of exactly the remaining width), token counts on both sides of the
+    tiled router (128 rows, tiles of 64 x 64 with ragged last tiles in both directions), expert counts that are not a
+    multiple of 64 or 32, pair counts on the many-CTA dispatch, the softmax and the sigmoid gate.  Bit-exact routing and
+    dispatch, outputs inside the bar."""
+    shapes = [
+        # base, T, E, K, D, I, SI
+        ("c2", 3, 24, 1, 256, 128, 128),
+        ("c1", 5, 40, 2, 256, 128, 0),
+        ("c2", 70, 96, 3, 512, 128, 128),
+        ("c1", 130, 72, 5, 256, 256, 0),
+        ("c2", 129, 100, 7, 512, 128, 128),
+        ("c1", 200, 130, 9, 256, 128, 0),
+        ("c2", 64, 48, 12, 256, 128, 128),
+        ("c1", 33, 64, 16, 512, 128, 0),
+        ("c2", 257, 200, 16, 256, 128, 128),
+        # more than 16384 pairs: the many-CTA dispatch, with a ragged last segment and expert counts off every power of two
+        ("c1", 2100, 100, 8, 256, 128, 0),
+        ("c2", 1701, 130, 10, 256, 128, 128),
+    ]
+    for base, T, E, K, D, I, SI in shapes:
+        case = synth_case(base, corr_bias_std=0.01 if base == "c2" else 0.0, T=T, E=E, K=K, D=D, I=I, SI=SI)
+        run_case(case, orc)
