@@ -388,6 +388,47 @@ template <int NJ>
 __device__ __forceinline__ void sw_topk_warp(const float *s_sb, const float *s_sc, int E, int K, int norm_topk,
                                              int *sel_t, float *w_t, bool pool = false, float pool_scale = 1.f, float *gate_t = nullptr) {
     const int lane = threadIdx.x & 31;
+    float wsel = 0.f;                            // lane a keeps the weight of rank a
+    if (NJ == 8) {
+        // Up to 256 experts: the rounds visit the experts in ONE total order -- value descending, id ascending, every value
+        // that never compares greater (NaN or <= -1e30f) in a lowest class -- so each lane sorts its eight experts by that
+        // order once (19 compare-exchanges in registers) and a round only looks at the lanes' heads: two warp reductions
+        // and a shift in the winning lane, instead of an eight-way scan and an eight-way update per round.
+        // An expert is the pair (kh, kl) = (order-preserving key of the value or 0, ~id); a larger pair is picked earlier.
+        uint32_t kh[8], kl[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int e = lane + 32 * j;
+            kh[j] = 0u; kl[j] = 0u;                                         // past the end: below every expert
+            if (e < E) {
+                const float v = s_sb[e] + 0.0f;                             // -0 -> +0
+                const uint32_t bits = __float_as_uint(v);
+                if (v > -1e30f) kh[j] = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+                kl[j] = ~(uint32_t)e;
+            }
+        }
+#define SW_CE(i, j) { const bool sw_ = kh[j] > kh[i] || (kh[j] == kh[i] && kl[j] > kl[i]);                                  \
+                      const uint32_t h_ = sw_ ? kh[j] : kh[i], l_ = sw_ ? kl[j] : kl[i];                                       \
+                      kh[j] = sw_ ? kh[i] : kh[j]; kl[j] = sw_ ? kl[i] : kl[j]; kh[i] = h_; kl[i] = l_; }
+        SW_CE(0, 1) SW_CE(2, 3) SW_CE(4, 5) SW_CE(6, 7)
+        SW_CE(0, 2) SW_CE(1, 3) SW_CE(4, 6) SW_CE(5, 7)
+        SW_CE(1, 2) SW_CE(5, 6)
+        SW_CE(0, 4) SW_CE(1, 5) SW_CE(2, 6) SW_CE(3, 7)
+        SW_CE(2, 4) SW_CE(3, 5)
+        SW_CE(1, 2) SW_CE(3, 4) SW_CE(5, 6)
+#undef SW_CE
+        for (int a = 0; a < K; a++) {
+            const uint32_t kmax = __reduce_max_sync(SW_FULL_MASK, kh[0]);
+            const uint32_t best = ~__reduce_max_sync(SW_FULL_MASK, kh[0] == kmax ? kl[0] : 0u);   // largest ~id = lowest id
+            if ((int)(best & 31) == lane) {
+#pragma unroll
+                for (int j = 0; j < 7; j++) { kh[j] = kh[j + 1]; kl[j] = kl[j + 1]; }
+                kh[7] = 0u; kl[7] = 0u;
+            }
+            if (lane == a) wsel = s_sc[best];
+            if (lane == 0) sel_t[a] = (int)best;
+        }
+    } else {
     float v[NJ];
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
@@ -395,7 +436,6 @@ __device__ __forceinline__ void sw_topk_warp(const float *s_sb, const float *s_s
         v[j] = e < E ? s_sb[e] + 0.0f : __int_as_float(0x7fc00000);     // -0 -> +0; past the end: NaN, never greater
     }
     uint32_t used = 0;                           // bit j: this lane's expert lane+32j is taken
-    float wsel = 0.f;                            // lane a keeps the weight of rank a
     for (int a = 0; a < K; a++) {
         float bv = -1e30f; int bj = -1;
 #pragma unroll
@@ -419,6 +459,7 @@ __device__ __forceinline__ void sw_topk_warp(const float *s_sb, const float *s_s
         }
         if (lane == a) wsel = s_sc[best];
         if (lane == 0) sel_t[a] = (int)best;
+    }
     }
     if (pool) {
         float sm = 0.f;
