@@ -327,25 +327,19 @@ __device__ __forceinline__ void sw_dispatch_block(int *sm, const int *sel, int n
     }
     if (lane == 31) { s_wsum[warp] = sc; s_gsum[warp] = sg; }
     __syncthreads();
-    if (warp == 0) {
-        int a = lane < NW ? s_wsum[lane] : 0, b = lane < NW ? s_gsum[lane] : 0;
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-            int ua = __shfl_up_sync(SW_FULL_MASK, a, off), ub = __shfl_up_sync(SW_FULL_MASK, b, off);
-            if (lane >= off) { a += ua; b += ub; }
-        }
-        s_wsum[lane] = a; s_gsum[lane] = b;      // inclusive over warps
-    }
-    __syncthreads();
     {
-        int excl = (warp ? s_wsum[warp - 1] : 0) + sc - c, gidx = (warp ? s_gsum[warp - 1] : 0) + sg - nz;
+        // every thread adds up the totals of the warps before its own (at most NW - 1 shared-memory reads): one barrier
+        // and one single-warp phase less than a second-level scan
+        int wbase = 0, gbase = 0;
+        for (int wv = 0; wv < warp; wv++) { wbase += s_wsum[wv]; gbase += s_gsum[wv]; }
+        int excl = wbase + sc - c, gidx = gbase + sg - nz;
         for (int e = e0; e < e1; e++) {
             const int ce = cnt[e];
             pos[e] = excl;
             if (ce > 0) { gexp[gidx] = e; gbeg[gidx] = excl; gcnt[gidx] = ce; gidx++; }
             excl += ce;
         }
-        if (tid == 0) { Gout[0] = s_gsum[31]; Gout[1] = s_wsum[31]; }   // groups, and pairs that selected an expert
+        if (tid == NTH - 1) { Gout[0] = gidx; Gout[1] = excl; }   // groups, and pairs that selected an expert
     }
     __syncthreads();
 
