@@ -20,8 +20,9 @@
 //   warps 13,14  MMA issuers, one per tile of the pair: eight tcgen05.mma kind::f16 per
 //                step with the A operand in tensor memory and B through its
 //                shared-memory descriptor (with two terms a second MMA against the lo
-//                tile into the same accumulator columns); one tcgen05.commit per step
-//                returns the slot and the step's A tiles.  The WHOLE warp runs the loop
+//                tile into the same accumulator columns); two tcgen05.commit per step:
+//                one returns the A tile to its tile's dequantising warps, one (counted
+//                from both issuers) the slot to the TMA warp.  The WHOLE warp runs the loop
 //                with warp-uniform values and an elected lane issues (elect.sync), so
 //                that the descriptors are computed in uniform registers
 //   warps 8-11   epilogue: tcgen05.ld the two accumulators of the item, apply the per-row
@@ -105,12 +106,8 @@ __device__ __forceinline__ uint64_t um_desc(unsigned saddr) {
 // warp-uniform lets the descriptors live in uniform registers, which is where the instruction takes them from; computed
 // per thread (inside an `if (lane == 0)`) every operand of every MMA is first moved across, and the moves, not the tensor
 // pipe, set the issue rate (measured: 190 against 64 clocks per M = 128, N = 128, K = 16 MMA).
-// A operand in tensor memory (128 lanes x 8 columns of two fp16 each per K = 16), B through its shared-memory descriptor:
-__device__ __forceinline__ void um_mma_ta_elect(unsigned d_tmem, unsigned a_tmem, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
-    asm volatile("{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-                 :: "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// the same with the election done once by the caller (um_elect): `leader` is 1 in the elected lane, 0 elsewhere
+// A operand in tensor memory (128 lanes x 8 columns of two fp16 each per K = 16), B through its shared-memory descriptor;
+// the election is done once by the caller (um_elect): `leader` is 1 in the elected lane, 0 elsewhere
 __device__ __forceinline__ unsigned um_elect() {
     unsigned l;
     asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\tselp.u32 %0, 1, 0, e;\n\t}" : "=r"(l));
@@ -123,7 +120,7 @@ __device__ __forceinline__ void um_mma_ta_lead(unsigned leader, unsigned d_tmem,
 __device__ __forceinline__ void um_commit_lead(unsigned leader, unsigned bar) {
     asm volatile("{\n\t.reg .pred e;\n\tsetp.ne.b32 e, %1, 0;\n\t@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" :: "r"(bar), "r"(leader) : "memory");
 }
-// both operands through shared-memory descriptors
+// both operands through shared-memory descriptors, election per instruction
 __device__ __forceinline__ void um_mma_elect(unsigned d_tmem, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
     asm volatile("{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
