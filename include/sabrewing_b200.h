@@ -279,7 +279,7 @@ int  sw_moe_get_routing(SwMoeCtx *ctx, int *sel, float *w, float *scores, int *G
  * 1e6 times the usual size, tests/test_moe_gpu.py), so in practice the bit means an
  * infinity or a NaN in the input. */
 int  sw_moe_status(SwMoeCtx *ctx);
-/* Context options.  SW_OPT_UMMA_TERMS: how the tcgen05 grouped GEMM (groups averaging >= 16
+/* Context options.  SW_OPT_UMMA_TERMS: how the tcgen05 grouped GEMM (groups averaging >= 8
  * rows: prefill, large batches) feeds f32 activations to the fp16 tensor cores.
  * 1 (default) = fp16(x) alone: each activation, and each SiLU*up value entering the down
  * product, is rounded to 11 significant bits; measured relative L2 of the block output

@@ -31,7 +31,7 @@ const SwTuning &sw_tuning() {
         v.force_simt = (f && *f && *f != '0') ? 1 : 0;
         if (v.force_simt) v.expert_pref = 0;
         v.row_scale = sw_env_int("SW_ROW_SCALE", 1);
-        v.umma_min_rows = sw_env_int("SW_UMMA_MIN_ROWS", 16);    // mean rows per group from which the tcgen05 kernels win (measured)
+        v.umma_min_rows = sw_env_int("SW_UMMA_MIN_ROWS", 8);     // mean rows per group from which the tcgen05 kernels win (measured)
         v.tma_mt = sw_env_int("SW_TMA_MT", 0);
         if (v.tma_mt != 1 && v.tma_mt != 2) v.tma_mt = 0;
         v.tma_p = sw_env_int("SW_TMA_P", 0);
@@ -211,7 +211,7 @@ extern "C" int sw_moe_ctx_create(SwMoeCtx **out, int dev, int max_tokens, int ma
         sw_sums_bytes(T, P, I),  // sums
         T * D * 4,            // spk
         P * D * 4,            // um.xg: gathered fp16 hi + lo token rows
-        (P / 128 + E + 64) * 8 + 256,   // um.chunks + nchunks
+        (P / 32 + E + 64) * 8 + 256,    // um.chunks + nchunks (chunks of 32 rows at least)
         ((size_t)((D + 127) / 128) * (T < 128 ? T : 128) + ((size_t)c->num_sms * 32 * 256 + E - 1) / E + T + 64) * (E + 1) * 8   // rpart
     };
     size_t total = 0; for (size_t s : sizes) total += sw_align(s);
@@ -327,7 +327,7 @@ static void sw_resident(const SwMoeDesc *d, const SwMoeLayer *L, int *lo, int *c
 // Expert path: 2 = TMA-staged tensor-core kernels (default when the driver exports the
 // tensor-map encoder), 1 = cp.async tensor-core kernels, 0 = CUDA-core f32 kernels.
 // SW_EXPERT_PATH=tma|mma|simt|umma overrides.
-// 3 = tcgen05/TMEM grouped GEMM, chosen when groups average SW_UMMA_MIN_ROWS (16) rows or more.
+// 3 = tcgen05/TMEM grouped GEMM, chosen when groups average SW_UMMA_MIN_ROWS (8) rows or more.
 static int sw_expert_path(int D, int I, int rows, int groups) {
     const SwTuning &t = sw_tuning();
     const int pref = t.expert_pref;
@@ -366,18 +366,22 @@ static int sw_run_experts(const SwLaunchCfg &cfg, SwQ4Args a, const void *gu_q, 
     if (path == 3) {
         // tcgen05 path: gather + split the token rows in packed-slot order, build the chunk list, two grouped GEMMs
         const long long nexp = a.expert_cnt > 4096 ? 4096 : a.expert_cnt;
-        const int P = a.max_rows, max_chunks = P / 128 + a.max_groups;
+        // groups averaging at most 12 rows: chunks of 32 rows and a deeper ring of smaller slots.  Measured: the Laguna-shaped
+        // layer at 256 tokens (10 rows per group) 0.658 ms this way, 0.708 with the large-group geometry, 0.695 on the
+        // streaming kernels; the very large layer at 1024 tokens (16 rows per group) 4.33 ms this way, 4.05 with the large one.
+        const bool small = (long long)a.max_rows <= 12LL * a.max_groups;
+        const int P = a.max_rows, max_chunks = P / sw_umma_chunk_rows(small) + a.max_groups;
         __half *xh = (__half *)um->xg, *xl = xh + (size_t)P * D;
         __half *gh = (__half *)glu, *gl = gh + (size_t)P * I;
         const SwSums sl = sw_sums_layout(sums, rows_x, a.max_rows);
         if (sl.rexp && sw_launch_row_exp(cfg, x, rows_x, D, sl.rexp)) return -1;
         if (sw_launch_umma_gather(cfg, x, a.grow, a.G + 1, P, D, xh, umma_terms == 2 ? xl : nullptr, status, sl.rexp, sl.srex)) return -1;
-        if (sw_launch_umma_chunks(cfg, a, um->nchunks, um->chunks)) return -1;
+        if (sw_launch_umma_chunks(cfg, a, um->nchunks, um->chunks, small)) return -1;
         a.q = (const uint8_t *)gu_q; a.s = gu_s; a.KD = D; a.OUT = I;
-        if (sw_launch_q4_umma(cfg, a, xh, xl, gh, gl, um->nchunks, um->chunks, max_chunks, status, nexp * 2 * I, true, umma_terms, sl.srex)) return -1;
+        if (sw_launch_q4_umma(cfg, a, xh, xl, gh, gl, um->nchunks, um->chunks, max_chunks, status, nexp * 2 * I, true, umma_terms, sl.srex, small)) return -1;
         if (mark) mark(mark_ctx, 0);
         a.q = (const uint8_t *)dn_q; a.s = dn_s; a.KD = I; a.OUT = D;
-        if (sw_launch_q4_umma(cfg, a, gh, gl, slots, nullptr, um->nchunks, um->chunks, max_chunks, status, nexp * D, false, umma_terms, nullptr)) return -1;
+        if (sw_launch_q4_umma(cfg, a, gh, gl, slots, nullptr, um->nchunks, um->chunks, max_chunks, status, nexp * D, false, umma_terms, nullptr, small)) return -1;
         if (!row_back) return -1;                                      // every caller of this path has a combine step
         *row_back = sl.rexp;
         if (mark) mark(mark_ctx, 1);

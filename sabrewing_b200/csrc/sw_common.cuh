@@ -140,10 +140,11 @@ bool sw_umma_available();
 int sw_launch_row_exp(const SwLaunchCfg &c, const float *x, int rows, int KD, float *rexp);
 int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow, const int *npairs, int P, int KD, void *hi, void *lo, int *status,
                           const float *rexp, float *srex);
-int sw_launch_umma_chunks(const SwLaunchCfg &c, const SwQ4Args &a, int *nchunks, void *chunks);
+int sw_umma_chunk_rows(bool small);   // rows per chunk: 128, or 32 for launches of small groups (deeper ring of smaller slots)
+int sw_launch_umma_chunks(const SwLaunchCfg &c, const SwQ4Args &a, int *nchunks, void *chunks, bool small);
 int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_hi, const void *act_lo, void *Y0, void *Y1,
                       const int *nchunks, const void *chunks, int max_chunks, int *status, long long wrows_total, bool gateup, int terms,
-                      const float *srex);
+                      const float *srex, bool small);
 int sw_launch_pack_bf16_planar(const SwLaunchCfg &c, const float *x, void *hi, void *lo, int rows, int KD);
 int sw_launch_bf16_umma(const SwLaunchCfg &c, const void *W0, const void *W1, const void *act_hi, const void *act_lo,
                         void *Y0, void *Y1, int T, int KD, int O, int *status, bool gateup);

@@ -61,7 +61,7 @@
 // bandwidth an SM has (128 B/cycle), and the dequantised tiles crossed it a second time on their way in.
 #define UM_STAGE_BYTES(terms) (2 * UM_RAW_A + 2 * (terms) * UM_BT)
 #define UM_STAGES_FOR(terms) ((terms) == 1 ? 4 : 2)
-#define UM_MAX_STAGES 4
+#define UM_MAX_STAGES 8
 #define UM_RING_BYTES (4 * UM_STAGE_BYTES(1))        // 192 KB: four slots of 48 KB, or two of 80 KB
 // Tensor memory (512 columns): the two accumulators of an item in columns [0, 256) (one buffer), and a ring of four
 // dequantised A tiles -- two steps of a tile pair, 64 columns each (128 rows x 128 fp16) -- in columns [256, 512).
@@ -249,14 +249,14 @@ k_umma_gather(const float *__restrict__ x, const int *__restrict__ grow, const i
     if (clamped && status) atomicOr(status, SW_ST_RANGE);
 }
 
-// work list: one entry per (group, chunk of <=128 rows): {group index, first row of the chunk inside the group}
+// work list: one entry per (group, chunk of <= cap rows): {group index, first row of the chunk inside the group}
 __global__ void __launch_bounds__(1024)
 k_umma_chunks(const int *__restrict__ Gp, const int *__restrict__ gexp, const int *__restrict__ gcnt,
-              int expert_lo, int expert_cnt, int *__restrict__ nchunks, int2 *__restrict__ chunks) {
+              int expert_lo, int expert_cnt, int *__restrict__ nchunks, int2 *__restrict__ chunks, int cap) {
     __shared__ int s_scan[1024];
     const int G = *Gp, tid = threadIdx.x;
     int c = 0;
-    if (tid < G) { const int e = gexp[tid] - expert_lo; if (e >= 0 && e < expert_cnt) c = (gcnt[tid] + 127) >> 7; }
+    if (tid < G) { const int e = gexp[tid] - expert_lo; if (e >= 0 && e < expert_cnt) c = (gcnt[tid] + cap - 1) / cap; }
     s_scan[tid] = c;
     __syncthreads();
     for (int off = 1; off < 1024; off <<= 1) {
@@ -266,7 +266,7 @@ k_umma_chunks(const int *__restrict__ Gp, const int *__restrict__ gexp, const in
         __syncthreads();
     }
     const int base = s_scan[tid] - c;
-    for (int i = 0; i < c; i++) chunks[base + i] = make_int2(tid, i * 128);
+    for (int i = 0; i < c; i++) chunks[base + i] = make_int2(tid, i * cap);
     if (tid == 1023) *nchunks = s_scan[1023];
 }
 
@@ -279,6 +279,11 @@ struct UmArgs {
     int KD, OUT, expert_lo;
     int terms;                     // fp16 terms per activation: 1 = hi only, 2 = hi + lo
     const float *srex;             // per packed row: the power of two its token row was divided by (null = 1)
+    // Ring geometry.  Large groups: chunks of up to 128 rows, 4 slots of 48 KB (2 of 80 KB with two terms).  Small groups
+    // (a launch whose groups average at most 32 rows): chunks of up to 32 rows, so that the activation tiles are 8 KB and
+    // the ring has 8 slots of 24 KB (6 of 32 KB) -- the weights of such a launch come cold from HBM, and the bytes in
+    // flight per SM, not the arithmetic, set its speed.
+    int chunk_rows, stages, stage_bytes;
 };
 
 template <bool GATEUP>
@@ -299,7 +304,8 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
     __shared__ __align__(16) float s_srex[2][2][128];
     __shared__ unsigned long long b_srex[2];
     unsigned char *smem = (unsigned char *)(((uintptr_t)um_dyn + 1023) & ~(uintptr_t)1023);
-    const unsigned STG = UM_STAGES_FOR(a.terms), SBYTES = UM_STAGE_BYTES(a.terms);   // ring depth and slot size
+    const unsigned STG = a.stages, SBYTES = a.stage_bytes;               // ring depth and slot size
+    const int CR = a.chunk_rows;                                         // rows per chunk at most
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KD = a.KD, OUT = a.OUT;
     const int nrows_w = GATEUP ? 2 * OUT : OUT;
@@ -347,7 +353,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
     auto epilogue_share = [&](int item, unsigned nitem, int part, bool &clamped) -> bool {
         const int q = warp & 3, trow = q * 32 + lane;                   // lane quarter of this warp, tile row of this thread
         int gi, c0, pr; decode(item, gi, c0, pr);
-        const int e = a.gexp[gi] - a.expert_lo, n = min(128, a.gcnt[gi] - c0), row0 = a.gbeg[gi] + c0;
+        const int e = a.gexp[gi] - a.expert_lo, n = min(CR, a.gcnt[gi] - c0), row0 = a.gbeg[gi] + c0;
         const float *ws = a.Ws + (size_t)e * nrows_w;
         if (!um_bar_wait(um_s32(&b_acc_full[0]), nitem & 1, abortp) ||
             !um_bar_wait(um_s32(&b_acc_full[1]), nitem & 1, abortp)) {
@@ -428,7 +434,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
             unsigned kk = 0;
             for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x) {
                 int gi, c0, pr; decode(item, gi, c0, pr);
-                const int e = a.gexp[gi] - a.expert_lo, n = min(128, a.gcnt[gi] - c0), row0 = a.gbeg[gi] + c0;
+                const int e = a.gexp[gi] - a.expert_lo, n = min(CR, a.gcnt[gi] - c0), row0 = a.gbeg[gi] + c0;
                 const int R = tile_rows(n);
                 const CUtensorMap *th = R == 16 ? &tmH16 : R == 32 ? &tmH32 : R == 64 ? &tmH64 : &tmH128;
                 const CUtensorMap *tl = R == 16 ? &tmL16 : R == 32 ? &tmL32 : R == 64 ? &tmL64 : &tmL128;
@@ -465,7 +471,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
             unsigned ks = 0, nitem = 0;                                  // step and item counters
             for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, nitem++) {
                 int gi, c0, pr; decode(item, gi, c0, pr);
-                const int n = __shfl_sync(0xffffffffu, min(128, a.gcnt[gi] - c0), 0);
+                const int n = __shfl_sync(0xffffffffu, min(CR, a.gcnt[gi] - c0), 0);
                 const int R = tile_rows(n);
                 const unsigned idesc = (1u << 4) | ((unsigned)(R >> 3) << 17) | ((128u >> 4) << 24);   // f32 accum, f16 x f16, K-major
                 const unsigned d_tmem = tmem + (unsigned)t * 128;
@@ -556,7 +562,7 @@ k_q4_umma(const __grid_constant__ CUtensorMap tmW,
         for (int item = blockIdx.x; item < items && !*abortp; item += gridDim.x, nitem++) {
             if (GATEUP) {   // this item's per-row powers of two -> shared memory (128 entries, ones past the chunk's end)
                 int gi, c0, pr; decode(item, gi, c0, pr);
-                const int n = min(128, a.gcnt[gi] - c0), row0 = a.gbeg[gi] + c0, i = (warp - UM_DQ_WARPS) * 32 + lane;
+                const int n = min(CR, a.gcnt[gi] - c0), row0 = a.gbeg[gi] + c0, i = (warp - UM_DQ_WARPS) * 32 + lane;
                 const float r = (a.srex && i < n) ? a.srex[row0 + i] : 1.f;
                 s_srex[nitem & 1][0][i] = r;
                 s_srex[nitem & 1][1][i] = __frcp_rn(r);
@@ -630,8 +636,10 @@ int sw_launch_umma_gather(const SwLaunchCfg &c, const float *x, const int *grow,
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
-int sw_launch_umma_chunks(const SwLaunchCfg &c, const SwQ4Args &a, int *nchunks, void *chunks) {
-    k_umma_chunks<<<1, 1024, 0, c.stream>>>(a.G, a.gexp, a.gcnt, a.expert_lo, a.expert_cnt, nchunks, (int2 *)chunks);
+int sw_umma_chunk_rows(bool small) { return small ? 32 : 128; }
+
+int sw_launch_umma_chunks(const SwLaunchCfg &c, const SwQ4Args &a, int *nchunks, void *chunks, bool small) {
+    k_umma_chunks<<<1, 1024, 0, c.stream>>>(a.G, a.gexp, a.gcnt, a.expert_lo, a.expert_cnt, nchunks, (int2 *)chunks, sw_umma_chunk_rows(small));
     sw_count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
@@ -640,7 +648,7 @@ int sw_launch_umma_chunks(const SwLaunchCfg &c, const SwQ4Args &a, int *nchunks,
 // gate/up: Y0/Y1 = fp16 hi/lo [max_rows, OUT]; down: Y0 = f32 [max_rows, OUT].
 int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_hi, const void *act_lo, void *Y0, void *Y1,
                       const int *nchunks, const void *chunks, int max_chunks, int *status, long long wrows_total, bool gateup, int terms,
-                      const float *srex) {
+                      const float *srex, bool small) {
     if (a.max_rows <= 0) return 0;
     if (terms != 1 && terms != 2) return -1;
     if (terms == 1) act_lo = act_hi;                                    // never read; keeps the tensor maps valid
@@ -664,6 +672,9 @@ int sw_launch_q4_umma(const SwLaunchCfg &c, const SwQ4Args &a, const void *act_h
     UmArgs ka;
     ka.Ws = a.s; ka.Y0 = Y0; ka.Y1 = Y1; ka.gexp = a.gexp; ka.gbeg = a.gbeg; ka.gcnt = a.gcnt; ka.nchunks = nchunks;
     ka.chunks = (const int2 *)chunks; ka.status = status; ka.KD = a.KD; ka.OUT = a.OUT; ka.expert_lo = a.expert_lo; ka.terms = terms; ka.srex = srex;
+    ka.chunk_rows = sw_umma_chunk_rows(small);
+    if (small) { ka.stage_bytes = 2 * UM_RAW_A + 2 * terms * (32 * 128); ka.stages = UM_RING_BYTES / ka.stage_bytes; if (ka.stages > UM_MAX_STAGES) ka.stages = UM_MAX_STAGES; }
+    else { ka.stage_bytes = UM_STAGE_BYTES(terms); ka.stages = UM_STAGES_FOR(terms); }
     const int pairs = a.OUT / (gateup ? 128 : 256);
     long long items = (long long)max_chunks * pairs;
     long long grid = c.num_sms;                        // one CTA per SM (shared memory and tensor memory are sized for that)

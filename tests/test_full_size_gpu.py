@@ -28,7 +28,8 @@ CASES = [
     ("c1", 32, 0, 2, 2),       # OLMoE-shaped, softmax, no shared expert
     ("c2", 1, 0, 2, 2),        # Laguna-shaped decode batch 1
     ("c2", 32, 0, 2, 2),       # ... batch 32 (the headline)
-    ("c2", 256, 0, 2, 2),      # ... batch 256
+    ("c2", 256, 0, 3, 2),      # ... batch 256: 10 rows per expert, tcgen05 path in its small-group geometry (32-row chunks)
+    ("c2", 256, 0, 3, 1),
     ("c4", 256, 0, 2, 2),      # wide layer, 384 experts, decode batch 256
     ("c3", 4096, 64, 3, 2),    # prefill, Zipf-skewed routing: tcgen05 path, activations as two fp16 terms
     ("c3", 4096, 64, 3, 1),    # ... as one fp16 term (half the tensor work): same ids, output error reported

@@ -89,7 +89,7 @@ def test_scaled_configs(orc, base, kw, T):
     ("c1", dict(D=256, I=128, E=8, K=2), 700),                # softmax, no shared, 175 rows per expert
 ])
 def test_large_groups_take_the_tensor_memory_path(orc, base, kw, T):
-    """Groups averaging >= 16 rows (with I % 128 == 0 and D % 256 == 0) run the tcgen05/TMEM grouped GEMM; same parity bars."""
+    """Groups averaging >= 8 rows (with I % 128 == 0 and D % 256 == 0) run the tcgen05/TMEM grouped GEMM; same parity bars."""
     case = synth_case(base, corr_bias_std=0.01, T=T, **kw)
     assert T * case.cfg.K >= 16 * case.cfg.E and case.cfg.I % 128 == 0 and case.cfg.D % 256 == 0
     run_case(case, orc, path=3)
