@@ -343,6 +343,11 @@ static int sw_expert_path(int D, int I, int rows, int groups) {
 // Every family reads the blobs 16 bytes at a time: alignment is checked at the entry points, not here.
 static int sw_resolve_path(const SwQ4Args &a, int D, int I, const SwUmmaScratch *um, int forced = -1) {
     int path = a.gs > 0 ? 0 : sw_expert_path(D, I, a.max_rows, a.max_groups);   // group scales: CUDA-core kernels
+    // Between 8 and 16 rows per group the tcgen05 kernels win only by what they save on a whole layer's weights (measured
+    // with every expert resident); a shard of the experts does a fraction of that work under the same three extra
+    // launches, so an expert-parallel rank stays on the streaming kernels there, as it was measured.
+    if (path == 3 && forced < 0 && sw_tuning().expert_pref == 2 && a.expert_cnt < a.max_groups &&
+        (long long)a.max_rows < 16LL * a.max_groups) path = 2;
     if (forced >= 0 && a.gs == 0) {
         path = forced;
         if (path > 0 && (D % 128 || I % 128)) path = 0;
