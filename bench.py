@@ -38,6 +38,7 @@ HBM_SPEC_GBS = 8000.0        # the part's nominal HBM3e bandwidth, quoted beside
 NCU_TRAFFIC = {
     ("c2", 32, "q4_gateup"): (776.06 / 776.67, "profiles/q4_tma_c2_batch32.md"),
     ("c2", 32, "q4_down"): (395.97 / 389.0, "profiles/q4_tma_c2_batch32.md"),
+    ("c2", 256, "q4_gateup"): ((1097.38 + 8.02) / 1090.52, "profiles/q4_umma_c2_batch256.md"),
     ("c3", 4096, "q4_gateup"): ((1421.16 + 83.80) / 1294.96, "profiles/q4_umma_c3_prefill.md"),
     ("c3", 4096, "q4_down"): ((622.61 + 631.14) / 1358.0, "profiles/q4_umma_c3_prefill.md"),
 }
